@@ -59,7 +59,7 @@ def build(force=False, reference_root=None):
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
         objs = list(ex.map(cc, theirs + own))
-    subprocess.check_call(["nvcc", "-shared", "-o", LIB] + objs + ["-lcufft", "-lcublas", "-lcusparse"])
+    subprocess.check_call(["nvcc", "-shared", "-o", LIB] + objs + ["-lcufft", "-lcublas", "-lcusparse", "-Xlinker", "-Bsymbolic"])
     return LIB
 
 

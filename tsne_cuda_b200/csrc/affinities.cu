@@ -1,0 +1,164 @@
+// From neighbour distances to the fixed-width affinity matrix P:
+//   global max-normalisation   (reference: util::MaxNormalizeDeviceVector, src/util/math_utils.cu:66-74)
+//   per-row perplexity search  (reference: src/kernels/perplexity_search.cu:10-141: two elementwise
+//                               kernels, two cuBLAS gemv row reductions and three device syncs per round)
+//   symmetrisation             (reference: syv2k, src/util/math_utils.cu:269-291)
+//
+// Here one warp owns one row for the whole bisection: the row's normalised distances sit in shared
+// memory, the row sums are warp shuffles, and p is written once (4*K bytes read + 4*K written per
+// point).  The update rule, the fast exp/log intrinsics and the 200-round cap follow the reference.
+#include <float.h>
+
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+__global__ void __launch_bounds__(256) absmax_kernel(const float *__restrict__ v, long long n, unsigned int *max_enc)
+{
+    float m = 0.0f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float a = fabsf(v[i]);
+        if (a > m && a < INFINITY) m = a;  // +inf marks an unfilled slot, never a distance
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(max_enc, enc_float(m));
+}
+
+__device__ __forceinline__ float cond_p(int s, float dist, float beta)
+{
+    // slot 0 is the point itself (distance exactly 0): p_ii = 0   (perplexity_search.cu:32)
+    return (s == 0 & dist == 0.0f) ? 0.0f : __expf(-beta * dist);
+}
+
+constexpr int kPerpWarps = 8;
+
+__global__ void __launch_bounds__(kPerpWarps * 32)
+perplexity_kernel(const float *__restrict__ d2, long long n_rows, int K, float perplexity, float eps,
+                  const unsigned int *__restrict__ max_enc, float *__restrict__ p, float *__restrict__ betas)
+{
+    extern __shared__ float srow[];
+    const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
+    const long long row = (long long)blockIdx.x * kPerpWarps + wi;
+    if (row >= n_rows) return;
+    float *d = srow + (size_t)wi * K;
+    const float maxv = dec_float(*max_enc);
+    for (int s = lane; s < K; s += 32) d[s] = d2[row * K + s] / maxv;
+    __syncwarp();
+    const float log_perp = __logf(perplexity);
+    float beta = 1.0f, lo = -FLT_MAX, hi = FLT_MAX;
+    float beta_eval = beta, S = 0.0f;
+    for (int it = 0; it < 200; it++) {
+        float sum = 0.0f, ent = 0.0f;
+        for (int s = lane; s < K; s += 32) {
+            const float v = cond_p(s, d[s], beta);
+            float e = v * logf(v);
+            e = (e != e || isinf(e)) ? 0.0f : e;  // FunctionalEntropy, thrust_transform_functions.h:32-37
+            sum += v;
+            ent += e;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            ent += __shfl_xor_sync(0xffffffffu, ent, o);
+        }
+        S = sum;
+        beta_eval = beta;
+        const float neg_ent = -ent;
+        const float H = (neg_ent / S) + __logf(S);
+        const float diff = H - log_perp;
+        if (diff < eps && -diff < eps) break;
+        if (diff > 0) {
+            lo = beta;
+            beta = (hi == FLT_MAX || hi == -FLT_MAX) ? beta * 2.0f : (beta + hi) / 2.0f;
+        } else {
+            hi = beta;
+            beta = (lo == -FLT_MAX || lo == FLT_MAX) ? beta / 2.0f : (beta + lo) / 2.0f;
+        }
+    }
+    // p of the last evaluated beta divided by its row sum.  A row that exhausts the 200 rounds keeps,
+    // like the reference, the values of the beta evaluated last, not of the beta it would try next.
+    for (int s = lane; s < K; s += 32) p[row * K + s] = cond_p(s, d[s], beta_eval) / S;
+    if (lane == 0 && betas) betas[row] = beta;
+}
+
+// One warp per row i.  For each slot s: j = ids[i][s]; scan the K ids of row j for i and add the
+// matching p[j][.]; divide by 2N in double like the reference.
+constexpr int kSymWarps = 8;
+__global__ void __launch_bounds__(kSymWarps * 32)
+symmetrize_kernel(const float *__restrict__ p, const int32_t *__restrict__ ids, long long N, int K, long long row_lo,
+                  long long n_rows, float *__restrict__ P_rows)
+{
+    const int lane = threadIdx.x & 31;
+    const long long r = (long long)blockIdx.x * kSymWarps + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const long long i = row_lo + r;
+    const double inv = 2.0 * (double)N;
+    for (int s0 = 0; s0 < K; s0 += 32) {
+        const int s_mine = s0 + lane;
+        int j_mine = -1;
+        float p_mine = 0.0f;
+        if (s_mine < K) {
+            j_mine = ids[i * K + s_mine];
+            p_mine = p[i * K + s_mine];
+        }
+        float acc_mine = p_mine;
+        const int cnt = min(32, K - s0);
+        for (int t = 0; t < cnt; t++) {
+            const int j = __shfl_sync(0xffffffffu, j_mine, t);
+            float add = 0.0f;
+            if ((unsigned long long)j < (unsigned long long)N) {
+                const int32_t *rj = ids + (long long)j * K;
+                const float *pj = p + (long long)j * K;
+                for (int u = lane; u < K; u += 32)
+                    if (rj[u] == (int32_t)i) add += pj[u];
+            }
+            // matches are rare (at most one for a valid neighbour list): reduce only when some lane has one
+            if (__any_sync(0xffffffffu, add != 0.0f)) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) add += __shfl_xor_sync(0xffffffffu, add, o);
+                if (lane == t) acc_mine += add;
+            }
+        }
+        if (s_mine < K) P_rows[r * K + s_mine] = (float)((double)acc_mine / inv);
+    }
+}
+
+inline unsigned nblk(long long n, int t) { return (unsigned)((n + t - 1) / t); }
+}  // namespace
+
+int launch_absmax(const float *v, int64_t n, unsigned int *max_enc, cudaStream_t st)
+{
+    if (n <= 0) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    absmax_kernel<<<blocks, 256, 0, st>>>(v, n, max_enc);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_perplexity(const float *d2, int64_t n_rows, int K, float perplexity, float eps, const unsigned int *max_enc,
+                      float *p, float *betas, cudaStream_t st)
+{
+    if (n_rows <= 0) return 0;
+    const size_t smem = (size_t)kPerpWarps * K * sizeof(float);
+    if (smem > 200 * 1024) { set_error("perplexity: num_neighbors too large for the shared-memory row buffer"); return -4; }
+    if (smem > 48 * 1024)
+        B200_CUDA(cudaFuncSetAttribute(perplexity_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    perplexity_kernel<<<nblk(n_rows, kPerpWarps), kPerpWarps * 32, smem, st>>>(d2, n_rows, K, perplexity, eps, max_enc, p,
+                                                                              betas);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_symmetrize(const float *p_all, const int32_t *ids_all, int64_t N, int K, int64_t row_lo, int64_t row_hi,
+                      float *P_rows, cudaStream_t st)
+{
+    const long long n_rows = row_hi - row_lo;
+    if (n_rows <= 0) return 0;
+    symmetrize_kernel<<<nblk(n_rows, kSymWarps), kSymWarps * 32, 0, st>>>(p_all, ids_all, N, K, row_lo, n_rows, P_rows);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace b200

@@ -1,0 +1,122 @@
+// Internal declarations shared by the kernels and the host orchestration of libtsnecuda.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+namespace b200 {
+
+// ---- FIt-SNE grid constants (reference: src/fit_tsne.cu:246-272) ----
+constexpr int kBoxes = 130;            // boxes per dimension (125 rounded up through the allowed list)
+constexpr int kInterp = 3;             // Lagrange nodes per box and dimension
+constexpr int kG = kBoxes * kInterp;   // 390 nodes per dimension
+constexpr int kTerms = 4;              // charges (1, x, y, x^2+y^2)
+constexpr int kM = 1024;               // transform length of the zero-padded convolution (>= 2*kG-1)
+constexpr int kStages = 8;             // instrumented stages (== B200TSNE_N_STAGES)
+
+// ---- error plumbing ----
+void set_error(const std::string &msg);
+const std::string &last_error();
+int cuda_fail(cudaError_t e, const char *what, const char *file, int line);
+
+#define B200_CUDA(expr)                                                        \
+    do {                                                                       \
+        cudaError_t _e = (expr);                                               \
+        if (_e != cudaSuccess) return ::b200::cuda_fail(_e, #expr, __FILE__, __LINE__); \
+    } while (0)
+
+#define B200_TRY(expr)            \
+    do {                          \
+        int _s = (expr);          \
+        if (_s != 0) return _s;   \
+    } while (0)
+
+// Per-iteration scalars that live in device memory so that an iteration needs no host round trip.
+// Slots are double-buffered by iteration parity: iteration `it` reads slot it&1 and prepares slot
+// (it+1)&1 for its successor.
+struct IterState {
+    unsigned int min_enc[2];   // order-preserving encodings of min / max over all coordinates
+    unsigned int max_enc[2];
+    double zsum[2];            // sum_i Z_i accumulated by the gather kernel
+    double unorm2;             // sum of squared updates (only maintained on request)
+    int bad;                   // set when a non-finite coordinate is produced
+    int pad;
+};
+
+// Lagrange constants evaluated on the host exactly as the reference does (src/fit_tsne.cu:303-320).
+struct InterpConsts {
+    float sp[kInterp];
+    float den[kInterp];
+};
+InterpConsts make_interp_consts();
+
+__host__ __device__ inline unsigned int enc_float(float f)
+{
+#ifdef __CUDA_ARCH__
+    unsigned int b = __float_as_uint(f);
+#else
+    union { float f; unsigned int u; } c; c.f = f; unsigned int b = c.u;
+#endif
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__host__ __device__ inline float dec_float(unsigned int e)
+{
+    unsigned int b = (e & 0x80000000u) ? (e & 0x7fffffffu) : ~e;
+#ifdef __CUDA_ARCH__
+    return __uint_as_float(b);
+#else
+    union { float f; unsigned int u; } c; c.u = b; return c.f;
+#endif
+}
+
+// ---- kernel launchers (all asynchronous on `st`; pointers are device memory) ----
+
+// knn.cu
+int launch_transpose(const float *X, int64_t N, int D, float *XT, cudaStream_t st);   // [N][D] -> [D][N]
+int launch_knn_exact(const float *XT, int64_t N, int D, int K, int64_t q_lo, int64_t q_hi, int64_t db_lo,
+                     int64_t db_hi, int32_t *ids, float *d2, cudaStream_t st);   // ids/d2 keep (INT_MAX,+inf) in unfilled slots
+int launch_knn_merge(const int32_t *ids_parts, const float *d2_parts, int parts, int64_t part_stride, int64_t n_rows,
+                     int K, int32_t *ids, float *d2, cudaStream_t st);
+int launch_knn_finalize(int32_t *ids, float *d2, int64_t n, cudaStream_t st);
+
+// affinities.cu
+int launch_absmax(const float *v, int64_t n, unsigned int *max_enc, cudaStream_t st);  // max_enc: enc_float accumulator, pre-set to enc(0)
+int launch_perplexity(const float *d2, int64_t n_rows, int K, float perplexity, float eps, const unsigned int *max_enc,
+                      float *p, float *betas, cudaStream_t st);
+int launch_symmetrize(const float *p_all, const int32_t *ids_all, int64_t N, int K, int64_t row_lo, int64_t row_hi,
+                      float *P_rows, cudaStream_t st);
+
+// attractive.cu   (Y2: AoS float2 [N]; F2: AoS float2, rows [row_lo,row_hi) written at their global index)
+int launch_attractive(const float *P_rows, const int32_t *ids_rows, const float2 *Y2, int64_t N, int K, int64_t row_lo,
+                      int64_t row_hi, float2 *F2, cudaStream_t st);
+
+// repulsive.cu
+struct FftWorkspace {
+    float2 *A;      // [2][kG][kM] row-transformed signal planes
+    float *Rk;      // [kG][kM] row-transformed kernel plane (real part)
+    float2 *B;      // [2][kG][kM] after the fused column pass
+    float2 *tw;     // [kM] forward twiddles e^{-2 pi i k / kM}
+};
+size_t fft_workspace_bytes();
+int fft_workspace_init(FftWorkspace *ws, void *mem, cudaStream_t st);
+int launch_state_reset(IterState *state, cudaStream_t st);   // both slots, sums and flags
+int launch_minmax_init(const float2 *Y2, int64_t N, IterState *state, int slot, cudaStream_t st);
+int launch_spread(const float2 *Y2, int64_t row_lo, int64_t row_hi, const IterState *state, int slot, InterpConsts ic,
+                  float4 *w, cudaStream_t st);
+int launch_convolve(float4 *w, float4 *ytilde, const IterState *state, int slot, const FftWorkspace &ws, bool zero_w,
+                    cudaStream_t st);
+int launch_gather(const float2 *Y2, int64_t row_lo, int64_t row_hi, IterState *state, int slot, InterpConsts ic,
+                  const float4 *ytilde, float2 *Frep2, cudaStream_t st);
+
+// update.cu
+int launch_update(float2 *Y2, const float2 *Fattr2, const float2 *Frep2, float2 *gains2, float2 *u2, int64_t N,
+                  int64_t row_lo, int64_t row_hi, IterState *state, int slot, float eta, float momentum,
+                  float exaggeration, int want_norm, cudaStream_t st);
+int launch_apply_forces_soa(float *Y, float *attr, float *rep, float *gains, float *old_forces, float eta, float Z,
+                            float momentum, float exaggeration, int64_t N, cudaStream_t st);
+int launch_soa_to_aos(const float *soa, float2 *aos, int64_t N, cudaStream_t st);
+int launch_aos_to_soa(const float2 *aos, float *soa, int64_t N, cudaStream_t st);
+int launch_fill(float *p, float v, int64_t n, cudaStream_t st);
+
+}  // namespace b200

@@ -1,0 +1,252 @@
+// Exact k-nearest-neighbour search, SIMT path.
+//
+// Replaces the reference's FAISS IVF-Flat call (src/util/distance_utils.cu:79-121, approximate, with
+// results returned to the host as int64 and re-uploaded) by an exact search that stays on the device
+// and writes int32 ids directly (so src/util/distance_utils.cu:125-154 has no counterpart).
+//
+// Canonical distance: squared L2 accumulated sequentially over d = 0..D-1 in fp32 with every
+// subtract, multiply and add rounded separately (no FMA); results ordered by (distance, id); the
+// query itself is included.  This is reproducible bit for bit on the CPU, which is what makes
+// "identical neighbour ids" a testable statement.
+//
+// Structure: a block owns 64 queries and walks the database in tiles of 128 points.  Distances of a
+// 64x128 tile are accumulated in registers (4x8 per thread) from dimension-major shared-memory
+// tiles, parked in shared memory, and then each warp filters its queries' rows against the current
+// k-th best; the rare survivors are inserted into the sorted result rows by the whole warp.
+// No N x N matrix is ever written.
+#include <limits.h>
+
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int BQ = 64;     // queries per block
+constexpr int BP = 128;    // database points per tile
+constexpr int DCH = 32;    // dimensions per shared-memory chunk
+constexpr int kThreads = 256;
+constexpr int DSTR = BP + 4;  // row stride of the parked distance tile (keeps float4 alignment)
+
+__global__ void transpose_kernel(const float *__restrict__ X, long long N, int D, float *__restrict__ XT)
+{
+    __shared__ float tile[32][33];
+    const long long r0 = (long long)blockIdx.x * 32;
+    const int d0 = blockIdx.y * 32;
+    for (int k = threadIdx.y; k < 32; k += blockDim.y) {
+        const long long r = r0 + k;
+        const int d = d0 + threadIdx.x;
+        tile[k][threadIdx.x] = (r < N && d < D) ? X[r * D + d] : 0.0f;
+    }
+    __syncthreads();
+    for (int k = threadIdx.y; k < 32; k += blockDim.y) {
+        const int d = d0 + k;
+        const long long r = r0 + threadIdx.x;
+        if (d < D && r < N) XT[(long long)d * N + r] = tile[threadIdx.x][k];
+    }
+}
+
+__global__ void knn_init_kernel(int32_t *ids, float *d2, long long n)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { ids[i] = INT_MAX; d2[i] = INFINITY; }
+}
+
+__global__ void knn_finalize_kernel(int32_t *ids, float *d2, long long n)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && ids[i] == INT_MAX) { ids[i] = -1; d2[i] = INFINITY; }
+}
+
+// Insert (d, id) into the ascending list (ld, li) of length K held in global memory; whole warp.
+__device__ __forceinline__ void warp_insert(volatile float *ld, volatile int32_t *li, int K, float d, int id, int lane)
+{
+    int pos = 0;
+    for (int e = lane; e < K; e += 32) {
+        const float de = ld[e];
+        const int ie = li[e];
+        pos += (de < d || (de == d && ie < id)) ? 1 : 0;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) pos += __shfl_xor_sync(0xffffffffu, pos, o);
+    for (int base = ((K - 1) / 32) * 32; base >= 0; base -= 32) {
+        const int e = base + lane;
+        const bool mv = (e > pos && e < K);
+        float de = 0.0f;
+        int ie = 0;
+        if (mv) { de = ld[e - 1]; ie = li[e - 1]; }
+        __syncwarp();
+        if (mv) { ld[e] = de; li[e] = ie; }
+        __syncwarp();
+    }
+    if (lane == 0) { ld[pos] = d; li[pos] = id; }
+    __syncwarp();
+}
+
+// XT: dimension-major copy of X ([D][N]).  Queries [q_lo,q_hi), database [db_lo,db_hi).
+// ids/d2: [(q_hi-q_lo)][K], pre-set to (INT_MAX, +inf).
+__global__ void __launch_bounds__(kThreads, 2)
+knn_exact_kernel(const float *__restrict__ XT, long long N, int D, int K, long long q_lo, long long q_hi, long long db_lo,
+                 long long db_hi, int32_t *ids, float *d2)
+{
+    extern __shared__ __align__(16) float sm[];
+    float *Qs = sm;                          // [DCH][BQ]
+    float *Ps = Qs + DCH * BQ;               // [DCH][BP]
+    float *Dist = Ps + DCH * BP;             // [BQ][DSTR]
+    float *thr_d = Dist + BQ * DSTR;         // [BQ]
+    int *thr_i = reinterpret_cast<int *>(thr_d + BQ);  // [BQ]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tx = tid & 15, ty = tid >> 4;
+    const long long q0 = q_lo + (long long)blockIdx.x * BQ;
+    if (tid < BQ) { thr_d[tid] = INFINITY; thr_i[tid] = INT_MAX; }
+
+    for (long long p0 = db_lo; p0 < db_hi; p0 += BP) {
+        float acc[4][8];
+#pragma unroll
+        for (int a = 0; a < 4; a++)
+#pragma unroll
+            for (int b = 0; b < 8; b++) acc[a][b] = 0.0f;
+
+        for (int d0 = 0; d0 < D; d0 += DCH) {
+            const int dlen = min(DCH, D - d0);
+            __syncthreads();  // previous chunk / previous tile's selection done with the buffers
+            for (int idx = tid; idx < dlen * BQ; idx += kThreads) {
+                const int dd = idx / BQ, q = idx % BQ;
+                const long long gq = q0 + q;
+                Qs[dd * BQ + q] = (gq < q_hi) ? XT[(long long)(d0 + dd) * N + gq] : 0.0f;
+            }
+            for (int idx = tid; idx < dlen * BP; idx += kThreads) {
+                const int dd = idx / BP, pp = idx % BP;
+                const long long gp = p0 + pp;
+                Ps[dd * BP + pp] = (gp < db_hi) ? XT[(long long)(d0 + dd) * N + gp] : 0.0f;
+            }
+            __syncthreads();
+#pragma unroll 4
+            for (int dd = 0; dd < dlen; dd++) {
+                const float4 q4 = *reinterpret_cast<const float4 *>(Qs + dd * BQ + ty * 4);
+                const float4 pa = *reinterpret_cast<const float4 *>(Ps + dd * BP + tx * 4);
+                const float4 pb = *reinterpret_cast<const float4 *>(Ps + dd * BP + 64 + tx * 4);
+                const float qv[4] = {q4.x, q4.y, q4.z, q4.w};
+                const float pv[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+                for (int a = 0; a < 4; a++)
+#pragma unroll
+                    for (int b = 0; b < 8; b++) {
+                        const float t = __fsub_rn(qv[a], pv[b]);
+                        acc[a][b] = __fadd_rn(acc[a][b], __fmul_rn(t, t));
+                    }
+            }
+        }
+        // park the tile
+#pragma unroll
+        for (int a = 0; a < 4; a++) {
+            float *row = Dist + (ty * 4 + a) * DSTR;
+            *reinterpret_cast<float4 *>(row + tx * 4) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+            *reinterpret_cast<float4 *>(row + 64 + tx * 4) = make_float4(acc[a][4], acc[a][5], acc[a][6], acc[a][7]);
+        }
+        __syncthreads();
+        // selection: warp `warp` owns queries warp, warp+8, ...
+        for (int q = warp; q < BQ; q += kThreads / 32) {
+            const long long gq = q0 + q;
+            if (gq >= q_hi) break;
+            const float4 dv = *reinterpret_cast<const float4 *>(Dist + q * DSTR + lane * 4);
+            const float dl[4] = {dv.x, dv.y, dv.z, dv.w};
+            float td = thr_d[q];
+            int ti = thr_i[q];
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const long long gp = p0 + lane * 4 + c;
+                const bool in_db = gp < db_hi;
+                unsigned m = __ballot_sync(0xffffffffu, in_db && (dl[c] < td || (dl[c] == td && (int)gp < ti)));
+                while (m) {
+                    const int src = __ffs(m) - 1;
+                    m &= m - 1;
+                    const float cd = __shfl_sync(0xffffffffu, dl[c], src);
+                    const int ci = (int)(p0 + src * 4 + c);
+                    if (cd < td || (cd == td && ci < ti)) {   // the threshold may have moved since the ballot
+                        volatile float *ld = d2 + (gq - q_lo) * K;
+                        volatile int32_t *li = ids + (gq - q_lo) * K;
+                        warp_insert(ld, li, K, cd, ci, lane);
+                        td = ld[K - 1];
+                        ti = li[K - 1];
+                    }
+                }
+            }
+            if (lane == 0) { thr_d[q] = td; thr_i[q] = ti; }
+        }
+    }
+}
+
+// Merge `parts` ascending lists per row (list p of row r at parts_base + p*part_stride + r*K) into the
+// K best by (distance, id).  One thread per row; used after a database-sharded search.
+__global__ void knn_merge_kernel(const int32_t *__restrict__ ids_parts, const float *__restrict__ d2_parts, int parts,
+                                 long long part_stride, long long n_rows, int K, int32_t *__restrict__ ids,
+                                 float *__restrict__ d2)
+{
+    const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    int head[16];
+    for (int p = 0; p < 16; p++) head[p] = 0;
+    for (int s = 0; s < K; s++) {
+        int best = -1, bi = INT_MAX;
+        float bd = INFINITY;
+        for (int p = 0; p < parts; p++) {
+            if (head[p] >= K) continue;
+            const long long o = (long long)p * part_stride + r * K + head[p];
+            const int ci = ids_parts[o];
+            const float cd = d2_parts[o];
+            if (best < 0 || cd < bd || (cd == bd && ci < bi)) { best = p; bd = cd; bi = ci; }
+        }
+        ids[r * K + s] = bi;
+        d2[r * K + s] = bd;
+        if (best >= 0) head[best]++;
+    }
+}
+
+constexpr size_t kKnnSmem = sizeof(float) * (DCH * BQ + DCH * BP + BQ * DSTR + BQ) + sizeof(int) * BQ;
+}  // namespace
+
+int launch_knn_finalize(int32_t *ids, float *d2, int64_t n, cudaStream_t st)
+{
+    if (n <= 0) return 0;
+    knn_finalize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ids, d2, n);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_knn_merge(const int32_t *ids_parts, const float *d2_parts, int parts, int64_t part_stride, int64_t n_rows,
+                     int K, int32_t *ids, float *d2, cudaStream_t st)
+{
+    if (n_rows <= 0) return 0;
+    if (parts > 16) { set_error("knn merge: more than 16 partial lists"); return -4; }
+    knn_merge_kernel<<<(unsigned)((n_rows + 127) / 128), 128, 0, st>>>(ids_parts, d2_parts, parts, part_stride, n_rows, K,
+                                                                      ids, d2);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_transpose(const float *X, int64_t N, int D, float *XT, cudaStream_t st)
+{
+    if (N <= 0 || D <= 0) return 0;
+    dim3 grid((unsigned)((N + 31) / 32), (unsigned)((D + 31) / 32));
+    transpose_kernel<<<grid, dim3(32, 8), 0, st>>>(X, N, D, XT);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// XT is the dimension-major copy of X produced by launch_transpose.
+int launch_knn_exact(const float *XT, int64_t N, int D, int K, int64_t q_lo, int64_t q_hi, int64_t db_lo,
+                     int64_t db_hi, int32_t *ids, float *d2, cudaStream_t st)
+{
+    const long long nq = q_hi - q_lo;
+    if (nq <= 0) return 0;
+    const long long n = nq * K;
+    knn_init_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ids, d2, n);
+    B200_CUDA(cudaGetLastError());
+    B200_CUDA(cudaFuncSetAttribute(knn_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKnnSmem));
+    knn_exact_kernel<<<(unsigned)((nq + BQ - 1) / BQ), kThreads, kKnnSmem, st>>>(XT, N, D, K, q_lo, q_hi, db_lo, db_hi, ids, d2);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace b200

@@ -1,0 +1,331 @@
+// Host orchestration of the device-resident FIt-SNE state: allocation, the set-up pipeline from
+// points to affinities, and the gradient loop (reference: the body of tsnecuda::RunTsne,
+// src/fit_tsne.cu:84-166 for the set-up and :402-580 for the loop).
+//
+// One iteration is seven kernels and no host synchronisation:
+//   stream  : spread -> FFT rows -> FFT columns -> FFT rows^-1 -> gather ------------> update
+//   stream2 : attractive (HBM-bound, overlaps the latency-bound grid pipeline) ------^
+// The embedding's min/max and the normalisation sum travel between kernels in device memory
+// (IterState), so the two per-iteration host round trips of the reference do not exist.
+#include "session.h"
+
+#include <math.h>
+#include <string.h>
+
+#include <algorithm>
+#include <string>
+
+#include "comm.h"
+
+namespace b200 {
+
+// ---- error plumbing -------------------------------------------------------------------------
+static thread_local std::string g_last_error;
+void set_error(const std::string &msg) { g_last_error = msg; }
+const std::string &last_error() { return g_last_error; }
+int cuda_fail(cudaError_t e, const char *what, const char *file, int line)
+{
+    g_last_error = std::string("CUDA error '") + cudaGetErrorString(e) + "' in " + what + " at " + file + ":" +
+                   std::to_string(line);
+    return -2;
+}
+
+// ---- arena ------------------------------------------------------------------------------------
+DeviceArena::~DeviceArena() { release(); }
+int DeviceArena::alloc(void **p, size_t bytes)
+{
+    *p = nullptr;
+    if (bytes == 0) bytes = 16;
+    B200_CUDA(cudaMalloc(p, bytes));
+    ptrs.push_back(*p);
+    return 0;
+}
+void DeviceArena::release()
+{
+    for (void *p : ptrs) cudaFree(p);
+    ptrs.clear();
+}
+
+// ---- session ------------------------------------------------------------------------------------
+int Session::init(int64_t N_, int K_, int64_t lo, int64_t hi, int device_)
+{
+    if (N_ <= 0 || K_ <= 0 || lo < 0 || hi > N_ || lo > hi) { set_error("session: invalid sizes"); return -1; }
+    if (N_ >= (int64_t)1 << 31) { set_error("session: more than 2^31-1 points are not supported (int32 ids)"); return -4; }
+    N = N_; K = K_; row_lo = lo; row_hi = hi; device = device_;
+    B200_CUDA(cudaSetDevice(device));
+    B200_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    B200_CUDA(cudaStreamCreateWithFlags(&stream2, cudaStreamNonBlocking));
+    B200_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+    B200_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
+    B200_CUDA(cudaEventCreate(&ev_t0));
+    B200_CUDA(cudaEventCreate(&ev_t1));
+    // Y2 and the force arrays are padded so that an in-place all-gather over up to 16 ranks fits
+    const int64_t npad = N + 16;
+    const int64_t r = std::max<int64_t>(rows(), 1);
+    B200_TRY(arena.alloc((void **)&P, sizeof(float) * r * K));
+    B200_TRY(arena.alloc((void **)&ids, sizeof(int32_t) * r * K));
+    B200_TRY(arena.alloc((void **)&Y2, sizeof(float2) * npad));
+    B200_TRY(arena.alloc((void **)&Fattr, sizeof(float2) * npad));
+    B200_TRY(arena.alloc((void **)&Frep, sizeof(float2) * npad));
+    B200_TRY(arena.alloc((void **)&gains, sizeof(float2) * r));
+    B200_TRY(arena.alloc((void **)&u, sizeof(float2) * r));
+    B200_TRY(arena.alloc((void **)&soa_tmp, sizeof(float) * 2 * N));
+    B200_TRY(arena.alloc((void **)&w, sizeof(float4) * kG * kG));
+    B200_TRY(arena.alloc((void **)&ytilde, sizeof(float4) * kG * kG));
+    B200_TRY(arena.alloc(&fft_mem, fft_workspace_bytes()));
+    B200_TRY(arena.alloc((void **)&state, sizeof(IterState)));
+    B200_CUDA(cudaMallocHost((void **)&h_state, sizeof(IterState)));
+    B200_TRY(fft_workspace_init(&fft, fft_mem, stream));
+    ic = make_interp_consts();
+    B200_CUDA(cudaMemsetAsync(w, 0, sizeof(float4) * kG * kG, stream));
+    B200_CUDA(cudaMemsetAsync(Y2, 0, sizeof(float2) * npad, stream));
+    B200_CUDA(cudaMemsetAsync(Fattr, 0, sizeof(float2) * npad, stream));
+    B200_CUDA(cudaMemsetAsync(Frep, 0, sizeof(float2) * npad, stream));
+    B200_TRY(launch_state_reset(state, stream));
+    B200_TRY(launch_fill(reinterpret_cast<float *>(gains), 1.0f, 2 * r, stream));
+    B200_CUDA(cudaMemsetAsync(u, 0, sizeof(float2) * r, stream));
+    B200_CUDA(cudaStreamSynchronize(stream));
+    return 0;
+}
+
+void Session::destroy()
+{
+    cudaSetDevice(device);
+    if (stream) cudaStreamSynchronize(stream);
+    if (stream2) cudaStreamSynchronize(stream2);
+    if (comm) { comm->destroy(); delete comm; comm = nullptr; }
+    arena.release();
+    if (h_state) cudaFreeHost(h_state);
+    if (ev_fork) cudaEventDestroy(ev_fork);
+    if (ev_join) cudaEventDestroy(ev_join);
+    if (ev_t0) cudaEventDestroy(ev_t0);
+    if (ev_t1) cudaEventDestroy(ev_t1);
+    if (stream) cudaStreamDestroy(stream);
+    if (stream2) cudaStreamDestroy(stream2);
+    h_state = nullptr; stream = stream2 = nullptr; ev_fork = ev_join = ev_t0 = ev_t1 = nullptr;
+}
+
+int Session::set_embedding_soa(const float *Y_host, bool reset)
+{
+    B200_CUDA(cudaSetDevice(device));
+    B200_CUDA(cudaMemcpyAsync(soa_tmp, Y_host, sizeof(float) * 2 * N, cudaMemcpyHostToDevice, stream));
+    B200_TRY(launch_soa_to_aos(soa_tmp, Y2, N, stream));
+    if (reset) {
+        const int64_t r = std::max<int64_t>(rows(), 1);
+        B200_TRY(launch_fill(reinterpret_cast<float *>(gains), 1.0f, 2 * r, stream));
+        B200_CUDA(cudaMemsetAsync(u, 0, sizeof(float2) * r, stream));
+        step = 0;
+    }
+    B200_TRY(launch_state_reset(state, stream));
+    B200_TRY(launch_minmax_init(Y2, N, state, step & 1, stream));
+    B200_CUDA(cudaMemsetAsync(w, 0, sizeof(float4) * kG * kG, stream));
+    B200_CUDA(cudaStreamSynchronize(stream));
+    launches += 4;
+    return 0;
+}
+
+int Session::get_embedding_soa(float *Y_host)
+{
+    B200_CUDA(cudaSetDevice(device));
+    B200_TRY(launch_aos_to_soa(Y2, soa_tmp, N, stream));
+    B200_CUDA(cudaMemcpyAsync(Y_host, soa_tmp, sizeof(float) * 2 * N, cudaMemcpyDeviceToHost, stream));
+    B200_CUDA(cudaStreamSynchronize(stream));
+    launches += 1;
+    return 0;
+}
+
+namespace {
+// Times the stages of one iteration when stage timers are on (serialised on one stream).
+struct StageClock {
+    Session *s;
+    cudaEvent_t a = nullptr, b = nullptr;
+    explicit StageClock(Session *s_) : s(s_)
+    {
+        if (s->stage_timers) { cudaEventCreate(&a); cudaEventCreate(&b); }
+    }
+    ~StageClock()
+    {
+        if (a) cudaEventDestroy(a);
+        if (b) cudaEventDestroy(b);
+    }
+    void begin(cudaStream_t st) { if (a) cudaEventRecord(a, st); }
+    void end(cudaStream_t st, int stage, int n_launches)
+    {
+        s->stage_launches[stage] += n_launches;
+        s->launches += n_launches;
+        if (!a) return;
+        cudaEventRecord(b, st);
+        cudaEventSynchronize(b);
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, a, b);
+        s->stage_ms[stage] += ms;
+    }
+};
+}  // namespace
+
+int Session::one_iteration(bool want_norm)
+{
+    const int slot = step & 1;
+    const bool late = step >= force_magnify_iters;
+    const float momentum = late ? post_momentum : pre_momentum;
+    const float exag = late ? 1.0f : exaggeration;
+    const bool multi = comm && comm->world > 1;
+    StageClock clk(this);
+    cudaStream_t sa = stage_timers ? stream : stream2;  // attractive stream
+
+    if (!stage_timers) {
+        B200_CUDA(cudaEventRecord(ev_fork, stream));
+        B200_CUDA(cudaStreamWaitEvent(stream2, ev_fork, 0));
+        B200_TRY(launch_attractive(P, ids, Y2, N, K, row_lo, row_hi, Fattr, sa));
+        B200_CUDA(cudaEventRecord(ev_join, stream2));
+        stage_launches[kStAttractive] += 1;
+        launches += 1;
+    }
+
+    clk.begin(stream);
+    B200_TRY(launch_spread(Y2, row_lo, row_hi, state, slot, ic, w, stream));
+    clk.end(stream, kStSpread, 1);
+    if (multi) {
+        clk.begin(stream);
+        B200_TRY(comm->all_reduce_sum_f32(reinterpret_cast<float *>(w), (size_t)kG * kG * 4, stream));
+        clk.end(stream, kStExchange, 0);
+    }
+    clk.begin(stream);
+    B200_TRY(launch_convolve(w, ytilde, state, slot, fft, true, stream));
+    clk.end(stream, kStConvolve, 3);
+    clk.begin(stream);
+    B200_TRY(launch_gather(Y2, row_lo, row_hi, state, slot, ic, ytilde, Frep, stream));
+    clk.end(stream, kStGather, 1);
+    if (multi) {
+        clk.begin(stream);
+        B200_TRY(comm->all_reduce_sum_f64(&state->zsum[slot], 1, stream));
+        clk.end(stream, kStExchange, 0);
+    }
+    if (stage_timers) {
+        clk.begin(stream);
+        B200_TRY(launch_attractive(P, ids, Y2, N, K, row_lo, row_hi, Fattr, stream));
+        clk.end(stream, kStAttractive, 1);
+    } else {
+        B200_CUDA(cudaStreamWaitEvent(stream, ev_join, 0));
+    }
+    clk.begin(stream);
+    B200_TRY(launch_update(Y2, Fattr, Frep, gains, u, N, row_lo, row_hi, state, slot, eta, momentum, exag,
+                           want_norm ? 1 : 0, stream));
+    clk.end(stream, kStUpdate, 1);
+    if (multi) {
+        clk.begin(stream);
+        const int64_t chunk = (N + comm->world - 1) / comm->world;
+        B200_TRY(comm->all_gather_inplace(Y2, sizeof(float2) * (size_t)chunk, stream));
+        B200_TRY(launch_minmax_init(Y2, N, state, slot ^ 1, stream));
+        clk.end(stream, kStExchange, 2);
+    }
+    step++;
+    return 0;
+}
+
+int Session::iterate(int n_iters, float min_gradient_norm, float *elapsed_ms, int *iters_done)
+{
+    B200_CUDA(cudaSetDevice(device));
+    const bool early_stop = min_gradient_norm > 0.0f;
+    const bool want_norm = early_stop || force_norm;
+    int done = 0;
+    B200_CUDA(cudaEventRecord(ev_t0, stream));
+    for (int it = 0; it < n_iters; it++) {
+        if (want_norm) B200_CUDA(cudaMemsetAsync(&state->unorm2, 0, sizeof(double), stream));
+        B200_TRY(one_iteration(want_norm));
+        done++;
+        if (early_stop) {
+            B200_CUDA(cudaMemcpyAsync(h_state, state, sizeof(IterState), cudaMemcpyDeviceToHost, stream));
+            B200_CUDA(cudaStreamSynchronize(stream));
+            double n2 = h_state->unorm2;
+            if (comm && comm->world > 1) {
+                // every rank must take the same decision: sum the squared norms
+                B200_TRY(comm->all_reduce_sum_f64(&state->unorm2, 1, stream));
+                B200_CUDA(cudaMemcpyAsync(h_state, state, sizeof(IterState), cudaMemcpyDeviceToHost, stream));
+                B200_CUDA(cudaStreamSynchronize(stream));
+                n2 = h_state->unorm2;
+            }
+            last_unorm = (float)sqrt(n2);
+            if (last_unorm < min_gradient_norm) break;
+        }
+    }
+    B200_CUDA(cudaEventRecord(ev_t1, stream));
+    B200_CUDA(cudaMemcpyAsync(h_state, state, sizeof(IterState), cudaMemcpyDeviceToHost, stream));
+    B200_CUDA(cudaStreamSynchronize(stream));
+    B200_CUDA(cudaStreamSynchronize(stream2));
+    if (elapsed_ms) B200_CUDA(cudaEventElapsedTime(elapsed_ms, ev_t0, ev_t1));
+    if (iters_done) *iters_done = done;
+    if (done > 0) last_Z = (float)h_state->zsum[(step - 1) & 1] - (float)N;
+    if (want_norm && !early_stop && done > 0) last_unorm = (float)sqrt(h_state->unorm2);
+    if (h_state->bad) { set_error("non-finite coordinates in the embedding"); return -3; }
+    return 0;
+}
+
+// ---- set-up: points -> kNN -> perplexity -> symmetrised fixed-width P ------------------------------
+int Session::affinities_from_points(const float *X_host, int D, float perplexity, float eps)
+{
+    B200_CUDA(cudaSetDevice(device));
+    if (D <= 0 || !X_host) { set_error("affinities: invalid points"); return -1; }
+    if (K > N) { set_error("affinities: num_neighbors exceeds num_points"); return -1; }
+    const bool multi = comm && comm->world > 1;
+    DeviceArena tmp;
+    float *X = nullptr, *XT = nullptr, *d2 = nullptr, *p_all = nullptr;
+    int32_t *ids_all = nullptr;
+    unsigned int *max_enc = nullptr;
+    const int64_t r = rows();
+    const int64_t chunk = multi ? (N + comm->world - 1) / comm->world : N;
+    const int64_t npad = multi ? chunk * comm->world : N;
+
+    StageClock clk(this);
+    clk.begin(stream);
+    B200_TRY(tmp.alloc((void **)&X, sizeof(float) * N * D));
+    B200_TRY(tmp.alloc((void **)&XT, sizeof(float) * N * D));
+    B200_CUDA(cudaMemcpyAsync(X, X_host, sizeof(float) * N * D, cudaMemcpyHostToDevice, stream));
+    B200_TRY(launch_transpose(X, N, D, XT, stream));
+    B200_TRY(tmp.alloc((void **)&d2, sizeof(float) * std::max<int64_t>(chunk, 1) * K));
+    B200_TRY(tmp.alloc((void **)&max_enc, sizeof(unsigned int)));
+    if (!multi) {
+        B200_TRY(launch_knn_exact(XT, N, D, K, row_lo, row_hi, 0, N, ids, d2, stream));
+    } else {
+        // database sharded by rows: every rank searches all queries against its own rows, the
+        // owners of the query rows receive the partial lists and merge them
+        int32_t *part_i = nullptr, *recv_i = nullptr;
+        float *part_d = nullptr, *recv_d = nullptr;
+        B200_TRY(tmp.alloc((void **)&part_i, sizeof(int32_t) * npad * K));
+        B200_TRY(tmp.alloc((void **)&part_d, sizeof(float) * npad * K));
+        B200_TRY(tmp.alloc((void **)&recv_i, sizeof(int32_t) * npad * K));
+        B200_TRY(tmp.alloc((void **)&recv_d, sizeof(float) * npad * K));
+        B200_CUDA(cudaMemsetAsync(part_i, 0x7f, sizeof(int32_t) * npad * K, stream));
+        B200_CUDA(cudaMemsetAsync(part_d, 0x7f, sizeof(float) * npad * K, stream));
+        B200_TRY(launch_knn_exact(XT, N, D, K, 0, N, row_lo, row_hi, part_i, part_d, stream));
+        B200_TRY(comm->all_to_all(part_i, recv_i, sizeof(int32_t) * (size_t)chunk * K, stream));
+        B200_TRY(comm->all_to_all(part_d, recv_d, sizeof(float) * (size_t)chunk * K, stream));
+        B200_TRY(launch_knn_merge(recv_i, recv_d, comm->world, chunk * K, r, K, ids, d2, stream));
+    }
+    B200_TRY(launch_knn_finalize(ids, d2, r * K, stream));
+    clk.end(stream, kStKnn, 4);
+
+    clk.begin(stream);
+    const unsigned int zero_enc = enc_float(0.0f);
+    B200_CUDA(cudaMemcpyAsync(max_enc, &zero_enc, sizeof(unsigned int), cudaMemcpyHostToDevice, stream));
+    B200_TRY(launch_absmax(d2, r * K, max_enc, stream));
+    if (multi) B200_TRY(comm->all_reduce_max_u32(max_enc, 1, stream));
+    B200_TRY(tmp.alloc((void **)&p_all, sizeof(float) * npad * K));
+    float *p_rows = p_all + (multi ? (size_t)comm->rank * chunk * K : 0);
+    B200_TRY(launch_perplexity(d2, r, K, perplexity, eps, max_enc, p_rows, nullptr, stream));
+    const int32_t *ids_for_sym = ids;
+    if (multi) {
+        B200_TRY(tmp.alloc((void **)&ids_all, sizeof(int32_t) * npad * K));
+        B200_CUDA(cudaMemcpyAsync(ids_all + (size_t)comm->rank * chunk * K, ids, sizeof(int32_t) * r * K,
+                                  cudaMemcpyDeviceToDevice, stream));
+        B200_TRY(comm->all_gather_inplace(ids_all, sizeof(int32_t) * (size_t)chunk * K, stream));
+        B200_TRY(comm->all_gather_inplace(p_all, sizeof(float) * (size_t)chunk * K, stream));
+        ids_for_sym = ids_all;
+    }
+    B200_TRY(launch_symmetrize(p_all, ids_for_sym, N, K, row_lo, row_hi, P, stream));
+    clk.end(stream, kStAffinities, 3);
+    B200_CUDA(cudaStreamSynchronize(stream));
+    return 0;
+}
+
+}  // namespace b200

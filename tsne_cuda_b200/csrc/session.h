@@ -1,0 +1,77 @@
+// Device-resident state of one FIt-SNE run on one GPU (one rank of a multi-GPU run).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <vector>
+
+#include "common.cuh"
+
+namespace b200 {
+
+struct Comm;  // comm.h
+
+enum Stage { kStSpread = 0, kStConvolve, kStGather, kStAttractive, kStUpdate, kStExchange, kStKnn, kStAffinities };
+
+// RAII holder for device allocations of a session
+struct DeviceArena {
+    std::vector<void *> ptrs;
+    ~DeviceArena();
+    int alloc(void **p, size_t bytes);
+    void release();
+};
+
+struct Session {
+    int device = 0;
+    int64_t N = 0;           // all points
+    int K = 0;
+    int64_t row_lo = 0, row_hi = 0;  // owned rows
+    cudaStream_t stream = nullptr;
+    cudaStream_t stream2 = nullptr;  // attractive force overlaps the grid pipeline
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_t0 = nullptr, ev_t1 = nullptr;
+    DeviceArena arena;
+
+    // affinities (owned rows)
+    float *P = nullptr;       // [rows][K]
+    int32_t *ids = nullptr;   // [rows][K]
+    // embedding and optimiser state
+    float2 *Y2 = nullptr;     // [N] AoS, replicated on every rank
+    float2 *Fattr = nullptr;  // [N] (owned rows valid)
+    float2 *Frep = nullptr;   // [N] (owned rows valid)
+    float2 *gains = nullptr;  // [rows]
+    float2 *u = nullptr;      // [rows]
+    float *soa_tmp = nullptr; // [2N] staging for SoA <-> AoS conversion
+    // grid
+    float4 *w = nullptr;      // [G][G]
+    float4 *ytilde = nullptr; // [G][G]
+    void *fft_mem = nullptr;
+    FftWorkspace fft;
+    IterState *state = nullptr;
+    IterState *h_state = nullptr;  // pinned mirror
+    InterpConsts ic;
+
+    // schedule
+    float eta = 200.0f, exaggeration = 12.0f, pre_momentum = 0.5f, post_momentum = 0.8f;
+    int force_magnify_iters = 250;
+    int step = 0;
+    float last_Z = 0.0f, last_unorm = 0.0f;
+
+    // instrumentation
+    bool stage_timers = false;
+    bool force_norm = false;   // maintain the update norm even without an early-stop threshold
+    float stage_ms[kStages] = {0};
+    int64_t stage_launches[kStages] = {0};
+    int64_t launches = 0;
+
+    Comm *comm = nullptr;  // null on a single GPU
+
+    int64_t rows() const { return row_hi - row_lo; }
+    int init(int64_t N, int K, int64_t row_lo, int64_t row_hi, int device);
+    void destroy();
+    int set_embedding_soa(const float *Y_host, bool reset);
+    int get_embedding_soa(float *Y_host);
+    int iterate(int n_iters, float min_gradient_norm, float *elapsed_ms, int *iters_done);
+    int one_iteration(bool want_norm);
+    int affinities_from_points(const float *X_host, int D, float perplexity, float eps);
+};
+
+}  // namespace b200
