@@ -1,0 +1,312 @@
+#!/usr/bin/env python
+"""Benchmark of the FIt-SNE hot path: gradient iterations/s and fit_transform seconds.
+
+  python bench.py --gpus 1 --steps K --warmup W            # this engine, 1 GPU
+  torchrun ... bench.py --gpus N --steps K --warmup W      # one rank per GPU, points sharded
+  python bench.py --impl reference ...                     # the reference's own CUDA build (oracle/_ref)
+
+A "step" is one gradient iteration (spread, FFT convolution, gather, attractive force, update) on
+the N = 1,000,000, D = 50 synthetic Gaussian mixture with exact 90-NN affinities (config c3).
+`value` is iterations/s with P, ids and Y resident in HBM, timed with CUDA events on the stream the
+kernels are launched on (inside libtsnecuda.so); `e2e` is a complete fit_transform through the
+drop-in symbol pymodule_tsne from host X to host Y.  One JSON line is printed by rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+G2 = 390 * 390
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(object):
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()   # the exact process started above
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for k, nm in enumerate(names):
+                if len(r) > 3 + k and r[3 + k].lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def workload(args):
+    from tsne_cuda_b200 import datasets
+    X, hp = datasets.make(args.config, n=args.n)
+    Y0 = datasets.initial_embedding(X.shape[0])
+    return X, hp, Y0
+
+
+def iter_bytes(n, k):
+    """Algorithmic bytes of one gradient iteration: 8NK + 104N + 48G^2 (P value + id per stored entry,
+    Y / force / gains / momentum traffic per point, three passes over the four-term grid)."""
+    return 8.0 * n * k + 104.0 * n + 48.0 * G2
+
+
+def run_ours(args):
+    from tsne_cuda_b200 import _lib, distributed
+    rank, local_rank, world = distributed.env_rank()
+    multi = world > 1
+    if multi:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl")
+    X, hp, Y0 = workload(args)
+    N, D = X.shape
+    K = hp["num_neighbors"]
+    lo, hi = distributed.shard_rows(N, world, rank)
+    s = distributed.open_session(N, K, rank, local_rank, world)
+    t0 = time.time()
+    s.affinities_from_points(X, hp["perplexity"], 1e-3)
+    setup_s = time.time() - t0
+    s.set_schedule(hp["learning_rate"], hp["early_exaggeration"], 250, 0.5, 0.8)
+    s.set_embedding(Y0)
+    s.run(args.warmup)
+
+    def barrier():
+        if multi:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    barrier()
+    l0 = s.launch_count()
+    with ClockSampler(local_rank) as clk:
+        ms, done = s.run(args.steps)
+    barrier()
+    launches = s.launch_count() - l0
+    if multi:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = args.steps / (ms * 1e-3)
+
+    # per-kernel durations of the same loop, stages serialised on one stream, CUDA events per stage
+    s.enable_stage_timers(True)
+    n_prof = max(5, min(50, args.steps))
+    s.run(n_prof)
+    stages = s.stage_times()
+    s.enable_stage_timers(False)
+    stage_us = {k: (v[0] / max(v[1], 1) * 1e3 * (3 if k == "convolve" else 1)) for k, v in stages.items() if v[1] > 0}
+    attr_s = stages["attractive"][0] / max(stages["attractive"][1], 1) * 1e-3
+    rows = hi - lo
+    attr_bytes = 8.0 * rows * K + 16.0 * rows
+    peak, peak_kind = load_peaks()
+    roof = {"bound": "hbm", "kernel": "attractive_kernel", "achieved": attr_bytes / attr_s / 1e9 if attr_s > 0 else None,
+            "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "traffic": None,
+            "algorithmic_bytes_per_launch": attr_bytes, "avg_launch_us": attr_s * 1e6}
+    roof["frac"] = roof["achieved"] / peak if roof["achieved"] else None
+    it_bytes = iter_bytes(N, K) / world
+    roof["iteration"] = {"achieved": it_bytes / (ms * 1e-3 / args.steps) / 1e9, "frac": it_bytes / (ms * 1e-3 / args.steps) / 1e9 / peak,
+                         "algorithmic_bytes": it_bytes}
+    s.close()
+
+    out = {"metric": "gradient_iterations_per_s", "value": value, "unit": "iterations/s", "n_gpus": world,
+           "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+           "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+           "config": {"workload": "%s: N=%d D=%d K=%d perplexity=%g, 4-component Gaussian mixture, exact kNN" %
+                                  (args.config, N, D, K, hp["perplexity"]),
+                      "l2_policy": "inputs larger than L2 (P+ids = %.0f MB per iteration)" % (8.0 * N * K / 1e6),
+                      "parallelism": "points sharded over %d GPU(s)" % world},
+           "gpu_launches": int(launches), "setup_s": setup_s, "stage_us_per_iteration": stage_us,
+           "roofline": roof, "clocks": clk.summary()}
+
+    if rank == 0 and not multi and not args.no_e2e:
+        out["e2e"] = e2e_ours(X, hp, Y0, args)
+    elif multi:
+        out["e2e"] = e2e_sharded(X, hp, Y0, args, rank, local_rank, world)
+    if rank == 0 and not multi and not args.no_cpu:
+        out["cpu_baseline"] = cpu_baseline(X, hp, Y0, args)
+    if multi:
+        dist.destroy_process_group()
+    return out if rank == 0 else None
+
+
+def e2e_ours(X, hp, Y0, args):
+    """fit_transform through the drop-in symbol: host X -> host Y, everything inside the timed region."""
+    from tsne_cuda_b200 import TSNE
+    n_iter = args.e2e_iters
+    t = TSNE(perplexity=hp["perplexity"], num_neighbors=hp["num_neighbors"], learning_rate=hp["learning_rate"],
+             early_exaggeration=hp["early_exaggeration"], n_iter=n_iter, perplexity_epsilon=1e-3)
+    y0 = np.asfortranarray(Y0.T)
+    t0 = time.time()
+    Y = t.fit_transform(X, y0)
+    T = time.time() - t0
+    assert np.isfinite(Y).all()
+    return {"value": n_iter / T, "unit": "iterations/s", "fit_transform_s": T, "iterations": n_iter,
+            "h2d_bytes_per_step": (X.nbytes + Y0.nbytes) / n_iter, "d2h_bytes_per_step": Y0.nbytes / n_iter,
+            "api": "tsne_cuda_b200.TSNE.fit_transform -> pymodule_tsne"}
+
+
+def e2e_sharded(X, hp, Y0, args, rank, local_rank, world):
+    """Host X -> host Y through the session C ABI on every rank (the 31-argument symbol carries one device)."""
+    import torch
+    import torch.distributed as dist
+    from tsne_cuda_b200 import distributed
+    n_iter = args.e2e_iters
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    s = distributed.open_session(X.shape[0], hp["num_neighbors"], rank, local_rank, world)
+    s.affinities_from_points(X, hp["perplexity"], 1e-3)
+    s.set_schedule(hp["learning_rate"], hp["early_exaggeration"], 250, 0.5, 0.8)
+    s.set_embedding(Y0)
+    s.run(n_iter)
+    Y = s.get_embedding()
+    dist.barrier()
+    T = time.time() - t0
+    s.close()
+    t = torch.tensor([T], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    T = float(t.item())
+    assert np.isfinite(Y).all()
+    return {"value": n_iter / T, "unit": "iterations/s", "fit_transform_s": T, "iterations": n_iter,
+            "h2d_bytes_per_step": (X.nbytes + Y0.nbytes) / n_iter, "d2h_bytes_per_step": Y0.nbytes / n_iter,
+            "api": "b200tsne_session_* on every rank"}
+
+
+def cpu_baseline(X, hp, Y0, args, budget_s=20.0):
+    """The OpenMP restatement of the same iteration (oracle/), timed on a bounded sample: random
+    fixed-width affinities of the workload's shape (the iteration's cost does not depend on their
+    values) and as many iterations as fit in ~20 s."""
+    from oracle import cpu
+    N, K = X.shape[0], hp["num_neighbors"]
+    rng = np.random.default_rng(1)
+    ids = rng.integers(0, N, (N, K), dtype=np.int32)
+    P = np.full((N, K), 1.0 / (N * K), np.float32)
+    Y = (rng.standard_normal((2, N)) * 10).astype(np.float32)
+    t0 = time.time()
+    cpu.iterate(P, ids, Y, 1, hp["learning_rate"])
+    one = time.time() - t0
+    n = int(max(1, min(50, budget_s / max(one, 1e-3))))
+    t0 = time.time()
+    cpu.iterate(P, ids, Y, n, hp["learning_rate"])
+    T = time.time() - t0
+    return {"value": n / T, "unit": "iterations/s", "cores": cpu.num_threads(), "kind": "port",
+            "sample": "%d full gradient iterations at N=%d K=%d on random affinities of the workload's shape" % (n, N, K)}
+
+
+def run_reference(args):
+    """The reference's own CUDA kernels (oracle/_ref, compiled from the reference tree for sm_100) through
+    its own pymodule_tsne.  The reference's neighbour search is FAISS, which is not installed; the exact
+    neighbour list is computed beforehand (outside the timed region) and injected.  When the reference
+    build is absent the OpenMP port is timed instead."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    from oracle import ref
+    X, hp, Y0 = workload(args)
+    N, D = X.shape
+    K = hp["num_neighbors"]
+    base = {"impl": "reference", "metric": "gradient_iterations_per_s", "unit": "iterations/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "%s: N=%d D=%d K=%d perplexity=%g, 4-component Gaussian mixture, exact kNN" %
+                                   (args.config, N, D, K, hp["perplexity"])}}
+    if not ref.available():
+        cb = cpu_baseline(X, hp, Y0, args, budget_s=60.0)
+        base.update({"value": cb["value"], "ms_per_step": 1e3 / cb["value"], "cpu_baseline": cb,
+                     "e2e": {"value": cb["value"], "unit": "iterations/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+        return base
+    from tsne_cuda_b200 import _lib
+    ids, d2 = _lib.knn(X, K)          # outside the timed region; stands in for the missing FAISS search
+    ref.set_knn(ids, d2)
+    kw = dict(perplexity=hp["perplexity"], learning_rate=hp["learning_rate"], num_neighbors=K,
+              early_exaggeration=hp["early_exaggeration"], perplexity_search_epsilon=1e-3)
+
+    def timed(n_iter):
+        t0 = time.time()
+        Y = ref.fit_transform(X, Y0, iterations=n_iter, **kw)
+        return time.time() - t0, Y
+
+    timed(max(args.warmup, 3))                      # context, plans, first-use costs
+    with ClockSampler(0) as clk:
+        t_a, _ = timed(args.warmup)
+        t_b, Y = timed(args.warmup + args.steps)
+    loop = max(t_b - t_a, 1e-9)
+    value = args.steps / loop
+    base.update({"value": value, "ms_per_step": loop / args.steps * 1e3, "clocks": clk.summary(),
+                 "cpu_baseline": {"value": value, "unit": "iterations/s", "cores": 1, "kind": "reference",
+                                  "sample": "reference CUDA kernels on the GPU driven by one host thread; "
+                                            "difference of two pymodule_tsne calls (%d and %d iterations), "
+                                            "neighbour list injected" % (args.warmup, args.warmup + args.steps)},
+                 "e2e": {"value": (args.warmup + args.steps) / t_b, "unit": "iterations/s", "fit_transform_s": t_b,
+                         "iterations": args.warmup + args.steps, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                         "note": "excludes the neighbour search (injected)"},
+                 "finite": bool(np.isfinite(Y).all())})
+    return base
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="c3")
+    ap.add_argument("--n", type=int, default=None, help="override the number of points (debugging)")
+    ap.add_argument("--e2e-iters", type=int, default=1000)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if out is not None:
+        print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

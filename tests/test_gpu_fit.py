@@ -1,0 +1,161 @@
+"""GPU suite: the gradient loop and the drop-in entry points end to end."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import mixture, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def test_session_loop_tracks_oracle(engine, oracle_cpu, golden):
+    P, ids, Y0 = golden["P"], golden["ids"], golden["Y_a"]
+    N, K = P.shape
+    with engine.Session(N, K) as s:
+        s.set_affinities(P, ids)
+        s.set_schedule(200.0, 12.0, 250, 0.5, 0.8)
+        s.set_embedding(Y0)
+        ms, done = s.run(20)
+        Y = s.get_embedding()
+        st = s.stats()
+        assert done == 20 and st["step"] == 20 and ms > 0 and s.launch_count() >= 20 * 7
+    Yc, _, _, Zc = oracle_cpu.iterate(P, ids, Y0, 20, 200.0)
+    assert rel_l2(Y, Yc) < 1e-3          # 20 exaggerated steps amplify last-bit differences of the forces
+    assert abs(st["Z"] - Zc) / abs(Zc) < 1e-4
+
+
+def test_session_matches_reference_quality(engine, oracle_cpu, golden):
+    """Same P and Y0 as the reference's own run (golden): KL within 1 %, 10-NN preservation within 0.5 points
+    (plus the spread two runs of the reference show among themselves, its spread atomics being unordered)."""
+    P, ids, Y0 = golden["P"], golden["ids"], golden["Y_a"]
+    N, K = P.shape
+    with engine.Session(N, K) as s:
+        s.set_affinities(P, ids)
+        s.set_schedule(200.0, 12.0, 250, 0.5, 0.8)
+        s.set_embedding(Y0)
+        s.run(1000)
+        Y = s.get_embedding()
+    kl = oracle_cpu.kl_divergence(P, ids, Y)
+    nnp = oracle_cpu.nn_preservation(ids, Y, 10)
+    assert abs(kl - float(golden["kl_fit"])) / float(golden["kl_fit"]) < 0.01
+    assert abs(nnp - float(golden["nnp_fit"])) < 0.005 + 0.01
+
+
+def test_chunked_run_equals_single_run_in_quality(engine, golden):
+    P, ids, Y0 = golden["P"], golden["ids"], golden["Y_a"]
+    N, K = P.shape
+    out = []
+    for chunks in ((60,), (1, 9, 50)):
+        with engine.Session(N, K) as s:
+            s.set_affinities(P, ids)
+            s.set_schedule(200.0, 12.0, 30, 0.5, 0.8)
+            s.set_embedding(Y0)
+            for c in chunks:
+                s.run(c)
+            out.append(s.get_embedding())
+    assert rel_l2(out[0], out[1]) < 1e-2     # identical schedule; only the spread's atomic order differs
+
+
+def test_min_gradient_norm_stops_early(engine, golden):
+    P, ids, Y0 = golden["P"], golden["ids"], golden["Y_a"]
+    with engine.Session(*P.shape) as s:
+        s.set_affinities(P, ids)
+        s.set_embedding(Y0)
+        ms, done = s.run(50, min_gradient_norm=1e9)
+        assert done == 1 and s.stats()["update_norm"] > 0
+
+
+def test_affinities_from_points_equals_stage_pipeline(engine, oracle_cpu):
+    X = mixture(2500, 40, 17)
+    with engine.Session(2500, 50) as s:
+        s.affinities_from_points(X, 25.0, 1e-4)
+        P, ids = s.get_affinities()
+    ids_o, d2_o = oracle_cpu.knn(X, 50)
+    assert np.array_equal(ids, ids_o)
+    p, _, _ = engine.perplexity(d2_o, 25.0, 1e-4)
+    assert np.array_equal(P, engine.symmetrize(p, ids_o))
+
+
+def test_drop_in_fit_transform(engine, oracle_cpu):
+    from tsne_cuda_b200 import TSNE
+    X = mixture(3000, 50, 33)
+    Y0 = (1e-4 * np.random.default_rng(1).standard_normal((3000, 2))).astype(np.float32)
+    Y = TSNE(perplexity=30, num_neighbors=90, learning_rate=200, n_iter=600).fit_transform(X, Y0)
+    assert Y.shape == (3000, 2) and Y.dtype == np.float32 and Y.flags["F_CONTIGUOUS"] and np.isfinite(Y).all()
+    ids, P = oracle_cpu.affinities(X, 90, 30.0, 1e-3)
+    nnp = oracle_cpu.nn_preservation(ids, np.ascontiguousarray(Y.T), 10)
+    lab = np.arange(3000) % 4
+    cent = np.stack([Y[lab == c].mean(0) for c in range(4)])
+    assert (np.linalg.norm(Y - cent[lab], axis=1) < np.linalg.norm(Y[:, None] - cent[None], axis=2).min(1) + 1e-6).mean() > 0.99
+    assert nnp > 0.1
+    # GAUSSIAN init (no y) and uniform data like the reference's smoke test
+    Y2 = TSNE(n_iter=50).fit_transform(np.random.default_rng(0).random((500, 20)))
+    assert np.isfinite(Y2).all() and Y2.std() > 0
+
+
+def test_fit_vs_live_reference(engine, oracle_cpu):
+    from oracle import ref
+    if not ref.available():
+        pytest.skip("oracle/_ref/libtsnecuda_ref.so was not built (needs the reference tree)")
+    from tsne_cuda_b200 import TSNE
+    X = mixture(4000, 50, 5)
+    K = 90
+    Y0 = (1e-4 * np.random.default_rng(2).standard_normal((2, 4000))).astype(np.float32)
+    ids, d2 = engine.knn(X, K)
+    ref.set_knn(ids, d2)
+    Yr = ref.fit_transform(X, Y0, perplexity=30.0, num_neighbors=K, perplexity_search_epsilon=1e-3, iterations=1000)
+    ref.clear_knn()
+    Ym = TSNE(perplexity=30, num_neighbors=K, n_iter=1000).fit_transform(X, np.asfortranarray(Y0.T))
+    Ym = np.ascontiguousarray(Ym.T)
+    ids_o, P = oracle_cpu.affinities(X, K, 30.0, 1e-3)
+    kl_r, kl_m = oracle_cpu.kl_divergence(P, ids_o, Yr), oracle_cpu.kl_divergence(P, ids_o, Ym)
+    n_r, n_m = oracle_cpu.nn_preservation(ids_o, Yr, 10), oracle_cpu.nn_preservation(ids_o, Ym, 10)
+    assert abs(kl_m - kl_r) / kl_r < 0.01, (kl_m, kl_r)
+    assert abs(n_m - n_r) < 0.005 + 0.01, (n_m, n_r)
+
+
+def test_snapshots_dump_and_errors(engine, tmp_path, capfd):
+    from tsne_cuda_b200 import TSNE
+    X = mixture(400, 10, 2)
+    snaps = TSNE(n_iter=40, num_neighbors=30, perplexity=10, return_style="snapshots", num_snapshots=5).fit_transform(X)
+    assert snaps.shape == (5, 400, 2) and np.isfinite(snaps).all()
+    assert not np.array_equal(snaps[0], snaps[-1])
+    dump = str(tmp_path / "dump.txt")
+    TSNE(n_iter=6, num_neighbors=30, perplexity=10, dump_points=True, dump_file=dump, dump_interval=2).fit_transform(X)
+    lines = open(dump).read().split("\n")
+    assert lines[0].split() == ["400", "2"] and len([l for l in lines if l]) == 1 + 3 * 400
+    # errors: message and return, never exit()
+    Y, Z = engine.fit(X, iterations=5, num_neighbors=2000, perplexity=10.0)      # K is clamped to N like the reference
+    assert np.isfinite(Y).all()
+    with pytest.raises(engine.TsneError):
+        engine.fit(X, iterations=5, initialization_type=3)                         # VECTOR without preinit data
+    with pytest.raises(engine.TsneError):
+        engine.fit(X, iterations=5, gpu_device=99)
+    Y, Z = engine.fit(X, iterations=30, num_neighbors=30, perplexity=10.0, verbosity=1, print_interval=10)
+    out = capfd.readouterr().out
+    assert "_time_knn:" in out and "[Step 20] Avg. Gradient Norm:" in out and "total_time:" in out and Z > 0
+
+
+def test_full_size_properties_one_million_points(engine, oracle_cpu):
+    """Size-independent properties at the benchmark's N = 10^6: exact neighbours on sampled queries, charge
+    conservation through the spread, and the grid identity for the normalisation."""
+    from tsne_cuda_b200 import datasets
+    N = 1000000
+    rng = np.random.default_rng(0)
+    Y = rng.normal(0, 12.0, (2, N)).astype(np.float32)
+    F, Z, w, yt = engine.repulsive(Y, True)
+    tot = w.reshape(-1, 4).astype(np.float64).sum(0)
+    expect = np.array([N, Y[0].astype(np.float64).sum(), Y[1].astype(np.float64).sum(),
+                       (Y[0].astype(np.float64) ** 2 + Y[1].astype(np.float64) ** 2).sum()])
+    assert np.allclose(tot, expect, rtol=2e-4, atol=2.0)
+    w64, yt64 = w.astype(np.float64), yt.astype(np.float64)
+    zs = ((w64[..., 0] + w64[..., 3]) * yt64[..., 0] - 2 * w64[..., 1] * yt64[..., 1] - 2 * w64[..., 2] * yt64[..., 2]
+          + w64[..., 0] * yt64[..., 3]).sum()
+    assert abs((zs - N) - Z) / abs(Z) < 1e-4
+    assert np.isfinite(F).all() and abs(F.astype(np.float64).sum()) < 1e-3 * np.abs(F).sum()   # momentum conservation
+    X = datasets.gaussian_mixture(200000, 50, seed=9)
+    ids, d2 = engine.knn(X, 90, q_lo=1000, q_hi=1064)
+    ids_o, d2_o = oracle_cpu.knn(X, 90, q_lo=1000, q_hi=1064)
+    assert np.array_equal(ids, ids_o) and np.array_equal(d2, d2_o)
+    assert (np.diff(d2, axis=1) >= 0).all() and np.array_equal(ids[:, 0], np.arange(1000, 1064))

@@ -201,6 +201,14 @@ int b200tsne_repulsive(const float *Y, int64_t N, float *Frep, float *Z, float *
     B200_CUDA(cudaMemcpyAsync(&hs, st, sizeof(IterState), cudaMemcpyDeviceToHost, sg.st));
     B200_CUDA(cudaStreamSynchronize(sg.st));
     *Z = (float)hs.zsum[0] - (float)N;
+    // the device keeps each node as (x, y, count, r^2); callers get the reference's (count, x, y, r^2)
+    for (float *g : {w_out, ytilde_out}) {
+        if (!g) continue;
+        for (size_t k = 0; k < (size_t)kG * kG; k++) {
+            const float a = g[4 * k], b = g[4 * k + 1], c = g[4 * k + 2];
+            g[4 * k] = c; g[4 * k + 1] = a; g[4 * k + 2] = b;
+        }
+    }
     return 0;
 }
 

@@ -9,8 +9,12 @@
 // Design (nothing here is a translation of the reference's kernels):
 //  * One kernel per point pass.  Box index, in-box coordinate, Lagrange weights and charges are
 //    recomputed in registers by spread and gather; the reference's nine N-sized intermediate
-//    arrays do not exist.  The grid is AoS float4 per node = two packed complex numbers
-//    (t0 + i t1, t2 + i t3), so a point issues 9 vector reductions instead of 36 scalar atomics.
+//    arrays do not exist.  The grid is AoS float4 per node, stored as (x-charge, y-charge, count,
+//    r^2-charge) = two packed complex numbers, so a point issues 9 vector reductions instead of 36
+//    scalar atomics.  The pairing is deliberate: a complex FFT leaks rounding error of the larger
+//    component into the smaller one, so the x and y charges (same magnitude) share one plane and the
+//    r^2 charge is multiplied by a power of two that brings it to the magnitude of the counts before
+//    it shares the other (scaling by a power of two is exact and is undone on the way out).
 //  * The convolution is a hand-written zero-padded 1024x1024 FFT (any length >= 779 gives the same
 //    linear convolution as the reference's 780) in three kernels: forward row pass, fused column
 //    pass (forward FFT, product with the kernel spectrum, inverse FFT, never leaving the SM), inverse
@@ -49,6 +53,7 @@ namespace {
 // ------------------------------------------------------------------------------------------
 struct GridGeom {
     float cmin, box_width;
+    float r2_scale, r2_unscale;   // powers of two: r2_scale * max possible (x^2+y^2) lies in [4, 8)
 };
 
 __device__ __forceinline__ GridGeom load_geom(const IterState *state, int slot)
@@ -61,6 +66,12 @@ __device__ __forceinline__ GridGeom load_geom(const IterState *state, int slot)
     // All points identical: the reference divides by zero here.  Use a tiny positive width so that
     // every point falls in box 0 with in-box coordinate 0 and all results stay finite.
     if (!(g.box_width > 0.0f)) g.box_width = 1e-30f;
+    const float r = fmaxf(fabsf(cmin), fabsf(cmax));
+    const float r2max = 2.0f * r * r;
+    int e = 0;
+    if (r2max > 0.0f && r2max < INFINITY) e = min(100, max(-100, 2 - ilogbf(r2max)));
+    g.r2_scale = scalbnf(1.0f, e);
+    g.r2_unscale = scalbnf(1.0f, -e);
     return g;
 }
 
@@ -140,7 +151,7 @@ spread_kernel(const float2 *__restrict__ Y2, long long row_lo, long long n_rows,
         for (int b = 0; b < kInterp; b++) {
             const float l = Lx[a] * Ly[b];
             float4 *dst = w + (size_t)(bx * kInterp + a) * kG + (by * kInterp + b);
-            atomicAdd(dst, make_float4(l, l * y.x, l * y.y, l * c3));
+            atomicAdd(dst, make_float4(l * y.x, l * y.y, l, l * c3));  // (x, y, count, r^2) charges
         }
     }
 }
@@ -168,7 +179,7 @@ gather_kernel(const float2 *__restrict__ Y2, long long row_lo, long long n_rows,
             for (int b = 0; b < kInterp; b++) {
                 const float l = Lx[a] * Ly[b];
                 const float4 v = __ldg(ytilde + (size_t)(bx * kInterp + a) * kG + (by * kInterp + b));
-                p1 += l * v.x; p2 += l * v.y; p3 += l * v.z; p4 += l * v.w;
+                p1 += l * v.z; p2 += l * v.x; p3 += l * v.y; p4 += l * v.w;  // node = (x, y, count, r^2) potentials
             }
         }
         zi = (1 + y.x * y.x + y.y * y.y) * p1 - 2 * (y.x * p2 + y.y * p3) + p4;
@@ -317,13 +328,16 @@ fft_rows_forward_kernel(float4 *__restrict__ w, float2 *__restrict__ A, float *_
     const int row = blockIdx.x * kRowsPerBlockA + wi / 3, plane = wi % 3;
     if (row >= kG) return;
     float2 v[32];
+    const GridGeom g = load_geom(state, slot);
     if (plane < 2) {
         float2 *wrow = reinterpret_cast<float2 *>(w + (size_t)row * kG) + plane;  // .xy or .zw of each node
+        const float imag_scale = (plane == 1) ? g.r2_scale : 1.0f;
 #pragma unroll
         for (int r = 0; r < 32; r++) {
             const int j = 32 * r + lane;
             if (j < kG) {
                 v[r] = wrow[2 * j];
+                v[r].y *= imag_scale;
                 if (zero_w) wrow[2 * j] = make_float2(0.0f, 0.0f);
             } else {
                 v[r] = make_float2(0.0f, 0.0f);
@@ -333,7 +347,6 @@ fft_rows_forward_kernel(float4 *__restrict__ w, float2 *__restrict__ A, float *_
         // Kernel values at node offsets (row, j), from float node coordinates exactly as the
         // reference forms them, summed and inverted in double (nbodyfft.cu:175-195); the weights
         // c_row * c_j (1 on the axes, 2 elsewhere) fold the three mirrored quadrants in.
-        const GridGeom g = load_geom(state, slot);
         const float h = g.box_width / (float)kInterp;
         const float x_min = g.cmin, y_min = g.cmin;
         const float x1 = y_min + h / 2;
@@ -424,7 +437,8 @@ fft_columns_kernel(const float2 *__restrict__ A, const float *__restrict__ Rk, f
 // ---- pass C: inverse transform along the y-node index of the G needed rows ----
 constexpr int kRowsPerBlockC = 2;
 __global__ void __launch_bounds__(kRowsPerBlockC * 2 * 32)
-fft_rows_inverse_kernel(const float2 *__restrict__ B, float4 *__restrict__ ytilde, const float2 *__restrict__ tw)
+fft_rows_inverse_kernel(const float2 *__restrict__ B, float4 *__restrict__ ytilde, const IterState *state, int slot,
+                        const float2 *__restrict__ tw)
 {
     extern __shared__ float2 smem[];
     float2 *tws = smem;
@@ -440,11 +454,12 @@ fft_rows_inverse_kernel(const float2 *__restrict__ B, float4 *__restrict__ ytild
     for (int r = 0; r < 32; r++) v[r] = __ldg(in + 32 * r + lane);
     fft1024_warp<true>(v, exch, tws, lane);
     const float scale = 1.0f / ((float)kM * (float)kM);
+    const float imag_scale = (plane == 1) ? scale * load_geom(state, slot).r2_unscale : scale;
     float2 *out = reinterpret_cast<float2 *>(ytilde + (size_t)row * kG) + plane;
 #pragma unroll
     for (int r = 0; r < 32; r++) {
         const int j = lane + 32 * r;
-        if (j < kG) out[2 * j] = make_float2(v[r].x * scale, v[r].y * scale);
+        if (j < kG) out[2 * j] = make_float2(v[r].x * scale, v[r].y * imag_scale);
     }
 }
 
@@ -525,7 +540,7 @@ int launch_convolve(float4 *w, float4 *ytilde, const IterState *state, int slot,
     B200_CUDA(cudaGetLastError());
     fft_columns_kernel<<<kM / kColsPerBlockB, kColsPerBlockB * 3 * 32, kSmemB, st>>>(ws.A, ws.Rk, ws.B, ws.tw);
     B200_CUDA(cudaGetLastError());
-    fft_rows_inverse_kernel<<<kG / kRowsPerBlockC, kRowsPerBlockC * 2 * 32, kSmemC, st>>>(ws.B, ytilde, ws.tw);
+    fft_rows_inverse_kernel<<<kG / kRowsPerBlockC, kRowsPerBlockC * 2 * 32, kSmemC, st>>>(ws.B, ytilde, state, slot, ws.tw);
     B200_CUDA(cudaGetLastError());
     return 0;
 }
