@@ -140,7 +140,7 @@ def run_ours(args):
     s.run(n_prof)
     stages = s.stage_times()
     s.enable_stage_timers(False)
-    stage_us = {k: (v[0] / max(v[1], 1) * 1e3 * (3 if k == "convolve" else 1)) for k, v in stages.items() if v[1] > 0}
+    stage_us = {k: v[0] / n_prof * 1e3 for k, v in stages.items() if v[1] > 0}
     attr_s = stages["attractive"][0] / max(stages["attractive"][1], 1) * 1e-3
     rows = hi - lo
     attr_bytes = 8.0 * rows * K + 16.0 * rows

@@ -170,7 +170,7 @@ int b200tsne_session_run(b200tsne_session *s, int n_iters, float min_gradient_no
 int b200tsne_session_stats(b200tsne_session *s, float *Z, float *update_norm, int *step);
 /* Per-stage device time accumulated since creation, in ms, into out[B200TSNE_N_STAGES]
  * (only collected after b200tsne_session_enable_stage_timers(s, 1), which serialises stages). */
-#define B200TSNE_N_STAGES 8
+#define B200TSNE_N_STAGES 9
 int b200tsne_session_enable_stage_timers(b200tsne_session *s, int enable);
 int b200tsne_session_stage_times(b200tsne_session *s, float *out_ms, int64_t *out_launches);
 const char *b200tsne_stage_name(int stage);

@@ -10,7 +10,7 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libtsnecuda.so")
-N_STAGES = 8
+N_STAGES = 9
 G = 390
 
 if not os.path.exists(LIB_PATH):

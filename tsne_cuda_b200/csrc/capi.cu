@@ -50,7 +50,7 @@ int b200tsne_version(void) { return (0 << 16) | (1 << 8) | 0; }
 
 const char *b200tsne_stage_name(int stage)
 {
-    static const char *names[kStages] = {"spread", "convolve", "gather", "attractive", "update", "exchange", "knn", "affinities"};
+    static const char *names[kStages] = {"spread", "convolve", "gather", "attractive", "update", "exchange", "knn", "affinities", "order"};
     return (stage >= 0 && stage < kStages) ? names[stage] : "";
 }
 
@@ -190,7 +190,7 @@ int b200tsne_repulsive(const float *Y, int64_t N, float *Frep, float *Z, float *
     B200_TRY(launch_state_reset(st, sg.st));
     B200_TRY(launch_minmax_init(dY2, N, st, 0, sg.st));
     const InterpConsts ic = make_interp_consts();
-    B200_TRY(launch_spread(dY2, 0, N, st, 0, ic, dw, sg.st));
+    B200_TRY(launch_spread(dY2, 0, N, nullptr, st, 0, ic, dw, sg.st));
     if (w_out) B200_TRY(down(w_out, reinterpret_cast<float *>(dw), (size_t)kG * kG * 4, sg.st));
     B200_TRY(launch_convolve(dw, dyt, st, 0, ws, false, sg.st));
     B200_TRY(launch_gather(dY2, 0, N, st, 0, ic, dyt, dF2, sg.st));

@@ -13,7 +13,7 @@ constexpr int kInterp = 3;             // Lagrange nodes per box and dimension
 constexpr int kG = kBoxes * kInterp;   // 390 nodes per dimension
 constexpr int kTerms = 4;              // charges (1, x, y, x^2+y^2)
 constexpr int kM = 1024;               // transform length of the zero-padded convolution (>= 2*kG-1)
-constexpr int kStages = 8;             // instrumented stages (== B200TSNE_N_STAGES)
+constexpr int kStages = 9;             // instrumented stages (== B200TSNE_N_STAGES)
 
 // ---- error plumbing ----
 void set_error(const std::string &msg);
@@ -102,8 +102,12 @@ size_t fft_workspace_bytes();
 int fft_workspace_init(FftWorkspace *ws, void *mem, cudaStream_t st);
 int launch_state_reset(IterState *state, cudaStream_t st);   // both slots, sums and flags
 int launch_minmax_init(const float2 *Y2, int64_t N, IterState *state, int slot, cudaStream_t st);
-int launch_spread(const float2 *Y2, int64_t row_lo, int64_t row_hi, const IterState *state, int slot, InterpConsts ic,
-                  float4 *w, cudaStream_t st);
+// order: local row indices sorted by box (null = natural order); see launch_order_refresh
+int launch_spread(const float2 *Y2, int64_t row_lo, int64_t row_hi, const int32_t *order, const IterState *state,
+                  int slot, InterpConsts ic, float4 *w, cudaStream_t st);
+int launch_order_identity(int32_t *order, int64_t n, cudaStream_t st);
+int launch_order_refresh(const float2 *Y2, int64_t row_lo, int64_t row_hi, const int32_t *order_in, int32_t *order_out,
+                         int32_t *keys, int32_t *hist, const IterState *state, int slot, cudaStream_t st);
 int launch_convolve(float4 *w, float4 *ytilde, const IterState *state, int slot, const FftWorkspace &ws, bool zero_w,
                     cudaStream_t st);
 int launch_gather(const float2 *Y2, int64_t row_lo, int64_t row_hi, IterState *state, int slot, InterpConsts ic,

@@ -132,28 +132,164 @@ __global__ void __launch_bounds__(256) minmax_kernel(const float2 *__restrict__ 
 // ------------------------------------------------------------------------------------------
 // spread
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
-spread_kernel(const float2 *__restrict__ Y2, long long row_lo, long long n_rows, const IterState *state, int slot,
-              InterpConsts ic, float4 *__restrict__ w)
+// Same-address floating-point reductions serialise in L2, and an embedding is anything but uniform
+// over its bounding square (during early exaggeration half the points sit in a few hundred boxes).
+// So the spread walks the points in an order that is sorted by box (refreshed every few iterations
+// by a counting sort; a stale order only costs efficiency, never correctness, because the box of
+// every point is recomputed here): lanes that fall into the same box are neighbours in the warp,
+// their 36 contributions are combined with a segmented shuffle reduction, and only the first lane of
+// each run issues the nine vector reductions.
+__device__ __forceinline__ int axis_box(float c, const GridGeom &g)
 {
-    const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (r >= n_rows) return;
+    int idx = (int)((c - g.cmin) / g.box_width);
+    idx = max(0, idx);
+    return min(kBoxes - 1, idx);
+}
+
+__global__ void __launch_bounds__(256)
+spread_kernel(const float2 *__restrict__ Y2, long long row_lo, long long n_rows, const int32_t *__restrict__ order,
+              const IterState *state, int slot, InterpConsts ic, float4 *__restrict__ w)
+{
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const bool valid = t < n_rows;
     const GridGeom g = load_geom(state, slot);
-    const float2 y = Y2[row_lo + r];
-    int bx, by;
-    float Lx[kInterp], Ly[kInterp];
-    axis_weights(y.x, g, ic, bx, Lx);
-    axis_weights(y.y, g, ic, by, Ly);
-    const float c3 = y.x * y.x + y.y * y.y;
+    int key = -1, bx = 0, by = 0;
+    float v[kInterp][kInterp][4];
+    if (valid) {
+        const long long r = order ? (long long)order[t] : t;
+        const float2 y = Y2[row_lo + r];
+        float Lx[kInterp], Ly[kInterp];
+        axis_weights(y.x, g, ic, bx, Lx);
+        axis_weights(y.y, g, ic, by, Ly);
+        key = by * kBoxes + bx;
+        const float c3 = y.x * y.x + y.y * y.y;
 #pragma unroll
-    for (int a = 0; a < kInterp; a++) {
+        for (int a = 0; a < kInterp; a++)
 #pragma unroll
-        for (int b = 0; b < kInterp; b++) {
-            const float l = Lx[a] * Ly[b];
-            float4 *dst = w + (size_t)(bx * kInterp + a) * kG + (by * kInterp + b);
-            atomicAdd(dst, make_float4(l * y.x, l * y.y, l, l * c3));  // (x, y, count, r^2) charges
+            for (int b = 0; b < kInterp; b++) {
+                const float l = Lx[a] * Ly[b];
+                v[a][b][0] = l * y.x; v[a][b][1] = l * y.y; v[a][b][2] = l; v[a][b][3] = l * c3;  // (x, y, count, r^2)
+            }
+    } else {
+#pragma unroll
+        for (int a = 0; a < kInterp; a++)
+#pragma unroll
+            for (int b = 0; b < kInterp; b++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) v[a][b][c] = 0.0f;
+    }
+    // runs of equal keys among neighbouring lanes
+    const int prev = __shfl_up_sync(0xffffffffu, key, 1);
+    const bool head = (lane == 0) || (key != prev);
+    const unsigned heads = __ballot_sync(0xffffffffu, head);
+    const unsigned above = (lane == 31) ? 0u : (heads & (0xffffffffu << (lane + 1)));
+    const int run_end = above ? (__ffs(above) - 2) : 31;   // last lane of this lane's run
+    if (heads != 0xffffffffu) {                             // at least one run longer than one lane
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const bool take = lane + d <= run_end;
+#pragma unroll
+            for (int a = 0; a < kInterp; a++)
+#pragma unroll
+                for (int b = 0; b < kInterp; b++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const float o = __shfl_down_sync(0xffffffffu, v[a][b][c], d);
+                        if (take) v[a][b][c] += o;
+                    }
         }
     }
+    if (head && key >= 0) {
+#pragma unroll
+        for (int a = 0; a < kInterp; a++)
+#pragma unroll
+            for (int b = 0; b < kInterp; b++) {
+                float4 *dst = w + (size_t)(bx * kInterp + a) * kG + (by * kInterp + b);
+                atomicAdd(dst, make_float4(v[a][b][0], v[a][b][1], v[a][b][2], v[a][b][3]));
+            }
+    }
+}
+
+// ---- counting sort of the owned points by box (order[t] = local row index) ----
+__global__ void order_identity_kernel(int32_t *order, long long n)
+{
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n) order[t] = (int32_t)t;
+}
+
+// keys[t] = box of point order[t]; hist[box] += 1 (one atomic per group of equal keys in a warp)
+__global__ void __launch_bounds__(256)
+order_histogram_kernel(const float2 *__restrict__ Y2, long long row_lo, long long n_rows, const int32_t *__restrict__ order,
+                       const IterState *state, int slot, int32_t *__restrict__ keys, int32_t *__restrict__ hist)
+{
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    int key = -1;
+    if (t < n_rows) {
+        const GridGeom g = load_geom(state, slot);
+        const float2 y = Y2[row_lo + order[t]];
+        key = axis_box(y.y, g) * kBoxes + axis_box(y.x, g);
+        keys[t] = key;
+    }
+    const unsigned same = __match_any_sync(0xffffffffu, key);
+    if (key >= 0 && lane == __ffs(same) - 1) atomicAdd(hist + key, __popc(same));
+}
+
+// exclusive scan of the kBoxes^2 counters in place (one block: serial within a thread, shuffles within
+// a warp, one pass over the 32 warp totals)
+__global__ void __launch_bounds__(1024) order_scan_kernel(int32_t *hist)
+{
+    constexpr int kBins = kBoxes * kBoxes;
+    constexpr int kPer = (kBins + 1023) / 1024;
+    __shared__ int warp_tot[32];
+    const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
+    const int base = threadIdx.x * kPer;
+    int local[kPer], sum = 0;
+#pragma unroll
+    for (int k = 0; k < kPer; k++) {
+        local[k] = (base + k < kBins) ? hist[base + k] : 0;
+        sum += local[k];
+    }
+    int incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += o;
+    }
+    if (lane == 31) warp_tot[wi] = incl;
+    __syncthreads();
+    if (wi == 0) {
+        int t = warp_tot[lane];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, t, d);
+            if (lane >= d) t += o;
+        }
+        warp_tot[lane] = t;   // inclusive totals of the warps
+    }
+    __syncthreads();
+    int run = incl - sum + (wi > 0 ? warp_tot[wi - 1] : 0);
+#pragma unroll
+    for (int k = 0; k < kPer; k++) {
+        if (base + k < kBins) hist[base + k] = run;
+        run += local[k];
+    }
+}
+
+__global__ void __launch_bounds__(256)
+order_scatter_kernel(const int32_t *__restrict__ order_in, const int32_t *__restrict__ keys, long long n_rows,
+                     int32_t *__restrict__ cursor, int32_t *__restrict__ order_out)
+{
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int key = (t < n_rows) ? keys[t] : -1;
+    const unsigned same = __match_any_sync(0xffffffffu, key);
+    const int leader = __ffs(same) - 1;
+    int basepos = 0;
+    if (key >= 0 && lane == leader) basepos = atomicAdd(cursor + key, __popc(same));
+    basepos = __shfl_sync(0xffffffffu, basepos, leader);
+    if (key >= 0) order_out[basepos + __popc(same & ((1u << lane) - 1u))] = order_in[t];
 }
 
 // ------------------------------------------------------------------------------------------
@@ -521,12 +657,37 @@ int launch_state_reset(IterState *state, cudaStream_t st)
     return 0;
 }
 
-int launch_spread(const float2 *Y2, int64_t row_lo, int64_t row_hi, const IterState *state, int slot, InterpConsts ic,
-                  float4 *w, cudaStream_t st)
+int launch_spread(const float2 *Y2, int64_t row_lo, int64_t row_hi, const int32_t *order, const IterState *state,
+                  int slot, InterpConsts ic, float4 *w, cudaStream_t st)
 {
     const long long n = row_hi - row_lo;
     if (n <= 0) return 0;
-    spread_kernel<<<nblk(n, 256), 256, 0, st>>>(Y2, row_lo, n, state, slot, ic, w);
+    spread_kernel<<<nblk(n, 256), 256, 0, st>>>(Y2, row_lo, n, order, state, slot, ic, w);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_order_identity(int32_t *order, int64_t n, cudaStream_t st)
+{
+    if (n <= 0) return 0;
+    order_identity_kernel<<<nblk(n, 256), 256, 0, st>>>(order, n);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// order_in -> order_out sorted by the box of the points' current position; keys: n ints of scratch,
+// hist: kBoxes^2 ints of scratch.
+int launch_order_refresh(const float2 *Y2, int64_t row_lo, int64_t row_hi, const int32_t *order_in, int32_t *order_out,
+                         int32_t *keys, int32_t *hist, const IterState *state, int slot, cudaStream_t st)
+{
+    const long long n = row_hi - row_lo;
+    if (n <= 0) return 0;
+    B200_CUDA(cudaMemsetAsync(hist, 0, sizeof(int32_t) * kBoxes * kBoxes, st));
+    order_histogram_kernel<<<nblk(n, 256), 256, 0, st>>>(Y2, row_lo, n, order_in, state, slot, keys, hist);
+    B200_CUDA(cudaGetLastError());
+    order_scan_kernel<<<1, 1024, 0, st>>>(hist);
+    B200_CUDA(cudaGetLastError());
+    order_scatter_kernel<<<nblk(n, 256), 256, 0, st>>>(order_in, keys, n, hist, order_out);
     B200_CUDA(cudaGetLastError());
     return 0;
 }

@@ -10,6 +10,7 @@
 #include "session.h"
 
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -64,6 +65,12 @@ int Session::init(int64_t N_, int K_, int64_t lo, int64_t hi, int device_)
     const int64_t r = std::max<int64_t>(rows(), 1);
     B200_TRY(arena.alloc((void **)&P, sizeof(float) * r * K));
     B200_TRY(arena.alloc((void **)&ids, sizeof(int32_t) * r * K));
+    B200_TRY(arena.alloc((void **)&order, sizeof(int32_t) * r));
+    B200_TRY(arena.alloc((void **)&order_alt, sizeof(int32_t) * r));
+    B200_TRY(arena.alloc((void **)&order_keys, sizeof(int32_t) * r));
+    B200_TRY(arena.alloc((void **)&box_hist, sizeof(int32_t) * kBoxes * kBoxes));
+    B200_TRY(launch_order_identity(order, rows(), stream));
+    if (const char *e = getenv("B200TSNE_ORDER_REFRESH")) order_refresh = atoi(e);
     B200_TRY(arena.alloc((void **)&Y2, sizeof(float2) * npad));
     B200_TRY(arena.alloc((void **)&Fattr, sizeof(float2) * npad));
     B200_TRY(arena.alloc((void **)&Frep, sizeof(float2) * npad));
@@ -151,9 +158,9 @@ struct StageClock {
     void begin(cudaStream_t st) { if (a) cudaEventRecord(a, st); }
     void end(cudaStream_t st, int stage, int n_launches)
     {
-        s->stage_launches[stage] += n_launches;
         s->launches += n_launches;
         if (!a) return;
+        s->stage_launches[stage] += n_launches;
         cudaEventRecord(b, st);
         cudaEventSynchronize(b);
         float ms = 0.0f;
@@ -178,12 +185,20 @@ int Session::one_iteration(bool want_norm)
         B200_CUDA(cudaStreamWaitEvent(stream2, ev_fork, 0));
         B200_TRY(launch_attractive(P, ids, Y2, N, K, row_lo, row_hi, Fattr, sa));
         B200_CUDA(cudaEventRecord(ev_join, stream2));
-        stage_launches[kStAttractive] += 1;
         launches += 1;
     }
 
+    // The embedding reshuffles quickly while it is being exaggerated and slowly afterwards: sort every
+    // iteration early, every order_refresh iterations later.
+    const bool settling = step < force_magnify_iters + 50;
+    if (order_refresh > 0 && (settling || step % order_refresh == 0)) {
+        clk.begin(stream);
+        B200_TRY(launch_order_refresh(Y2, row_lo, row_hi, order, order_alt, order_keys, box_hist, state, slot, stream));
+        std::swap(order, order_alt);
+        clk.end(stream, kStOrder, 3);
+    }
     clk.begin(stream);
-    B200_TRY(launch_spread(Y2, row_lo, row_hi, state, slot, ic, w, stream));
+    B200_TRY(launch_spread(Y2, row_lo, row_hi, order_refresh > 0 ? order : nullptr, state, slot, ic, w, stream));
     clk.end(stream, kStSpread, 1);
     if (multi) {
         clk.begin(stream);

@@ -10,7 +10,7 @@ namespace b200 {
 
 struct Comm;  // comm.h
 
-enum Stage { kStSpread = 0, kStConvolve, kStGather, kStAttractive, kStUpdate, kStExchange, kStKnn, kStAffinities };
+enum Stage { kStSpread = 0, kStConvolve, kStGather, kStAttractive, kStUpdate, kStExchange, kStKnn, kStAffinities, kStOrder };
 
 // RAII holder for device allocations of a session
 struct DeviceArena {
@@ -40,6 +40,8 @@ struct Session {
     float2 *gains = nullptr;  // [rows]
     float2 *u = nullptr;      // [rows]
     float *soa_tmp = nullptr; // [2N] staging for SoA <-> AoS conversion
+    int32_t *order = nullptr, *order_alt = nullptr, *order_keys = nullptr, *box_hist = nullptr;  // spread order (owned rows)
+    int order_refresh = 8;    // iterations between two counting sorts of the spread order once the embedding has settled (0 = natural order)
     // grid
     float4 *w = nullptr;      // [G][G]
     float4 *ytilde = nullptr; // [G][G]
