@@ -103,6 +103,11 @@ int b200tsne_fit(const float *points, int64_t num_points, int num_dims, const b2
 int b200tsne_knn(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_hi, int64_t db_lo,
                  int64_t db_hi, int32_t *ids, float *d2, int device);
 
+/* How the last b200tsne_knn call of this thread ran: whether the tensor-core path was used, how many rows
+ * its proof could not certify (recomputed by the SIMT search) and the largest observed filter error as a
+ * fraction of the assumed bound.  No counterpart in the reference. */
+int b200tsne_knn_last_stats(int *tensor_core, int *rows_recomputed, float *filter_error_ratio);
+
 /* Global max-normalisation of the squared distances followed by the per-row perplexity search;
  * p receives the row-normalised conditional probabilities, betas (may be NULL) the found betas,
  * max_out (may be NULL) the normalising maximum.  If max_override > 0 it is used instead of the

@@ -45,6 +45,7 @@ SIGNATURES = {
     "b200tsne_default_options": (None, [C.POINTER(Options)]),
     "b200tsne_fit": (C.c_int, [_fp, _i64, C.c_int, C.POINTER(Options), _fp, _fp]),
     "b200tsne_knn": (C.c_int, [_fp, _i64, C.c_int, C.c_int, _i64, _i64, _i64, _i64, _ip, _fp, C.c_int]),
+    "b200tsne_knn_last_stats": (C.c_int, [C.POINTER(C.c_int), C.POINTER(C.c_int), _fp]),
     "b200tsne_perplexity": (C.c_int, [_fp, _i64, C.c_int, C.c_float, C.c_float, C.c_float, _fp, _fp, _fp, C.c_int]),
     "b200tsne_symmetrize": (C.c_int, [_fp, _ip, _i64, C.c_int, _fp, C.c_int]),
     "b200tsne_attractive": (C.c_int, [_fp, _ip, _fp, _i64, C.c_int, _i64, _i64, _fp, C.c_int]),
@@ -105,6 +106,12 @@ def knn(X, K, q_lo=0, q_hi=None, db_lo=0, db_hi=None, device=0):
     d2 = np.empty((q_hi - q_lo, K), np.float32)
     check(lib.b200tsne_knn(_f(X), N, D, K, q_lo, q_hi, db_lo, db_hi, _i(ids), _f(d2), device))
     return ids, d2
+
+
+def knn_last_stats():
+    tc, rows, ratio = C.c_int(), C.c_int(), C.c_float()
+    lib.b200tsne_knn_last_stats(C.byref(tc), C.byref(rows), C.byref(ratio))
+    return {"tensor_core": tc.value, "rows_recomputed": rows.value, "filter_error_ratio": ratio.value}
 
 
 def perplexity(d2, perp, eps, max_override=0.0, device=0):

@@ -16,6 +16,8 @@ struct b200tsne_session {
     Session s;
 };
 
+static thread_local KnnStats g_last_knn_stats;
+
 namespace {
 int check_device(int device)
 {
@@ -66,15 +68,13 @@ int b200tsne_knn(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t 
     StreamGuard sg;
     B200_TRY(sg.create());
     DeviceArena a;
-    float *dX = nullptr, *dXT = nullptr, *dd = nullptr;
+    float *dX = nullptr, *dd = nullptr;
     int32_t *di = nullptr;
     const size_t nq = (size_t)(q_hi - q_lo);
     B200_TRY(up(a, &dX, X, (size_t)N * D, sg.st));
-    B200_TRY(a.alloc((void **)&dXT, sizeof(float) * (size_t)N * D));
     B200_TRY(a.alloc((void **)&di, sizeof(int32_t) * std::max<size_t>(nq * K, 1)));
     B200_TRY(a.alloc((void **)&dd, sizeof(float) * std::max<size_t>(nq * K, 1)));
-    B200_TRY(launch_transpose(dX, N, D, dXT, sg.st));
-    B200_TRY(launch_knn_exact(dXT, N, D, K, q_lo, q_hi, db_lo, db_hi, di, dd, sg.st));
+    B200_TRY(knn_search(dX, N, D, K, q_lo, q_hi, db_lo, db_hi, di, dd, &g_last_knn_stats, sg.st));
     B200_TRY(launch_knn_finalize(di, dd, (int64_t)nq * K, sg.st));
     B200_TRY(down(ids, di, nq * K, sg.st));
     B200_TRY(down(d2, dd, nq * K, sg.st));
@@ -229,6 +229,14 @@ int b200tsne_apply_forces(float *Y, float *attr, float *rep, float *gains, float
     B200_TRY(launch_apply_forces_soa(d[0], d[1], d[2], d[3], d[4], eta, normalization, momentum, exaggeration, N, sg.st));
     for (int k = 0; k < 5; k++) B200_TRY(down(h[k], d[k], (size_t)2 * N, sg.st));
     B200_CUDA(cudaStreamSynchronize(sg.st));
+    return 0;
+}
+
+int b200tsne_knn_last_stats(int *tensor_core, int *rows_recomputed, float *filter_error_ratio)
+{
+    if (tensor_core) *tensor_core = g_last_knn_stats.tensor_core;
+    if (rows_recomputed) *rows_recomputed = g_last_knn_stats.rows_recomputed;
+    if (filter_error_ratio) *filter_error_ratio = g_last_knn_stats.filter_error_ratio;
     return 0;
 }
 

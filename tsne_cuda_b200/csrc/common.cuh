@@ -76,6 +76,22 @@ __host__ __device__ inline float dec_float(unsigned int e)
 int launch_transpose(const float *X, int64_t N, int D, float *XT, cudaStream_t st);   // [N][D] -> [D][N]
 int launch_knn_exact(const float *XT, int64_t N, int D, int K, int64_t q_lo, int64_t q_hi, int64_t db_lo,
                      int64_t db_hi, int32_t *ids, float *d2, cudaStream_t st);   // ids/d2 keep (INT_MAX,+inf) in unfilled slots
+int launch_knn_exact_rows(const float *XT, int64_t N, int D, int K, const int *q_index, int64_t nq, int64_t out_base,
+                          int64_t db_lo, int64_t db_hi, int32_t *ids, float *d2, cudaStream_t st);
+// knn_tc.cu: tensor-core filter + exact re-rank + proof (D <= 64)
+bool knn_tc_supported(int64_t N, int D, int K);
+size_t knn_tc_workspace_bytes(int64_t N, int D, int K, int64_t nq);
+int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_hi, int64_t db_lo, int64_t db_hi,
+                  int32_t *ids, float *d2, void *workspace, int **failed_list, int *n_failed_host, float *err_ratio_host,
+                  cudaStream_t st);
+struct KnnStats {
+    int tensor_core = 0;            // 1 when the tensor-core path ran
+    int rows_recomputed = 0;        // rows the proof could not certify, recomputed by the SIMT search
+    float filter_error_ratio = 0;   // largest observed filter error on the candidates / assumed bound
+};
+// X: [N][D] row-major on the device; picks the path, handles the fallback rows, synchronises `st`.
+int knn_search(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_hi, int64_t db_lo, int64_t db_hi,
+               int32_t *ids, float *d2, KnnStats *stats, cudaStream_t st);
 int launch_knn_merge(const int32_t *ids_parts, const float *d2_parts, int parts, int64_t part_stride, int64_t n_rows,
                      int K, int32_t *ids, float *d2, cudaStream_t st);
 int launch_knn_finalize(int32_t *ids, float *d2, int64_t n, cudaStream_t st);

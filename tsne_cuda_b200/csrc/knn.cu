@@ -15,8 +15,11 @@
 // k-th best; the rare survivors are inserted into the sorted result rows by the whole warp.
 // No N x N matrix is ever written.
 #include <limits.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
+#include "session.h"
 
 namespace b200 {
 namespace {
@@ -82,11 +85,13 @@ __device__ __forceinline__ void warp_insert(volatile float *ld, volatile int32_t
     __syncwarp();
 }
 
-// XT: dimension-major copy of X ([D][N]).  Queries [q_lo,q_hi), database [db_lo,db_hi).
-// ids/d2: [(q_hi-q_lo)][K], pre-set to (INT_MAX, +inf).
+// XT: dimension-major copy of X ([D][N]).  The nq queries are rows q_lo, q_lo+1, ... or, when q_index is
+// given, the rows it lists; database rows [db_lo,db_hi).  The list of query row g is written to row
+// (g - out_base) of ids/d2 ([.][K], pre-set to (INT_MAX, +inf)).
 __global__ void __launch_bounds__(kThreads, 2)
-knn_exact_kernel(const float *__restrict__ XT, long long N, int D, int K, long long q_lo, long long q_hi, long long db_lo,
-                 long long db_hi, int32_t *ids, float *d2)
+knn_exact_kernel(const float *__restrict__ XT, long long N, int D, int K, long long q_lo, long long nq,
+                 const int *__restrict__ q_index, long long out_base, long long db_lo, long long db_hi, int32_t *ids,
+                 float *d2)
 {
     extern __shared__ __align__(16) float sm[];
     float *Qs = sm;                          // [DCH][BQ]
@@ -97,8 +102,15 @@ knn_exact_kernel(const float *__restrict__ XT, long long N, int D, int K, long l
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tx = tid & 15, ty = tid >> 4;
-    const long long q0 = q_lo + (long long)blockIdx.x * BQ;
-    if (tid < BQ) { thr_d[tid] = INFINITY; thr_i[tid] = INT_MAX; }
+    const long long q0 = (long long)blockIdx.x * BQ;   // position in the query list
+    int *q_row = thr_i + BQ;                            // [BQ] global row of each query, -1 beyond the list
+    if (tid < BQ) {
+        thr_d[tid] = INFINITY;
+        thr_i[tid] = INT_MAX;
+        const long long pos = q0 + tid;
+        q_row[tid] = (pos < nq) ? (q_index ? q_index[pos] : (int)(q_lo + pos)) : -1;
+    }
+    __syncthreads();
 
     for (long long p0 = db_lo; p0 < db_hi; p0 += BP) {
         float acc[4][8];
@@ -112,8 +124,8 @@ knn_exact_kernel(const float *__restrict__ XT, long long N, int D, int K, long l
             __syncthreads();  // previous chunk / previous tile's selection done with the buffers
             for (int idx = tid; idx < dlen * BQ; idx += kThreads) {
                 const int dd = idx / BQ, q = idx % BQ;
-                const long long gq = q0 + q;
-                Qs[dd * BQ + q] = (gq < q_hi) ? XT[(long long)(d0 + dd) * N + gq] : 0.0f;
+                const int gq = q_row[q];
+                Qs[dd * BQ + q] = (gq >= 0) ? XT[(long long)(d0 + dd) * N + gq] : 0.0f;
             }
             for (int idx = tid; idx < dlen * BP; idx += kThreads) {
                 const int dd = idx / BP, pp = idx % BP;
@@ -147,8 +159,8 @@ knn_exact_kernel(const float *__restrict__ XT, long long N, int D, int K, long l
         __syncthreads();
         // selection: warp `warp` owns queries warp, warp+8, ...
         for (int q = warp; q < BQ; q += kThreads / 32) {
-            const long long gq = q0 + q;
-            if (gq >= q_hi) break;
+            const long long gq = q_row[q];
+            if (gq < 0) break;
             const float4 dv = *reinterpret_cast<const float4 *>(Dist + q * DSTR + lane * 4);
             const float dl[4] = {dv.x, dv.y, dv.z, dv.w};
             float td = thr_d[q];
@@ -164,8 +176,8 @@ knn_exact_kernel(const float *__restrict__ XT, long long N, int D, int K, long l
                     const float cd = __shfl_sync(0xffffffffu, dl[c], src);
                     const int ci = (int)(p0 + src * 4 + c);
                     if (cd < td || (cd == td && ci < ti)) {   // the threshold may have moved since the ballot
-                        volatile float *ld = d2 + (gq - q_lo) * K;
-                        volatile int32_t *li = ids + (gq - q_lo) * K;
+                        volatile float *ld = d2 + (gq - out_base) * K;
+                        volatile int32_t *li = ids + (gq - out_base) * K;
                         warp_insert(ld, li, K, cd, ci, lane);
                         td = ld[K - 1];
                         ti = li[K - 1];
@@ -203,7 +215,16 @@ __global__ void knn_merge_kernel(const int32_t *__restrict__ ids_parts, const fl
     }
 }
 
-constexpr size_t kKnnSmem = sizeof(float) * (DCH * BQ + DCH * BP + BQ * DSTR + BQ) + sizeof(int) * BQ;
+constexpr size_t kKnnSmem = sizeof(float) * (DCH * BQ + DCH * BP + BQ * DSTR + BQ) + sizeof(int) * 2 * BQ;
+
+__global__ void knn_init_rows_kernel(int32_t *ids, float *d2, const int *__restrict__ q_index, long long nq, long long out_base, int K)
+{
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= nq * K) return;
+    const long long row = q_index[t / K] - out_base;
+    ids[row * K + t % K] = INT_MAX;
+    d2[row * K + t % K] = INFINITY;
+}
 }  // namespace
 
 int launch_knn_finalize(int32_t *ids, float *d2, int64_t n, cudaStream_t st)
@@ -244,8 +265,67 @@ int launch_knn_exact(const float *XT, int64_t N, int D, int K, int64_t q_lo, int
     knn_init_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ids, d2, n);
     B200_CUDA(cudaGetLastError());
     B200_CUDA(cudaFuncSetAttribute(knn_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKnnSmem));
-    knn_exact_kernel<<<(unsigned)((nq + BQ - 1) / BQ), kThreads, kKnnSmem, st>>>(XT, N, D, K, q_lo, q_hi, db_lo, db_hi, ids, d2);
+    knn_exact_kernel<<<(unsigned)((nq + BQ - 1) / BQ), kThreads, kKnnSmem, st>>>(XT, N, D, K, q_lo, nq, nullptr, q_lo, db_lo, db_hi,
+                                                                                 ids, d2);
     B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// Same search for an explicit list of query rows (device array q_index of nq global row ids); the list
+// of row g replaces row (g - out_base) of ids/d2.
+int launch_knn_exact_rows(const float *XT, int64_t N, int D, int K, const int *q_index, int64_t nq, int64_t out_base,
+                          int64_t db_lo, int64_t db_hi, int32_t *ids, float *d2, cudaStream_t st)
+{
+    if (nq <= 0) return 0;
+    const long long n = nq * K;
+    knn_init_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ids, d2, q_index, nq, out_base, K);
+    B200_CUDA(cudaGetLastError());
+    B200_CUDA(cudaFuncSetAttribute(knn_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKnnSmem));
+    knn_exact_kernel<<<(unsigned)((nq + BQ - 1) / BQ), kThreads, kKnnSmem, st>>>(XT, N, D, K, 0, nq, q_index, out_base, db_lo, db_hi,
+                                                                                 ids, d2);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+
+// Exact search of queries [q_lo,q_hi) against database rows [db_lo,db_hi) of X ([N][D], device),
+// choosing the tensor-core path where it applies and falling back to the SIMT search for the rows it
+// cannot certify.  Unfilled slots keep (INT_MAX, +inf); see launch_knn_finalize.
+int knn_search(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_hi, int64_t db_lo, int64_t db_hi,
+               int32_t *ids, float *d2, KnnStats *stats, cudaStream_t st)
+{
+    KnnStats local;
+    if (!stats) stats = &local;
+    *stats = KnnStats();
+    const int64_t nq = q_hi - q_lo;
+    if (nq <= 0) return 0;
+    const char *force = getenv("B200TSNE_KNN");
+    const bool want_tc = knn_tc_supported(N, D, K) && !(force && strcmp(force, "simt") == 0);
+    DeviceArena tmp;
+    float *XT = nullptr;
+    auto ensure_xt = [&]() -> int {
+        if (XT) return 0;
+        B200_TRY(tmp.alloc((void **)&XT, sizeof(float) * (size_t)N * D));
+        return launch_transpose(X, N, D, XT, st);
+    };
+    if (!want_tc) {
+        B200_TRY(ensure_xt());
+        B200_TRY(launch_knn_exact(XT, N, D, K, q_lo, q_hi, db_lo, db_hi, ids, d2, st));
+        B200_CUDA(cudaStreamSynchronize(st));   // XT is released on return
+        return 0;
+    }
+    void *ws = nullptr;
+    B200_TRY(tmp.alloc(&ws, knn_tc_workspace_bytes(N, D, K, nq)));
+    int *failed_list = nullptr;
+    int n_failed = 0;
+    B200_TRY(launch_knn_tc(X, N, D, K, q_lo, q_hi, db_lo, db_hi, ids, d2, ws, &failed_list, &n_failed, &stats->filter_error_ratio, st));
+    stats->tensor_core = 1;
+    stats->rows_recomputed = n_failed;
+    if (n_failed > 0) {
+        B200_TRY(ensure_xt());
+        B200_TRY(launch_knn_exact_rows(XT, N, D, K, failed_list, n_failed, q_lo, db_lo, db_hi, ids, d2, st));
+    }
+    B200_CUDA(cudaStreamSynchronize(st));
     return 0;
 }
 

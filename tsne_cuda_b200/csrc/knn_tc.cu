@@ -1,0 +1,746 @@
+// Exact k-nearest-neighbour search on the tensor cores (tcgen05 + TMEM), for D <= 64.
+//
+// Replaces the reference's FAISS IVF-Flat call (src/util/distance_utils.cu:79-121, approximate).
+// The result is the same as the SIMT search of knn.cu: ids ordered by the canonical fp32 distance
+// (sequential, unfused) with ties broken by index.  It is obtained in three steps:
+//
+//  1. Filter.  Ranking keys  key_ij = |x_j|^2 - 2 x_i.x_j  come straight out of the tensor cores: the
+//     query operand is [x_i, 1], the database operand [-2 x_j, |x_j|^2] (one of the padding columns of
+//     the 8-aligned inner dimension carries the norm), multiplied as a 3xTF32 product (v = hi + lo with
+//     hi, lo representable in TF32;  hi.hi + lo.hi + hi.lo, accumulated in fp32 in TMEM), accurate to
+//     about 2^-20 of |x_i||x_j|.  A block owns 128 queries (one TMEM lane each) and
+//     walks the database in tiles of 128 points; each epilogue thread compares its row of the
+//     accumulator tile with a threshold (the L-th best key its query had at the last compaction,
+//     L = K + slack) and appends the rare survivors to the query's candidate buffer with plain
+//     stores; when a buffer is nearly full its warp sorts it (bitonic network in registers) and keeps
+//     the L best, which tightens the threshold.  No N x N matrix is written.
+//  2. Re-rank.  The canonical distance of the L candidates is evaluated exactly and they are ordered by
+//     (distance, id).
+//  3. Proof.  Every point that is not a candidate has a key >= T (the largest key in the list), hence a
+//     canonical distance >= (|x_i|^2 + T - E)(1 - theta) with E bounding the filter's error and theta the
+//     rounding of the canonical sum.  If the K-th candidate distance is strictly below that bound the
+//     first K candidates are provably the exact answer; otherwise the row is flagged and recomputed by
+//     the SIMT search.  The observed filter error on the candidates is checked against E as well.
+//
+// Operand staging: the prepared operands live in global memory as ready-made shared-memory images,
+// one per 128-row tile: for hi then lo, for every 8-wide K step, the 128 x 8 block in the
+// no-swizzle K-major core-matrix order (8 rows x 16 bytes contiguous; the two 16-byte halves of a K
+// step 128 bytes apart; 8-row groups 256 bytes apart).  A tile is therefore ONE contiguous bulk
+// copy (cp.async.bulk + mbarrier complete_tx) with no tensor map and no swizzle.
+//
+// Two passes for large databases.  With the threshold maintained online, a query appends about
+// L ln(N/L) candidates, and although that is rare per thread it is not rare per warp of 32 queries.  So
+// pass 1 runs the online scheme on every 32nd database tile only, pass 2 scans everything against a FIXED
+// per-query threshold tau = the key of rank ~3L/32 in the sample: about 3L points beat it, no buffer is
+// compacted during the scan, and the L best are selected once at the end.  A row with fewer than L or
+// more than the buffer's capacity of candidates is flagged and recomputed by the SIMT search.
+//
+// Epilogue: a thread first reduces its 32 keys of a chunk to their minimum (a tree of independent
+// min operations); only if that minimum beats the threshold, which becomes rare as the scan
+// proceeds, does it locate and append the survivors.
+//
+// Warp roles (192 threads): warps 0-3 epilogue (TMEM lane quarter = warp id), warp 4 bulk-copy
+// producer, warp 5 MMA issuer and TMEM owner.  Two B stages and two accumulator buffers, so the MMAs
+// of tile t+1 overlap the epilogue of tile t.  Every wait has a time limit; on expiry the kernel sets
+// an error flag, drains and frees its TMEM.
+#include <limits.h>
+#include <string.h>
+
+#include "common.cuh"
+
+#include <algorithm>
+
+namespace b200 {
+namespace {
+
+constexpr int TM = 128;             // queries per block = accumulator rows = TMEM lanes
+constexpr int TN = 128;             // database points per tile = accumulator columns
+constexpr int kBStages = 2;
+constexpr int kAccBufs = 2;
+constexpr int kTcThreads = 192;
+constexpr uint32_t kTmemCols = 256;  // kAccBufs * TN
+
+// ------------------------------------------------------------------------------------------------
+// PTX helpers
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: gives up after 4 s or as soon as another thread of the block has given up.  A waiting
+// thread sleeps between polls: the producer and the MMA issuer share their schedulers with epilogue
+// warps, and a busy poll would take every other issue slot from them.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned sleep_ns = 128)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    int spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(sleep_ns);
+        if ((++spins & 63) == 0) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > 4000000000ull) { *abort_flag = 1; return false; }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, 128 x 128 x 8, TF32 operands, fp32 accumulation
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// 32 consecutive accumulator columns of this thread's TMEM lane: asynchronous issue ...
+__device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+        " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+// ... and the wait that makes the registers valid (they are listed so that no use is scheduled above it)
+__device__ __forceinline__ void tc_ld32_wait(uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                   "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                   "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                   "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes, the two
+// 16-byte halves of a K step 128 bytes apart (leading offset), 8-row groups 256 bytes apart (stride
+// offset); offsets are encoded in 16-byte units; bits 46-47 carry the descriptor version (1).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3fff);
+    d |= (uint64_t)(128 >> 4) << 16;
+    d |= (uint64_t)(256 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+// Instruction descriptor: fp32 accumulate (bits 4-5 = 1), TF32 A and B (bits 7-9, 10-12 = 2), both
+// K-major (bits 15, 16 = 0), N/8 in bits 17-22, M/16 in bits 24-28.
+constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+
+// ------------------------------------------------------------------------------------------------
+// operand preparation
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float to_tf32(float x)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+// offset (in floats) of element (row r, dimension k) inside a tile image part (hi or lo)
+__device__ __forceinline__ size_t image_offset(int r, int k)
+{
+    return (size_t)(k >> 3) * 1024 + (size_t)(r >> 3) * 64 + (size_t)((k >> 2) & 1) * 32 + (size_t)(r & 7) * 4 + (k & 3);
+}
+
+// X [N][D] -> query images and database images, each [tiles][2 (hi, lo)][Dp/8][1024 floats], and the
+// exact squared norms (double).  Query rows are [x, 1, 0...], database rows [-2x, |x|^2, 0...]; rows
+// beyond N get zeros (queries) and a huge finite norm (database), so they never rank.
+__global__ void __launch_bounds__(128)
+knn_tc_prepare_kernel(const float *__restrict__ X, long long N, int D, int Dp, float *__restrict__ img_q,
+                      float *__restrict__ img_db, double *__restrict__ norms_exact)
+{
+    const long long tile = blockIdx.x;
+    const int r = threadIdx.x;
+    const long long i = tile * TM + r;
+    float *iq = img_q + (size_t)tile * 2 * Dp * 128;
+    float *id = img_db + (size_t)tile * 2 * Dp * 128;
+    const size_t part = (size_t)Dp * 128;
+    double n2 = 0.0;
+    for (int k = 0; k < D; k++) {
+        const float x = (i < N) ? X[i * D + k] : 0.0f;
+        n2 += (double)x * (double)x;
+    }
+    for (int k = 0; k < Dp; k++) {
+        float q = 0.0f, d = 0.0f;
+        if (k < D) {
+            q = (i < N) ? X[i * D + k] : 0.0f;
+            d = -2.0f * q;
+        } else if (k == D) {
+            q = (i < N) ? 1.0f : 0.0f;
+            d = (i < N) ? (float)n2 : 3.0e38f;
+        }
+        const float qh = to_tf32(q), dh = to_tf32(d);
+        iq[image_offset(r, k)] = qh;
+        iq[part + image_offset(r, k)] = to_tf32(q - qh);
+        id[image_offset(r, k)] = dh;
+        id[part + image_offset(r, k)] = to_tf32(d - dh);
+    }
+    norms_exact[i] = n2;
+}
+
+// ------------------------------------------------------------------------------------------------
+// candidate buffers: compaction by a warp-wide bitonic sort, EPL elements per lane (32*EPL = capacity)
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool pair_less(float ka, int ia, float kb, int ib) { return ka < kb || (ka == kb && ia < ib); }
+
+template <int EPL>
+__device__ __forceinline__ void warp_bitonic_sort(float (&k)[EPL], int (&id)[EPL], int lane)
+{
+    // element index = lane * EPL + r: the low log2(EPL) bits select the register, the rest the lane
+#pragma unroll
+    for (int size = 2; size <= 32 * EPL; size <<= 1) {
+#pragma unroll
+        for (int j = size >> 1; j > 0; j >>= 1) {
+            if (j >= EPL) {
+                const int lj = j / EPL;
+#pragma unroll
+                for (int r = 0; r < EPL; r++) {
+                    const int idx = lane * EPL + r;
+                    const float ok = __shfl_xor_sync(0xffffffffu, k[r], lj);
+                    const int oi = __shfl_xor_sync(0xffffffffu, id[r], lj);
+                    const bool up = (idx & size) == 0;          // ascending block
+                    const bool lower = (idx & j) == 0;          // this element is the lower index of its pair
+                    const bool other_less = pair_less(ok, oi, k[r], id[r]);
+                    const bool take = (lower == up) ? other_less : !other_less && !(ok == k[r] && oi == id[r]);
+                    if (take) { k[r] = ok; id[r] = oi; }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < EPL; r++) {
+                    if ((r & j) == 0) {
+                        const int idx = lane * EPL + r;
+                        const bool up = (idx & size) == 0;
+                        const bool swap = up ? pair_less(k[r + j], id[r + j], k[r], id[r]) : pair_less(k[r], id[r], k[r + j], id[r + j]);
+                        if (swap) {
+                            const float tk = k[r]; k[r] = k[r + j]; k[r + j] = tk;
+                            const int ti = id[r]; id[r] = id[r + j]; id[r + j] = ti;
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Sort the first n entries of one query's buffer (capacity 32*EPL) and keep the L best (L = 16*EPL).
+// Whole warp; returns the new threshold (key of the L-th best, +inf while fewer than L entries exist).
+template <int EPL>
+__device__ __forceinline__ float warp_compact(float *bk, int32_t *bi, int n, int lane)
+{
+    constexpr int L = 16 * EPL;
+    float k[EPL];
+    int id[EPL];
+#pragma unroll
+    for (int r = 0; r < EPL; r++) {
+        const int idx = lane * EPL + r;
+        k[r] = (idx < n) ? __ldcg(bk + idx) : INFINITY;
+        id[r] = (idx < n) ? __ldcg(bi + idx) : INT_MAX;
+    }
+    warp_bitonic_sort<EPL>(k, id, lane);
+#pragma unroll
+    for (int r = 0; r < EPL; r++) {
+        const int idx = lane * EPL + r;
+        if (idx < L) { __stcg(bk + idx, k[r]); __stcg(bi + idx, id[r]); }
+    }
+    return __shfl_sync(0xffffffffu, k[EPL - 1], 15);   // element L-1 sits in lane 15, last register
+}
+
+// ------------------------------------------------------------------------------------------------
+// filter kernel
+// ------------------------------------------------------------------------------------------------
+struct TcShared {
+    uint64_t full_a;
+    uint64_t full_b[kBStages];
+    uint64_t empty_b[kBStages];
+    uint64_t acc_full[kAccBufs];
+    uint64_t acc_empty[kAccBufs];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+// img_q / img_db: tile images of all points (query form, database form); query tiles [qt_lo, qt_hi), database tiles [dt_lo, dt_hi); only
+// candidates with db_lo <= id < db_hi are kept, only queries in [q_lo, q_hi) are served.
+// cand_key / cand_id: [(q_hi - q_lo)][32*EPL] candidate buffers; on return the first L = 16*EPL entries of
+// each are the L best keys in ascending order ((+inf, INT_MAX) where the database had fewer points).
+// FIXED = false: threshold maintained online, buffers of 32*EPL entries, database tiles dt_lo, dt_lo +
+// tile_stride, ...   FIXED = true: threshold tau[query] fixed, buffers of `cap` entries (row stride of
+// cand_key / cand_id in both modes), row_flags[query] set when a buffer overflows or ends with fewer than L.
+template <int EPL, bool FIXED>
+__global__ void __launch_bounds__(kTcThreads, 1)
+knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int Dp, long long qt_lo,
+                     long long dt_lo, long long dt_hi, int tile_stride, long long q_lo, long long q_hi, long long db_lo,
+                     long long db_hi, const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id,
+                     int *__restrict__ row_flags, int *error_flag)
+{
+    constexpr int C = 32 * EPL;   // capacity handled by one compaction
+    constexpr int L = 16 * EPL;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ __align__(8) TcShared sh;
+    const uint32_t image_bytes = (uint32_t)Dp * 1024u;        // hi + lo
+    float *sA = reinterpret_cast<float *>(smem);
+    float *sB = reinterpret_cast<float *>(smem + image_bytes);  // [kBStages] images
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nks = Dp >> 3;
+    const long long qt = qt_lo + blockIdx.x;
+    const long long n_tiles = (dt_hi - dt_lo + tile_stride - 1) / tile_stride;
+    volatile int *abort_flag = &sh.abort_flag;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sh.full_a, 1);
+        for (int s = 0; s < kBStages; s++) { mbar_init(&sh.full_b[s], 1); mbar_init(&sh.empty_b[s], 1); }
+        for (int b = 0; b < kAccBufs; b++) { mbar_init(&sh.acc_full[b], 1); mbar_init(&sh.acc_empty[b], 4); }
+        sh.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh.tmem_base;
+
+    if (warp == 4) {
+        // ---------------- producer: one bulk copy per tile image ----------------
+        if (lane == 0) {
+            mbar_expect_tx(&sh.full_a, image_bytes);
+            bulk_load(sA, img_q + (size_t)qt * (image_bytes / 4), image_bytes, &sh.full_a);
+            for (long long t = 0; t < n_tiles; t++) {
+                const int s = (int)(t % kBStages);
+                const uint32_t ph = (uint32_t)((t / kBStages) & 1);
+                if (!mbar_wait(&sh.empty_b[s], ph ^ 1u, abort_flag)) break;
+                mbar_expect_tx(&sh.full_b[s], image_bytes);
+                bulk_load(sB + (size_t)s * (image_bytes / 4), img_db + (size_t)(dt_lo + t * tile_stride) * (image_bytes / 4), image_bytes,
+                          &sh.full_b[s]);
+            }
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            bool ok = mbar_wait(&sh.full_a, 0, abort_flag);
+            const uint32_t a_hi = smem_u32(sA), a_lo = a_hi + (uint32_t)nks * 4096u;
+            for (long long t = 0; ok && t < n_tiles; t++) {
+                const int s = (int)(t % kBStages), b = (int)(t % kAccBufs);
+                const uint32_t ph_s = (uint32_t)((t / kBStages) & 1), ph_b = (uint32_t)((t / kAccBufs) & 1);
+                if (!mbar_wait(&sh.acc_empty[b], ph_b ^ 1u, abort_flag)) break;
+                if (!mbar_wait(&sh.full_b[s], ph_s, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t b_hi = smem_u32(sB + (size_t)s * (image_bytes / 4)), b_lo = b_hi + (uint32_t)nks * 4096u;
+                const uint32_t d_tmem = tmem_base + (uint32_t)b * TN;
+                uint32_t acc = 0;
+                for (int ks = 0; ks < nks; ks++) {      // hi . hi
+                    tc_mma_tf32(d_tmem, make_desc(a_hi + ks * 4096u), make_desc(b_hi + ks * 4096u), kInstrDesc, acc);
+                    acc = 1;
+                }
+                for (int ks = 0; ks < nks; ks++)        // lo . hi
+                    tc_mma_tf32(d_tmem, make_desc(a_lo + ks * 4096u), make_desc(b_hi + ks * 4096u), kInstrDesc, 1);
+                for (int ks = 0; ks < nks; ks++)        // hi . lo
+                    tc_mma_tf32(d_tmem, make_desc(a_hi + ks * 4096u), make_desc(b_lo + ks * 4096u), kInstrDesc, 1);
+                tc_commit(&sh.empty_b[s]);    // the stage may be refilled once these MMAs have read it
+                tc_commit(&sh.acc_full[b]);   // the accumulator tile is complete
+            }
+        }
+    } else {
+        // ---------------- epilogue: one query per thread ----------------
+        const int row = warp * 32 + lane;                       // TMEM lane
+        const long long gq = qt * TM + row;
+        const bool serve = gq >= q_lo && gq < q_hi;
+        float *bk = cand_key + (serve ? (gq - q_lo) : 0) * cap;
+        int32_t *bi = cand_id + (serve ? (gq - q_lo) : 0) * cap;
+        float thr = serve ? (FIXED ? tau[gq - q_lo] : INFINITY) : -INFINITY;
+        int cnt = 0;
+        bool overflow = false;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+
+        // One chunk = 32 accumulator columns = 32 keys of this thread's query.  Fast path: a tree of
+        // independent min operations and one comparison.  Only if the minimum beats the threshold (rare
+        // once the scan is under way) are the quarters whose minimum does so compared element by element;
+        // everything is indexed statically, so the keys never leave the registers.
+        auto process_chunk = [&](const uint32_t (&r)[32], long long col0, bool tile_inside) {
+            float m16[16], m8[8], m4[4];
+#pragma unroll
+            for (int k = 0; k < 16; k++) m16[k] = fminf(__uint_as_float(r[2 * k]), __uint_as_float(r[2 * k + 1]));
+#pragma unroll
+            for (int k = 0; k < 8; k++) m8[k] = fminf(m16[2 * k], m16[2 * k + 1]);
+#pragma unroll
+            for (int k = 0; k < 4; k++) m4[k] = fminf(m8[2 * k], m8[2 * k + 1]);
+            const float mn = fminf(fminf(m4[0], m4[1]), fminf(m4[2], m4[3]));
+            if (mn < thr) {
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    if (m4[q] < thr) {
+#pragma unroll
+                        for (int e = 0; e < 8; e++) {
+                            const int c = q * 8 + e;
+                            const float key = __uint_as_float(r[c]);
+                            const long long cid = col0 + c;
+                            const bool pass = key < thr && (tile_inside || (cid >= db_lo && cid < db_hi));
+                            if (pass) {
+                                __stcg(bk + cnt, key);
+                                __stcg(bi + cnt, (int32_t)cid);
+                                cnt++;
+                            }
+                        }
+                    }
+                }
+            }
+            if (FIXED) {
+                // a chunk appends at most 32 entries: stop a buffer that could overflow in the next one
+                if (cnt > cap - 32) { overflow = true; thr = -INFINITY; }
+            } else {
+                // a chunk appends at most 32 entries: compact every buffer that could overflow in the next one
+                unsigned full = __ballot_sync(0xffffffffu, cnt > C - 32);
+                while (full) {
+                    const int owner = __ffs(full) - 1;
+                    full &= full - 1;
+                    const long long oq = qt * TM + warp * 32 + owner - q_lo;
+                    const int n = __shfl_sync(0xffffffffu, cnt, owner);
+                    const float nt = warp_compact<EPL>(cand_key + oq * cap, cand_id + oq * cap, n, lane);
+                    if (lane == owner) { thr = nt; cnt = L; }
+                }
+            }
+        };
+
+        for (long long t = 0; t < n_tiles; t++) {
+            const int b = (int)(t % kAccBufs);
+            const uint32_t ph_b = (uint32_t)((t / kAccBufs) & 1);
+            if (!mbar_wait(&sh.acc_full[b], ph_b, abort_flag, 32)) break;
+            tc_fence_after();
+            const long long p0 = (dt_lo + t * tile_stride) * TN;
+            const bool inside = p0 >= db_lo && p0 + TN <= db_hi;
+            const uint32_t tcol = lane_base + (uint32_t)(b * TN);
+            // the TMEM read of chunk c+1 is in flight while chunk c is compared
+            uint32_t ra[32], rb[32];
+            tc_ld32_issue(tcol + 0, ra);
+            tc_ld32_wait(ra);
+            tc_ld32_issue(tcol + 32, rb);
+            process_chunk(ra, p0 + 0, inside);
+            tc_ld32_wait(rb);
+            tc_ld32_issue(tcol + 64, ra);
+            process_chunk(rb, p0 + 32, inside);
+            tc_ld32_wait(ra);
+            tc_ld32_issue(tcol + 96, rb);
+            process_chunk(ra, p0 + 64, inside);
+            tc_ld32_wait(rb);
+            // all four reads have landed: hand the accumulator buffer back before the last comparison
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.acc_empty[b]);
+            process_chunk(rb, p0 + 96, inside);
+        }
+        // final selection: leave the L best, sorted, in front of every served buffer
+        unsigned m = __ballot_sync(0xffffffffu, serve);
+        while (m) {
+            const int owner = __ffs(m) - 1;
+            m &= m - 1;
+            const long long oq = qt * TM + warp * 32 + owner - q_lo;
+            const int n = __shfl_sync(0xffffffffu, cnt, owner);
+            float *ok = cand_key + oq * cap;
+            int32_t *oi = cand_id + oq * cap;
+            int first = min(n, C);
+            (void)warp_compact<EPL>(ok, oi, first, lane);
+            for (int pos = first; pos < n; pos += C - L) {     // FIXED mode only: fold the rest in, C - L at a time
+                const int chunk = min(C - L, n - pos);
+                for (int e = lane; e < chunk; e += 32) {
+                    __stcg(ok + L + e, __ldcg(ok + pos + e));
+                    __stcg(oi + L + e, __ldcg(oi + pos + e));
+                }
+                __syncwarp();
+                (void)warp_compact<EPL>(ok, oi, L + chunk, lane);
+            }
+            if (FIXED && lane == owner) row_flags[oq] = (overflow || n < L) ? 1 : 0;
+        }
+    }
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (threadIdx.x == 0 && sh.abort_flag) atomicExch(error_flag, 1);
+    if (warp == 5) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// exact re-rank + proof
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float canon_dist(const float *__restrict__ a, const float *__restrict__ b, int D)
+{
+    float acc = 0.0f;
+    for (int d = 0; d < D; d++) {
+        const float t = __fsub_rn(a[d], b[d]);
+        acc = __fadd_rn(acc, __fmul_rn(t, t));
+    }
+    return acc;
+}
+
+constexpr int kRerankWarps = 4;
+constexpr int kMaxL = 256;
+
+// One warp per query.  ids/d2 [nq][K] receive the K best candidates by (canonical distance, id);
+// failed[q] = 1 when the proof does not close for the row.
+__global__ void __launch_bounds__(kRerankWarps * 32)
+knn_tc_rerank_kernel(const float *__restrict__ X, int D, long long q_lo, long long nq, const float *__restrict__ cand_key,
+                     const int32_t *__restrict__ cand_id, int L, int C, int K, const double *__restrict__ norms_exact,
+                     float err_scale, const int *__restrict__ row_flags, int32_t *__restrict__ ids, float *__restrict__ d2,
+                     int *__restrict__ failed,
+                     int *__restrict__ n_failed, float *__restrict__ max_err_ratio)
+{
+    __shared__ float s_d[kRerankWarps][kMaxL];
+    __shared__ int s_i[kRerankWarps][kMaxL];
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long q = (long long)blockIdx.x * kRerankWarps + w;
+    if (q >= nq) return;
+    const long long gq = q_lo + q;
+    const float *xq = X + gq * D;
+    const double ni = norms_exact[gq];
+    float worst = 0.0f;   // largest observed |filter distance - canonical distance| among the candidates
+    float T = -INFINITY;
+    int n_valid = 0;
+    for (int e = lane; e < L; e += 32) {
+        const int id = cand_id[q * C + e];
+        const float key = cand_key[q * C + e];
+        float dist = INFINITY;
+        if (id != INT_MAX) {
+            dist = canon_dist(xq, X + (long long)id * D, D);
+            n_valid++;
+            T = fmaxf(T, key);
+            const double approx = ni + (double)key;
+            worst = fmaxf(worst, (float)fabs(approx - (double)dist));
+        }
+        s_d[w][e] = dist;
+        s_i[w][e] = id;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        worst = fmaxf(worst, __shfl_xor_sync(0xffffffffu, worst, o));
+        T = fmaxf(T, __shfl_xor_sync(0xffffffffu, T, o));
+        n_valid += __shfl_xor_sync(0xffffffffu, n_valid, o);
+    }
+    __syncwarp();
+    // rank by counting (ties by id), scatter the first K
+    float dK = INFINITY;
+    for (int e = lane; e < L; e += 32) {
+        const float de = s_d[w][e];
+        const int ie = s_i[w][e];
+        int rank = 0;
+        for (int u = 0; u < L; u++) {
+            const float du = s_d[w][u];
+            const int iu = s_i[w][u];
+            rank += (du < de || (du == de && iu < ie)) ? 1 : 0;
+        }
+        if (rank < K) {
+            ids[q * K + rank] = (ie == INT_MAX) ? -1 : ie;
+            d2[q * K + rank] = de;
+        }
+        if (rank == K - 1) dK = de;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dK = fminf(dK, __shfl_xor_sync(0xffffffffu, dK, o));
+    if (lane == 0) {
+        bool ok = true;
+        // Error bound of the filter's key for this row: it scales with |x_i||x_j|, and a point whose key is
+        // near T lies within sqrt(|x_i|^2 + T) of x_i, so |x_i||x_j| <= |x_i|^2 + (|x_i|^2 + T)+ up to a factor 2.
+        const double E = (double)err_scale * (ni + fmax(0.0, ni + (double)T) + 1.0);
+        if (n_valid == L) {
+            // outsiders: key >= T  =>  canonical distance >= (ni + T - E) * (1 - theta)
+            const double theta = (double)(D + 4) * 5.9604644775390625e-08;   // (D+4) * 2^-24
+            const double bound = (ni + (double)T - E) * (1.0 - theta);
+            ok = (double)dK < bound;
+        }
+        const float ratio = (float)((double)worst / E);
+        if (ratio > 0.5f) ok = false;   // the filter was less accurate than the bound assumes
+        if (row_flags && row_flags[q]) ok = false;   // the fixed threshold kept too few or too many candidates
+        failed[q] = ok ? 0 : 1;
+        if (!ok) atomicAdd(n_failed, 1);
+        atomicMax(reinterpret_cast<int *>(max_err_ratio), __float_as_int(ratio));   // ratio >= 0: int order == float order
+    }
+}
+
+// tau[q] = key of rank `rank` (0-based) in the sorted sample list of query q (+inf if the list is shorter)
+__global__ void knn_tc_tau_kernel(const float *__restrict__ sample_key, const int32_t *__restrict__ sample_id, int stride,
+                                  int rank, long long nq, float *__restrict__ tau)
+{
+    const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= nq) return;
+    tau[q] = (sample_id[q * stride + rank] == INT_MAX) ? INFINITY : sample_key[q * stride + rank];
+}
+
+__global__ void knn_tc_collect_failed_kernel(const int *__restrict__ failed, long long nq, long long q_lo, int *__restrict__ list,
+                                             int *__restrict__ count)
+{
+    const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (q < nq && failed[q]) list[atomicAdd(count, 1)] = (int)(q_lo + q);
+}
+
+}  // namespace
+
+bool knn_tc_supported(int64_t N, int D, int K)
+{
+    if (D > 64 || K + 32 > kMaxL) return false;   // three images of (D + 1 padded to 8) x 1 KB must fit in shared memory
+    return N >= 2048;   // below this the SIMT search is faster than the set-up of this one
+}
+
+constexpr int kFixedCap = 1024;      // candidate buffer entries per query in the fixed-threshold pass
+constexpr int kSampleStride = 32;    // pass 1 looks at every 32nd database tile
+constexpr long long kTwoPassMinTiles = 512;   // below this many database tiles the online pass alone is used
+
+// Workspace (device) needed by launch_knn_tc; all sizes in bytes.
+size_t knn_tc_workspace_bytes(int64_t N, int D, int K, int64_t nq)
+{
+    const int Dp = (D + 1 + 7) / 8 * 8;   // one extra inner column carries the norm
+    const int64_t tiles = (N + TM - 1) / TM;
+    const int C = (K + 32 <= 128) ? 256 : 512;
+    size_t b = 0;
+    b += (size_t)tiles * Dp * 1024 * 2;             // query and database images
+    b += sizeof(double) * (size_t)tiles * TM;       // exact norms
+    b += (sizeof(float) + sizeof(int32_t)) * (size_t)nq * C;   // online / sample candidate buffers
+    if (tiles >= kTwoPassMinTiles) {
+        b += (sizeof(float) + sizeof(int32_t)) * (size_t)nq * kFixedCap;   // fixed-threshold buffers
+        b += sizeof(float) * (size_t)nq + sizeof(int) * (size_t)nq;        // tau, row flags
+    }
+    b += sizeof(int) * ((size_t)nq * 2 + 16);       // failed flags, failed list, counters
+    return b + 4096;
+}
+
+// X: [N][D] row-major (device).  ids/d2: [(q_hi-q_lo)][K].  n_failed_host receives the number of rows
+// whose proof did not close; their global row indices are in failed_list (device, first n entries) and
+// the caller recomputes them with the SIMT search.  Returns after the kernels are queued, except for
+// the small synchronous read of the counters.
+int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_hi, int64_t db_lo, int64_t db_hi,
+                  int32_t *ids, float *d2, void *workspace, int **failed_list, int *n_failed_host, float *err_ratio_host,
+                  cudaStream_t st)
+{
+    const long long nq = q_hi - q_lo;
+    *n_failed_host = 0;
+    if (nq <= 0) return 0;
+    const int Dp = (D + 1 + 7) / 8 * 8;
+    const long long tiles = (N + TM - 1) / TM;
+    const int EPL = (K + 32 <= 128) ? 8 : 16, C = 32 * EPL, L = 16 * EPL;
+    const long long qt_lo = q_lo / TM, qt_hi = (q_hi + TM - 1) / TM;
+    const long long dt_lo = db_lo / TN, dt_hi = (db_hi + TN - 1) / TN;
+    const bool two_pass = (dt_hi - dt_lo) >= kTwoPassMinTiles && tiles >= kTwoPassMinTiles;
+    char *p = static_cast<char *>(workspace);
+    float *img_q = reinterpret_cast<float *>(p); p += (size_t)tiles * Dp * 1024;
+    float *img_db = reinterpret_cast<float *>(p); p += (size_t)tiles * Dp * 1024;
+    double *norms_exact = reinterpret_cast<double *>(p); p += sizeof(double) * (size_t)tiles * TM;
+    float *cand_key = reinterpret_cast<float *>(p); p += sizeof(float) * (size_t)nq * C;
+    int32_t *cand_id = reinterpret_cast<int32_t *>(p); p += sizeof(int32_t) * (size_t)nq * C;
+    float *fix_key = nullptr, *tau = nullptr;
+    int32_t *fix_id = nullptr;
+    int *row_flags = nullptr;
+    if (tiles >= kTwoPassMinTiles) {
+        fix_key = reinterpret_cast<float *>(p); p += sizeof(float) * (size_t)nq * kFixedCap;
+        fix_id = reinterpret_cast<int32_t *>(p); p += sizeof(int32_t) * (size_t)nq * kFixedCap;
+        tau = reinterpret_cast<float *>(p); p += sizeof(float) * (size_t)nq;
+        row_flags = reinterpret_cast<int *>(p); p += sizeof(int) * (size_t)nq;
+    }
+    int *failed = reinterpret_cast<int *>(p); p += sizeof(int) * (size_t)nq;
+    int *flist = reinterpret_cast<int *>(p); p += sizeof(int) * (size_t)nq;
+    int *counters = reinterpret_cast<int *>(p);   // [0] wait time-out flag, [1] failed rows, [2] listed rows, [3] max error ratio (float bits)
+    B200_CUDA(cudaMemsetAsync(counters, 0, sizeof(int) * 16, st));
+    knn_tc_prepare_kernel<<<(unsigned)tiles, 128, 0, st>>>(X, N, D, Dp, img_q, img_db, norms_exact);
+    B200_CUDA(cudaGetLastError());
+    const size_t smem = (size_t)(1 + kBStages) * Dp * 1024;
+    const unsigned grid = (unsigned)(qt_hi - qt_lo);
+#define B200_KNN_FILTER(EPL_, FIXED_, stride_, tau_, cap_, key_, id_, flags_)                                                   \
+    do {                                                                                                                        \
+        B200_CUDA(cudaFuncSetAttribute(knn_tc_filter_kernel<EPL_, FIXED_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        knn_tc_filter_kernel<EPL_, FIXED_><<<grid, kTcThreads, smem, st>>>(img_q, img_db, Dp, qt_lo, dt_lo, dt_hi, stride_, q_lo, q_hi, \
+                                                                          db_lo, db_hi, tau_, cap_, key_, id_, flags_, counters + 0); \
+        B200_CUDA(cudaGetLastError());                                                                                          \
+    } while (0)
+    const float *final_key = cand_key;
+    const int32_t *final_id = cand_id;
+    int final_stride = C;
+    if (!two_pass) {
+        if (EPL == 8) B200_KNN_FILTER(8, false, 1, nullptr, C, cand_key, cand_id, nullptr);
+        else B200_KNN_FILTER(16, false, 1, nullptr, C, cand_key, cand_id, nullptr);
+    } else {
+        // pass 1: online threshold on every kSampleStride-th tile; pass 2: everything against the fixed tau
+        if (EPL == 8) B200_KNN_FILTER(8, false, kSampleStride, nullptr, C, cand_key, cand_id, nullptr);
+        else B200_KNN_FILTER(16, false, kSampleStride, nullptr, C, cand_key, cand_id, nullptr);
+        const int rank = std::max(4, (3 * L + kSampleStride - 1) / kSampleStride) - 1;
+        knn_tc_tau_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(cand_key, cand_id, C, rank, nq, tau);
+        B200_CUDA(cudaGetLastError());
+        if (EPL == 8) B200_KNN_FILTER(8, true, 1, tau, kFixedCap, fix_key, fix_id, row_flags);
+        else B200_KNN_FILTER(16, true, 1, tau, kFixedCap, fix_key, fix_id, row_flags);
+        final_key = fix_key;
+        final_id = fix_id;
+        final_stride = kFixedCap;
+    }
+#undef B200_KNN_FILTER
+    // Error bound of the filter relative to (|x_i|^2 + d^2 + 1): 3xTF32 drops terms of order 2^-22 |x_i||x_j|
+    // and the tensor-core accumulation is not IEEE; 2^-14 covers both with a wide margin, and the re-rank
+    // checks the observed error of every candidate against half of it.
+    const float err_scale = 6.103515625e-05f;   // 2^-14
+    knn_tc_rerank_kernel<<<(unsigned)((nq + kRerankWarps - 1) / kRerankWarps), kRerankWarps * 32, 0, st>>>(
+        X, D, q_lo, nq, final_key, final_id, L, final_stride, K, norms_exact, err_scale, two_pass ? row_flags : nullptr, ids, d2,
+        failed, counters + 1, reinterpret_cast<float *>(counters + 3));
+    B200_CUDA(cudaGetLastError());
+    knn_tc_collect_failed_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(failed, nq, q_lo, flist, counters + 2);
+    B200_CUDA(cudaGetLastError());
+    int h[4] = {0, 0, 0, 0};
+    B200_CUDA(cudaMemcpyAsync(h, counters, sizeof(h), cudaMemcpyDeviceToHost, st));
+    B200_CUDA(cudaStreamSynchronize(st));
+    if (h[0]) { set_error("tensor-core kNN: a wait inside the kernel ran out of time"); return -2; }
+    *n_failed_host = h[2];
+    *failed_list = flist;
+    if (err_ratio_host) memcpy(err_ratio_host, &h[3], sizeof(float));
+    return 0;
+}
+
+}  // namespace b200

@@ -284,7 +284,7 @@ int Session::affinities_from_points(const float *X_host, int D, float perplexity
     if (K > N) { set_error("affinities: num_neighbors exceeds num_points"); return -1; }
     const bool multi = comm && comm->world > 1;
     DeviceArena tmp;
-    float *X = nullptr, *XT = nullptr, *d2 = nullptr, *p_all = nullptr;
+    float *X = nullptr, *d2 = nullptr, *p_all = nullptr;
     int32_t *ids_all = nullptr;
     unsigned int *max_enc = nullptr;
     const int64_t r = rows();
@@ -294,13 +294,11 @@ int Session::affinities_from_points(const float *X_host, int D, float perplexity
     StageClock clk(this);
     clk.begin(stream);
     B200_TRY(tmp.alloc((void **)&X, sizeof(float) * N * D));
-    B200_TRY(tmp.alloc((void **)&XT, sizeof(float) * N * D));
     B200_CUDA(cudaMemcpyAsync(X, X_host, sizeof(float) * N * D, cudaMemcpyHostToDevice, stream));
-    B200_TRY(launch_transpose(X, N, D, XT, stream));
     B200_TRY(tmp.alloc((void **)&d2, sizeof(float) * std::max<int64_t>(chunk, 1) * K));
     B200_TRY(tmp.alloc((void **)&max_enc, sizeof(unsigned int)));
     if (!multi) {
-        B200_TRY(launch_knn_exact(XT, N, D, K, row_lo, row_hi, 0, N, ids, d2, stream));
+        B200_TRY(knn_search(X, N, D, K, row_lo, row_hi, 0, N, ids, d2, &knn_stats, stream));
     } else {
         // database sharded by rows: every rank searches all queries against its own rows, the
         // owners of the query rows receive the partial lists and merge them
@@ -312,7 +310,7 @@ int Session::affinities_from_points(const float *X_host, int D, float perplexity
         B200_TRY(tmp.alloc((void **)&recv_d, sizeof(float) * npad * K));
         B200_CUDA(cudaMemsetAsync(part_i, 0x7f, sizeof(int32_t) * npad * K, stream));
         B200_CUDA(cudaMemsetAsync(part_d, 0x7f, sizeof(float) * npad * K, stream));
-        B200_TRY(launch_knn_exact(XT, N, D, K, 0, N, row_lo, row_hi, part_i, part_d, stream));
+        B200_TRY(knn_search(X, N, D, K, 0, N, row_lo, row_hi, part_i, part_d, &knn_stats, stream));
         B200_TRY(comm->all_to_all(part_i, recv_i, sizeof(int32_t) * (size_t)chunk * K, stream));
         B200_TRY(comm->all_to_all(part_d, recv_d, sizeof(float) * (size_t)chunk * K, stream));
         B200_TRY(launch_knn_merge(recv_i, recv_d, comm->world, chunk * K, r, K, ids, d2, stream));

@@ -64,6 +64,7 @@ struct Session {
     int64_t stage_launches[kStages] = {0};
     int64_t launches = 0;
 
+    KnnStats knn_stats;    // of the last affinities_from_points
     Comm *comm = nullptr;  // null on a single GPU
 
     int64_t rows() const { return row_hi - row_lo; }
