@@ -232,40 +232,53 @@ knn_tc_prepare_kernel(const float *__restrict__ X, long long N, int D, int Dp, f
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ bool pair_less(float ka, int ia, float kb, int ib) { return ka < kb || (ka == kb && ia < ib); }
 
+// One compare-exchange step between registers r and r + J of the same lane (J < EPL).
+template <int EPL, int J>
+__device__ __forceinline__ void bitonic_in_lane(float (&k)[EPL], int (&id)[EPL], int lane, int size)
+{
+#pragma unroll
+    for (int r = 0; r < EPL; r++) {
+        if ((r & J) == 0) {
+            const bool up = ((lane * EPL + r) & size) == 0;
+            const bool swap = up ? pair_less(k[r + J], id[r + J], k[r], id[r]) : pair_less(k[r], id[r], k[r + J], id[r + J]);
+            if (swap) {
+                const float tk = k[r]; k[r] = k[r + J]; k[r + J] = tk;
+                const int ti = id[r]; id[r] = id[r + J]; id[r + J] = ti;
+            }
+        }
+    }
+}
+
+// Warp-wide bitonic sort of 32*EPL (key, id) pairs, ascending; element index = lane * EPL + r.  The two
+// outer loops are real loops (the sort runs rarely and from cold instruction cache: a fully unrolled
+// network of ~2500 instructions costs more in instruction fetch than it saves).
 template <int EPL>
 __device__ __forceinline__ void warp_bitonic_sort(float (&k)[EPL], int (&id)[EPL], int lane)
 {
-    // element index = lane * EPL + r: the low log2(EPL) bits select the register, the rest the lane
-#pragma unroll
+#pragma unroll 1
     for (int size = 2; size <= 32 * EPL; size <<= 1) {
-#pragma unroll
+#pragma unroll 1
         for (int j = size >> 1; j > 0; j >>= 1) {
             if (j >= EPL) {
                 const int lj = j / EPL;
+                const bool lower = ((lane * EPL) & j) == 0;     // same for all registers of the lane: j >= EPL
 #pragma unroll
                 for (int r = 0; r < EPL; r++) {
-                    const int idx = lane * EPL + r;
                     const float ok = __shfl_xor_sync(0xffffffffu, k[r], lj);
                     const int oi = __shfl_xor_sync(0xffffffffu, id[r], lj);
-                    const bool up = (idx & size) == 0;          // ascending block
-                    const bool lower = (idx & j) == 0;          // this element is the lower index of its pair
-                    const bool other_less = pair_less(ok, oi, k[r], id[r]);
-                    const bool take = (lower == up) ? other_less : !other_less && !(ok == k[r] && oi == id[r]);
+                    const bool up = ((lane * EPL + r) & size) == 0;      // ascending block
+                    const bool keep_min = (lower == up);
+                    const bool take = keep_min ? pair_less(ok, oi, k[r], id[r]) : pair_less(k[r], id[r], ok, oi);
                     if (take) { k[r] = ok; id[r] = oi; }
                 }
+            } else if (j == 1) {
+                bitonic_in_lane<EPL, 1>(k, id, lane, size);
+            } else if (j == 2) {
+                bitonic_in_lane<EPL, 2>(k, id, lane, size);
+            } else if (j == 4) {
+                bitonic_in_lane<EPL, 4>(k, id, lane, size);
             } else {
-#pragma unroll
-                for (int r = 0; r < EPL; r++) {
-                    if ((r & j) == 0) {
-                        const int idx = lane * EPL + r;
-                        const bool up = (idx & size) == 0;
-                        const bool swap = up ? pair_less(k[r + j], id[r + j], k[r], id[r]) : pair_less(k[r], id[r], k[r + j], id[r + j]);
-                        if (swap) {
-                            const float tk = k[r]; k[r] = k[r + j]; k[r + j] = tk;
-                            const int ti = id[r]; id[r] = id[r + j]; id[r + j] = ti;
-                        }
-                    }
-                }
+                if constexpr (EPL > 8) bitonic_in_lane<EPL, 8>(k, id, lane, size);
             }
         }
     }
@@ -274,7 +287,7 @@ __device__ __forceinline__ void warp_bitonic_sort(float (&k)[EPL], int (&id)[EPL
 // Sort the first n entries of one query's buffer (capacity 32*EPL) and keep the L best (L = 16*EPL).
 // Whole warp; returns the new threshold (key of the L-th best, +inf while fewer than L entries exist).
 template <int EPL>
-__device__ __forceinline__ float warp_compact(float *bk, int32_t *bi, int n, int lane)
+__device__ __noinline__ float warp_compact(float *bk, int32_t *bi, int n, int lane)
 {
     constexpr int L = 16 * EPL;
     float k[EPL];
@@ -462,24 +475,20 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
             const long long p0 = (dt_lo + t * tile_stride) * TN;
             const bool inside = p0 >= db_lo && p0 + TN <= db_hi;
             const uint32_t tcol = lane_base + (uint32_t)(b * TN);
-            // the TMEM read of chunk c+1 is in flight while chunk c is compared
-            uint32_t ra[32], rb[32];
-            tc_ld32_issue(tcol + 0, ra);
-            tc_ld32_wait(ra);
-            tc_ld32_issue(tcol + 32, rb);
-            process_chunk(ra, p0 + 0, inside);
-            tc_ld32_wait(rb);
-            tc_ld32_issue(tcol + 64, ra);
-            process_chunk(rb, p0 + 32, inside);
-            tc_ld32_wait(ra);
-            tc_ld32_issue(tcol + 96, rb);
-            process_chunk(ra, p0 + 64, inside);
-            tc_ld32_wait(rb);
-            // all four reads have landed: hand the accumulator buffer back before the last comparison
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh.acc_empty[b]);
-            process_chunk(rb, p0 + 96, inside);
+            // one copy of the chunk code, executed four times: the epilogue is issue- and
+            // instruction-fetch-bound, so small code beats overlapping the (fast) TMEM reads
+#pragma unroll 1
+            for (int c0 = 0; c0 < TN; c0 += 32) {
+                uint32_t r[32];
+                tc_ld32_issue(tcol + (uint32_t)c0, r);
+                tc_ld32_wait(r);
+                if (c0 == TN - 32) {   // the last read has landed: hand the accumulator buffer back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh.acc_empty[b]);
+                }
+                process_chunk(r, p0 + c0, inside);
+            }
         }
         // final selection: leave the L best, sorted, in front of every served buffer
         unsigned m = __ballot_sync(0xffffffffu, serve);
