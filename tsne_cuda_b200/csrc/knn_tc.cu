@@ -39,8 +39,8 @@
 // min operations); only if that minimum beats the threshold, which becomes rare as the scan
 // proceeds, does it locate and append the survivors.
 //
-// Warp roles (192 threads): warps 0-3 epilogue (TMEM lane quarter = warp id), warp 4 bulk-copy
-// producer, warp 5 MMA issuer and TMEM owner.  Two B stages and two accumulator buffers, so the MMAs
+// Warp roles (320 threads): warps 0-7 epilogue in two groups of four (TMEM lane quarter = warp % 4),
+// warp 8 bulk-copy producer, warp 9 MMA issuer and TMEM owner.  Two B stages and two accumulator buffers, so the MMAs
 // of tile t+1 overlap the epilogue of tile t.  Every wait has a time limit; on expiry the kernel sets
 // an error flag, drains and frees its TMEM.
 #include <limits.h>
@@ -57,7 +57,8 @@ constexpr int TM = 128;             // queries per block = accumulator rows = TM
 constexpr int TN = 128;             // database points per tile = accumulator columns
 constexpr int kBStages = 2;
 constexpr int kAccBufs = 2;
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;      // 8 epilogue warps (two groups of four), producer warp, MMA warp
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr uint32_t kTmemCols = 256;  // kAccBufs * TN
 
 // ------------------------------------------------------------------------------------------------
@@ -318,6 +319,8 @@ struct TcShared {
     uint64_t acc_empty[kAccBufs];
     uint32_t tmem_base;
     int abort_flag;
+    int cnt[2][TM];       // candidates appended per epilogue group and query
+    int overflow[2][TM];
 };
 
 // img_q / img_db: tile images of all points (query form, database form); query tiles [qt_lo, qt_hi), database tiles [dt_lo, dt_hi); only
@@ -355,7 +358,7 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)),
                      "r"(kTmemCols)
                      : "memory");
@@ -366,7 +369,7 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
     tc_fence_after();
     const uint32_t tmem_base = sh.tmem_base;
 
-    if (warp == 4) {
+    if (warp == kProducerWarp) {
         // ---------------- producer: one bulk copy per tile image ----------------
         if (lane == 0) {
             mbar_expect_tx(&sh.full_a, image_bytes);
@@ -380,7 +383,7 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
                           &sh.full_b[s]);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             bool ok = mbar_wait(&sh.full_a, 0, abort_flag);
@@ -408,15 +411,22 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
         }
     } else {
         // ---------------- epilogue: one query per thread ----------------
-        const int row = warp * 32 + lane;                       // TMEM lane
+        // Two groups of four warps; a warp reaches the TMEM lane quarter (warp % 4).  With a fixed
+        // threshold group g takes the tiles t = g, g+2, ... (always accumulator buffer g) and appends
+        // to its own half of the query's buffer, so the groups share nothing; with the online threshold
+        // (per-query state that cannot be shared) only group 0 works.
+        const int group = warp >> 2, quarter = warp & 3;
+        const int n_groups = FIXED ? 2 : 1;
+        const int my_cap = FIXED ? cap / 2 : cap;
+        const int row = quarter * 32 + lane;                    // TMEM lane
         const long long gq = qt * TM + row;
-        const bool serve = gq >= q_lo && gq < q_hi;
-        float *bk = cand_key + (serve ? (gq - q_lo) : 0) * cap;
-        int32_t *bi = cand_id + (serve ? (gq - q_lo) : 0) * cap;
+        const bool serve = gq >= q_lo && gq < q_hi && group < n_groups;
+        float *bk = cand_key + (serve ? (gq - q_lo) : 0) * cap + group * my_cap;
+        int32_t *bi = cand_id + (serve ? (gq - q_lo) : 0) * cap + group * my_cap;
         float thr = serve ? (FIXED ? tau[gq - q_lo] : INFINITY) : -INFINITY;
         int cnt = 0;
         bool overflow = false;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
 
         // One chunk = 32 accumulator columns = 32 keys of this thread's query.  Fast path: a tree of
         // independent min operations and one comparison.  Only if the minimum beats the threshold (rare
@@ -452,14 +462,14 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
             }
             if (FIXED) {
                 // a chunk appends at most 32 entries: stop a buffer that could overflow in the next one
-                if (cnt > cap - 32) { overflow = true; thr = -INFINITY; }
+                if (cnt > my_cap - 32) { overflow = true; thr = -INFINITY; }
             } else {
                 // a chunk appends at most 32 entries: compact every buffer that could overflow in the next one
                 unsigned full = __ballot_sync(0xffffffffu, cnt > C - 32);
                 while (full) {
                     const int owner = __ffs(full) - 1;
                     full &= full - 1;
-                    const long long oq = qt * TM + warp * 32 + owner - q_lo;
+                    const long long oq = qt * TM + quarter * 32 + owner - q_lo;
                     const int n = __shfl_sync(0xffffffffu, cnt, owner);
                     const float nt = warp_compact<EPL>(cand_key + oq * cap, cand_id + oq * cap, n, lane);
                     if (lane == owner) { thr = nt; cnt = L; }
@@ -467,7 +477,7 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
             }
         };
 
-        for (long long t = 0; t < n_tiles; t++) {
+        for (long long t = group; t < n_tiles && group < n_groups; t += n_groups) {
             const int b = (int)(t % kAccBufs);
             const uint32_t ph_b = (uint32_t)((t / kAccBufs) & 1);
             if (!mbar_wait(&sh.acc_full[b], ph_b, abort_flag, 32)) break;
@@ -490,18 +500,43 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
                 process_chunk(r, p0 + c0, inside);
             }
         }
-        // final selection: leave the L best, sorted, in front of every served buffer
-        unsigned m = __ballot_sync(0xffffffffu, serve);
+        if (group < n_groups) { sh.cnt[group][row] = cnt; sh.overflow[group][row] = overflow ? 1 : 0; }
+    }
+    __syncthreads();   // every tile has been compared (or the block has given up)
+    if (warp < 8) {
+        // final selection: leave the L best, sorted, in front of every served query's buffer.  With two
+        // groups, group g selects for the queries whose TMEM lane has parity g.
+        const int group = warp >> 2, quarter = warp & 3;
+        const int n_groups = FIXED ? 2 : 1;
+        const long long gq_lane = qt * TM + quarter * 32 + lane;
+        const bool mine = gq_lane >= q_lo && gq_lane < q_hi && group < n_groups && (lane % n_groups) == group;
+        unsigned m = __ballot_sync(0xffffffffu, mine);
         while (m) {
             const int owner = __ffs(m) - 1;
             m &= m - 1;
-            const long long oq = qt * TM + warp * 32 + owner - q_lo;
-            const int n = __shfl_sync(0xffffffffu, cnt, owner);
+            const int orow = quarter * 32 + owner;
+            const long long oq = qt * TM + orow - q_lo;
             float *ok = cand_key + oq * cap;
             int32_t *oi = cand_id + oq * cap;
-            int first = min(n, C);
+            int n = sh.cnt[0][orow];
+            bool ovf = sh.overflow[0][orow] != 0;
+            if (FIXED) {   // bring the second group's segment next to the first (moving down, 32 at a time)
+                const int n1 = sh.cnt[1][orow];
+                ovf = ovf || sh.overflow[1][orow] != 0;
+                for (int e0 = 0; e0 < n1; e0 += 32) {
+                    const int e = e0 + lane;
+                    float kk = 0.0f;
+                    int ii = 0;
+                    if (e < n1) { kk = __ldcg(ok + cap / 2 + e); ii = __ldcg(oi + cap / 2 + e); }
+                    __syncwarp();
+                    if (e < n1) { __stcg(ok + n + e, kk); __stcg(oi + n + e, ii); }
+                    __syncwarp();
+                }
+                n += n1;
+            }
+            const int first = min(n, C);
             (void)warp_compact<EPL>(ok, oi, first, lane);
-            for (int pos = first; pos < n; pos += C - L) {     // FIXED mode only: fold the rest in, C - L at a time
+            for (int pos = first; pos < n; pos += C - L) {     // fold the rest in, C - L at a time
                 const int chunk = min(C - L, n - pos);
                 for (int e = lane; e < chunk; e += 32) {
                     __stcg(ok + L + e, __ldcg(ok + pos + e));
@@ -510,7 +545,7 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
                 __syncwarp();
                 (void)warp_compact<EPL>(ok, oi, L + chunk, lane);
             }
-            if (FIXED && lane == owner) row_flags[oq] = (overflow || n < L) ? 1 : 0;
+            if (FIXED && lane == 0) row_flags[oq] = (ovf ? 1 : 0) | (n < L ? 2 : 0);   // bit 0: a buffer overflowed, bit 1: fewer than L candidates
         }
     }
     // ---------------- teardown ----------------
@@ -518,7 +553,7 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
     __syncthreads();
     tc_fence_after();
     if (threadIdx.x == 0 && sh.abort_flag) atomicExch(error_flag, 1);
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
@@ -619,13 +654,88 @@ knn_tc_rerank_kernel(const float *__restrict__ X, int D, long long q_lo, long lo
     }
 }
 
-// tau[q] = key of rank `rank` (0-based) in the sorted sample list of query q (+inf if the list is shorter)
+// First threshold level on the CUDA cores: tau[q] = the key of rank `rank` (0-based, < 16) among m sample
+// points X[s_lo + k * s_stride + jitter_k], k = 0..m-1, for each of the nq queries starting at row q_lo.  Keys are
+// plain fp32 FMA sums: this threshold only has to be roughly right (it sizes the candidate set of the
+// next level).  One query per thread, held in registers; sample points staged 32 at a time in shared
+// memory and read as broadcast float4.
+constexpr int kTauThreads = 128;
+__global__ void __launch_bounds__(kTauThreads)
+knn_sample_tau_kernel(const float *__restrict__ X, int D, long long q_lo, long long nq, long long s_lo, long long s_stride,
+                      int m, int rank, float *__restrict__ tau)
+{
+    __shared__ __align__(16) float s_pt[32][64];
+    __shared__ float s_nrm[32];
+    const long long q = (long long)blockIdx.x * kTauThreads + threadIdx.x;
+    float4 qv[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int d = 4 * i + e;
+            v[e] = (q < nq && d < D) ? X[(q_lo + q) * D + d] : 0.0f;
+        }
+        qv[i] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    float top[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) top[i] = INFINITY;
+    for (int k0 = 0; k0 < m; k0 += 32) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 32 * 64; idx += kTauThreads) {
+            const int p = idx >> 6, d = idx & 63;
+            // jittered systematic sample: a plain stride would alias with any periodic ordering of the data
+            const long long k = k0 + p;
+            const long long j = s_lo + k * s_stride + (long long)(((unsigned long long)k * 2654435761ull) % (unsigned long long)s_stride);
+            s_pt[p][d] = (k < m && d < D) ? X[j * D + d] : 0.0f;
+        }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float n2 = 0.0f;
+            for (int d = 0; d < 64; d++) n2 += s_pt[threadIdx.x][d] * s_pt[threadIdx.x][d];
+            s_nrm[threadIdx.x] = (k0 + threadIdx.x < m) ? n2 : INFINITY;
+        }
+        __syncthreads();
+        for (int p = 0; p < 32; p++) {
+            const float4 *sp = reinterpret_cast<const float4 *>(s_pt[p]);
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const float4 a = sp[i];
+                dot += qv[i].x * a.x + qv[i].y * a.y + qv[i].z * a.z + qv[i].w * a.w;
+            }
+            const float key = fmaf(-2.0f, dot, s_nrm[p]);
+            if (key < top[15]) {
+                top[15] = key;
+#pragma unroll
+                for (int i = 15; i > 0; i--) {
+                    const float lo = fminf(top[i - 1], top[i]), hi = fmaxf(top[i - 1], top[i]);
+                    top[i - 1] = lo;
+                    top[i] = hi;
+                }
+            }
+        }
+    }
+    if (q < nq) {
+        float t = top[0];
+#pragma unroll
+        for (int i = 1; i < 16; i++) t = (i == rank) ? top[i] : t;
+        tau[q] = t;
+    }
+}
+
+// tau[q] = key of rank `rank` (0-based) in the sorted sample list of query q.  A list shorter than that,
+// or a sample pass that flagged the row, gives -inf: the next pass keeps nothing for the row, flags it,
+// and the row is recomputed by the SIMT search.  (When the whole database is smaller than the list the
+// caller does not use a sample pass.)
 __global__ void knn_tc_tau_kernel(const float *__restrict__ sample_key, const int32_t *__restrict__ sample_id, int stride,
-                                  int rank, long long nq, float *__restrict__ tau)
+                                  int rank, const int *__restrict__ flags, long long nq, float *__restrict__ tau)
 {
     const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (q >= nq) return;
-    tau[q] = (sample_id[q * stride + rank] == INT_MAX) ? INFINITY : sample_key[q * stride + rank];
+    const bool bad = sample_id[q * stride + rank] == INT_MAX || (flags && (flags[q] & 1));   // overflow loses keys below tau; a short list does not
+    tau[q] = bad ? -INFINITY : sample_key[q * stride + rank];
 }
 
 __global__ void knn_tc_collect_failed_kernel(const int *__restrict__ failed, long long nq, long long q_lo, int *__restrict__ list,
@@ -644,7 +754,7 @@ bool knn_tc_supported(int64_t N, int D, int K)
 }
 
 constexpr int kFixedCap = 1024;      // candidate buffer entries per query in the fixed-threshold pass
-constexpr int kSampleStride = 32;    // pass 1 looks at every 32nd database tile
+constexpr int kSampleStride = 16;    // the sample pass looks at every 16th database tile
 constexpr long long kTwoPassMinTiles = 512;   // below this many database tiles the online pass alone is used
 
 // Workspace (device) needed by launch_knn_tc; all sizes in bytes.
@@ -719,11 +829,24 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         if (EPL == 8) B200_KNN_FILTER(8, false, 1, nullptr, C, cand_key, cand_id, nullptr);
         else B200_KNN_FILTER(16, false, 1, nullptr, C, cand_key, cand_id, nullptr);
     } else {
-        // pass 1: online threshold on every kSampleStride-th tile; pass 2: everything against the fixed tau
-        if (EPL == 8) B200_KNN_FILTER(8, false, kSampleStride, nullptr, C, cand_key, cand_id, nullptr);
-        else B200_KNN_FILTER(16, false, kSampleStride, nullptr, C, cand_key, cand_id, nullptr);
-        const int rank = std::max(4, (3 * L + kSampleStride - 1) / kSampleStride) - 1;
-        knn_tc_tau_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(cand_key, cand_id, C, rank, nq, tau);
+        // Three levels, each fixing the threshold of the next:
+        //  A  (CUDA cores) rank ~10 of a few thousand sample points spread over the database -> tau_A,
+        //     chosen so that ~300 points of sample B beat it;
+        //  B  every kSampleStride-th tile against tau_A;
+        //  C  everything against tau_B = the key of rank ~3L/kSampleStride in sample B: ~3L points beat it.
+        const long long n_db_tiles = dt_hi - dt_lo;
+        const double b_points = (double)((n_db_tiles + kSampleStride - 1) / kSampleStride) * TN;
+        const long long db_n = db_hi - db_lo;
+        const int m_a = (int)std::min<long long>(db_n, std::min<long long>(16384, std::max<long long>(2048, (long long)(b_points / 32))));
+        const long long a_stride = std::max<long long>(1, db_n / m_a);
+        const int rank_a = std::min(15, std::max(4, (int)(300.0 * m_a / b_points + 0.5))) - 1;
+        const int rank_b = std::max(4, (3 * L + kSampleStride - 1) / kSampleStride) - 1;
+        knn_sample_tau_kernel<<<(unsigned)((nq + kTauThreads - 1) / kTauThreads), kTauThreads, 0, st>>>(X, D, q_lo, nq, db_lo, a_stride,
+                                                                                                m_a, rank_a, tau);
+        B200_CUDA(cudaGetLastError());
+        if (EPL == 8) B200_KNN_FILTER(8, true, kSampleStride, tau, kFixedCap, fix_key, fix_id, row_flags);
+        else B200_KNN_FILTER(16, true, kSampleStride, tau, kFixedCap, fix_key, fix_id, row_flags);
+        knn_tc_tau_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(fix_key, fix_id, kFixedCap, rank_b, row_flags, nq, tau);
         B200_CUDA(cudaGetLastError());
         if (EPL == 8) B200_KNN_FILTER(8, true, 1, tau, kFixedCap, fix_key, fix_id, row_flags);
         else B200_KNN_FILTER(16, true, 1, tau, kFixedCap, fix_key, fix_id, row_flags);
