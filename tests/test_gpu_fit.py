@@ -42,19 +42,22 @@ def test_session_matches_reference_quality(engine, oracle_cpu, golden):
     assert abs(nnp - float(golden["nnp_fit"])) < 0.005 + 0.01
 
 
-def test_chunked_run_equals_single_run_in_quality(engine, golden):
+def test_chunked_run_equals_single_run_in_quality(engine, oracle_cpu, golden):
+    """Running the loop in pieces follows the same schedule; only the order of the spread's floating-point
+    reductions differs, which exaggerated iterations amplify, so the runs are compared by their KL."""
     P, ids, Y0 = golden["P"], golden["ids"], golden["Y_a"]
     N, K = P.shape
-    out = []
-    for chunks in ((60,), (1, 9, 50)):
+    kl = []
+    for chunks in ((300,), (1, 9, 50, 240)):
         with engine.Session(N, K) as s:
             s.set_affinities(P, ids)
-            s.set_schedule(200.0, 12.0, 30, 0.5, 0.8)
+            s.set_schedule(200.0, 12.0, 100, 0.5, 0.8)
             s.set_embedding(Y0)
             for c in chunks:
                 s.run(c)
-            out.append(s.get_embedding())
-    assert rel_l2(out[0], out[1]) < 1e-2     # identical schedule; only the spread's atomic order differs
+            assert s.stats()["step"] == 300
+            kl.append(oracle_cpu.kl_divergence(P, ids, s.get_embedding()))
+    assert abs(kl[0] - kl[1]) / kl[0] < 0.02
 
 
 def test_min_gradient_norm_stops_early(engine, golden):
