@@ -108,6 +108,23 @@ int b200tsne_knn(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t 
  * fraction of the assumed bound.  No counterpart in the reference. */
 int b200tsne_knn_last_stats(int *tensor_core, int *rows_recomputed, float *filter_error_ratio);
 
+/* Exact k nearest neighbours without any allocation.  This entry point has no counterpart in the
+ * reference.  It is for hosts that must not allocate device memory when they call in: a framework that
+ * hands out all device memory from its own pool, a service whose footprint is fixed at start-up, a
+ * latency-bound loop where cudaMalloc's implicit synchronisation is unacceptable.  X_device ([N][D]),
+ * ids_device and d2_device ([N][K]) are DEVICE pointers on the current device, owned by the caller; the
+ * one piece of scratch the search needs (a dimension-major copy of X) lives in a fixed array inside the
+ * library, so N * D must not exceed b200tsne_knn_noalloc_max_elements() (4 Mi floats = 16 MiB, resident
+ * on every GPU that loads the library); larger inputs are rejected with B200TSNE_ERR_UNSUPPORTED.
+ * The work is queued on cuda_stream (a cudaStream_t, NULL = default stream) and the call returns without
+ * waiting.  The first call on a device looks up the array's device address; make that call before any
+ * stream capture.  All calls share the one array, which keeps the previous call's contents (every element
+ * the search reads is rewritten first): two calls whose GPU work overlaps, on different streams or from
+ * different threads, race on it.  Results equal b200tsne_knn's (SIMT search; whole database, all queries). */
+int b200tsne_knn_noalloc(const float *X_device, int64_t N, int D, int K, int32_t *ids_device, float *d2_device,
+                         void *cuda_stream);
+int64_t b200tsne_knn_noalloc_max_elements(void);
+
 /* Global max-normalisation of the squared distances followed by the per-row perplexity search;
  * p receives the row-normalised conditional probabilities, betas (may be NULL) the found betas,
  * max_out (may be NULL) the normalising maximum.  If max_override > 0 it is used instead of the

@@ -46,6 +46,8 @@ SIGNATURES = {
     "b200tsne_fit": (C.c_int, [_fp, _i64, C.c_int, C.POINTER(Options), _fp, _fp]),
     "b200tsne_knn": (C.c_int, [_fp, _i64, C.c_int, C.c_int, _i64, _i64, _i64, _i64, _ip, _fp, C.c_int]),
     "b200tsne_knn_last_stats": (C.c_int, [C.POINTER(C.c_int), C.POINTER(C.c_int), _fp]),
+    "b200tsne_knn_noalloc": (C.c_int, [C.c_void_p, _i64, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200tsne_knn_noalloc_max_elements": (_i64, []),
     "b200tsne_perplexity": (C.c_int, [_fp, _i64, C.c_int, C.c_float, C.c_float, C.c_float, _fp, _fp, _fp, C.c_int]),
     "b200tsne_symmetrize": (C.c_int, [_fp, _ip, _i64, C.c_int, _fp, C.c_int]),
     "b200tsne_attractive": (C.c_int, [_fp, _ip, _fp, _i64, C.c_int, _i64, _i64, _fp, C.c_int]),

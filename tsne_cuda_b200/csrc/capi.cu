@@ -240,6 +240,16 @@ int b200tsne_knn_last_stats(int *tensor_core, int *rows_recomputed, float *filte
     return 0;
 }
 
+int b200tsne_knn_noalloc(const float *X_device, int64_t N, int D, int K, int32_t *ids_device, float *d2_device,
+                         void *cuda_stream)
+{
+    if (!X_device || !ids_device || !d2_device) { set_error("b200tsne_knn_noalloc: null pointer"); return B200TSNE_ERR_INVALID; }
+    if (N > 2147483647LL) { set_error("b200tsne_knn_noalloc: too many points"); return B200TSNE_ERR_UNSUPPORTED; }
+    return knn_noalloc(X_device, N, D, K, ids_device, d2_device, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int64_t b200tsne_knn_noalloc_max_elements(void) { return knn_noalloc_max_elems(); }
+
 // ---- session -------------------------------------------------------------------------------------
 int b200tsne_session_create(b200tsne_session **out, int64_t N, int K, int64_t row_lo, int64_t row_hi, int device)
 {

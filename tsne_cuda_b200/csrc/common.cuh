@@ -92,6 +92,9 @@ struct KnnStats {
 // X: [N][D] row-major on the device; picks the path, handles the fallback rows, synchronises `st`.
 int knn_search(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_hi, int64_t db_lo, int64_t db_hi,
                int32_t *ids, float *d2, KnnStats *stats, cudaStream_t st);
+// knn.cu: search with the scratch in a fixed device array of the library (no allocation)
+long long knn_noalloc_max_elems();
+int knn_noalloc(const float *X, int64_t N, int D, int K, int32_t *ids, float *d2, cudaStream_t st);
 int launch_knn_merge(const int32_t *ids_parts, const float *d2_parts, int parts, int64_t part_stride, int64_t n_rows,
                      int K, int32_t *ids, float *d2, cudaStream_t st);
 int launch_knn_finalize(int32_t *ids, float *d2, int64_t n, cudaStream_t st);

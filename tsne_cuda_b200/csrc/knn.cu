@@ -18,6 +18,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <string>
+
 #include "common.cuh"
 #include "session.h"
 
@@ -326,6 +328,55 @@ int knn_search(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_
         B200_TRY(launch_knn_exact_rows(XT, N, D, K, failed_list, n_failed, q_lo, db_lo, db_hi, ids, d2, st));
     }
     B200_CUDA(cudaStreamSynchronize(st));
+    return 0;
+}
+
+
+// ---------------------------------------------------------------------------------------------------
+// Exact search for callers that must not allocate.
+//
+// Some hosts own every byte of device memory themselves (a framework with its own pool, a service that
+// pre-sizes its footprint at start-up, a real-time loop in which cudaMalloc's implicit device
+// synchronisation is not acceptable).  For them the dimension-major copy of the points that the SIMT
+// search reads lives in a fixed array that is part of the library image: every GPU that loads the
+// library carries kNoAllocMaxElems floats (16 MiB) for it until the process exits.
+// ---------------------------------------------------------------------------------------------------
+constexpr long long kNoAllocMaxElems = 4ll << 20;   // N * D may not exceed this
+static __device__ __align__(256) float g_noalloc_xt[kNoAllocMaxElems];
+
+// In host code `g_noalloc_xt` is only a handle; the address a kernel can use comes from the runtime and
+// differs per device.  Looked up once per device, with that device current.
+static int noalloc_scratch(float **out)
+{
+    static float *cached[64] = {nullptr};
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) { set_error("knn_noalloc: device ordinal out of range"); return -4; }
+    if (!cached[dev]) {
+        float *p = nullptr;
+        B200_CUDA(cudaGetSymbolAddress((void **)&p, g_noalloc_xt));
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return 0;
+}
+
+long long knn_noalloc_max_elems() { return kNoAllocMaxElems; }
+
+// X, ids, d2: device memory of the current device.  Queues the search on `st` and returns.
+int knn_noalloc(const float *X, int64_t N, int D, int K, int32_t *ids, float *d2, cudaStream_t st)
+{
+    if (N <= 0 || D <= 0 || K <= 0) { set_error("knn_noalloc: invalid sizes"); return -1; }
+    if ((long long)N * D > kNoAllocMaxElems) {
+        set_error("knn_noalloc: N * D = " + std::to_string((long long)N * D) + " exceeds the built-in scratch of " +
+                  std::to_string(kNoAllocMaxElems) + " floats; use b200tsne_knn");
+        return -4;
+    }
+    float *XT = nullptr;
+    B200_TRY(noalloc_scratch(&XT));
+    B200_TRY(launch_transpose(X, N, D, XT, st));      // overwrites every element the search will read
+    B200_TRY(launch_knn_exact(XT, N, D, K, 0, N, 0, N, ids, d2, st));
+    B200_TRY(launch_knn_finalize(ids, d2, N * K, st));
     return 0;
 }
 
