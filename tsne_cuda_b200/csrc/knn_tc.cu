@@ -10,10 +10,8 @@
 //     hi, lo representable in TF32;  hi.hi + lo.hi + hi.lo, accumulated in fp32 in TMEM), accurate to
 //     about 2^-20 of |x_i||x_j|.  A block owns 128 queries (one TMEM lane each) and
 //     walks the database in tiles of 128 points; each epilogue thread compares its row of the
-//     accumulator tile with a threshold (the L-th best key its query had at the last compaction,
-//     L = K + slack) and appends the rare survivors to the query's candidate buffer with plain
-//     stores; when a buffer is nearly full its warp sorts it (bitonic network in registers) and keeps
-//     the L best, which tightens the threshold.  No N x N matrix is written.
+//     accumulator tile with a per-query threshold and appends the rare survivors to the query's
+//     candidate buffer with plain stores; the L = K + slack best are kept.  No N x N matrix is written.
 //  2. Re-rank.  The canonical distance of the L candidates is evaluated exactly and they are ordered by
 //     (distance, id).
 //  3. Proof.  Every point that is not a candidate has a key >= T (the largest key in the list), hence a
@@ -28,12 +26,15 @@
 // step 128 bytes apart; 8-row groups 256 bytes apart).  A tile is therefore ONE contiguous bulk
 // copy (cp.async.bulk + mbarrier complete_tx) with no tensor map and no swizzle.
 //
-// Two passes for large databases.  With the threshold maintained online, a query appends about
-// L ln(N/L) candidates, and although that is rare per thread it is not rare per warp of 32 queries.  So
-// pass 1 runs the online scheme on every 32nd database tile only, pass 2 scans everything against a FIXED
-// per-query threshold tau = the key of rank ~3L/32 in the sample: about 3L points beat it, no buffer is
-// compacted during the scan, and the L best are selected once at the end.  A row with fewer than L or
-// more than the buffer's capacity of candidates is flagged and recomputed by the SIMT search.
+// Thresholds.  For a small database the threshold is maintained online: the L-th best key at the last
+// compaction of the query's buffer (a warp-wide bitonic sort).  That appends about L ln(N/L) candidates per
+// query, which is rare per thread but not per warp of 32 queries, and each compaction costs thousands of
+// issue slots.  For a large database (>= 512 tiles) the threshold is therefore FIXED per query, in three
+// levels, each sizing the candidate set of the next: (A) on the CUDA cores, the key of rank ~10 among a
+// few thousand jittered sample points; (B) every 16th tile against tau_A (~300 candidates); (C) all
+// tiles against tau_B = the key of rank ~3L/16 of sample B, which about 3L points beat.  Nothing is
+// compacted during a fixed-threshold scan; the L best are selected once at the end.  A row whose buffer
+// overflows or ends with fewer than L candidates is flagged and recomputed by the SIMT search.
 //
 // Epilogue: a thread first reduces its 32 keys of a chunk to their minimum (a tree of independent
 // min operations); only if that minimum beats the threshold, which becomes rare as the scan
