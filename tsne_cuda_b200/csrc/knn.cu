@@ -18,6 +18,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <string>
 
 #include "common.cuh"
@@ -316,16 +317,27 @@ int knn_search(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_
         B200_CUDA(cudaStreamSynchronize(st));   // XT is released on return
         return 0;
     }
+    // Queries go through in batches of 2^20 so that the candidate buffers (about 10 KB per query) stay
+    // bounded however large N is; the operand images are rebuilt per batch (a millisecond per million points).
+    const int64_t batch = (int64_t)1 << 20;
     void *ws = nullptr;
-    B200_TRY(tmp.alloc(&ws, knn_tc_workspace_bytes(N, D, K, nq)));
-    int *failed_list = nullptr;
-    int n_failed = 0;
-    B200_TRY(launch_knn_tc(X, N, D, K, q_lo, q_hi, db_lo, db_hi, ids, d2, ws, &failed_list, &n_failed, &stats->filter_error_ratio, st));
+    B200_TRY(tmp.alloc(&ws, knn_tc_workspace_bytes(N, D, K, std::min(nq, batch))));
     stats->tensor_core = 1;
-    stats->rows_recomputed = n_failed;
-    if (n_failed > 0) {
-        B200_TRY(ensure_xt());
-        B200_TRY(launch_knn_exact_rows(XT, N, D, K, failed_list, n_failed, q_lo, db_lo, db_hi, ids, d2, st));
+    for (int64_t b_lo = q_lo; b_lo < q_hi; b_lo += batch) {
+        const int64_t b_hi = std::min(q_hi, b_lo + batch);
+        int *failed_list = nullptr;
+        int n_failed = 0;
+        float ratio = 0.0f;
+        int32_t *ids_b = ids + (b_lo - q_lo) * K;
+        float *d2_b = d2 + (b_lo - q_lo) * K;
+        B200_TRY(launch_knn_tc(X, N, D, K, b_lo, b_hi, db_lo, db_hi, ids_b, d2_b, ws, &failed_list, &n_failed, &ratio, st));
+        stats->rows_recomputed += n_failed;
+        stats->filter_error_ratio = std::max(stats->filter_error_ratio, ratio);
+        if (n_failed > 0) {
+            B200_TRY(ensure_xt());
+            B200_TRY(launch_knn_exact_rows(XT, N, D, K, failed_list, n_failed, b_lo, db_lo, db_hi, ids_b, d2_b, st));
+            B200_CUDA(cudaStreamSynchronize(st));   // the failed list lives in the workspace the next batch reuses
+        }
     }
     B200_CUDA(cudaStreamSynchronize(st));
     return 0;
