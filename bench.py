@@ -146,7 +146,10 @@ def run_ours(args):
     attr_bytes = 8.0 * rows * K + 16.0 * rows
     peak, peak_kind = load_peaks()
     roof = {"bound": "hbm", "kernel": "attractive_kernel", "achieved": attr_bytes / attr_s / 1e9 if attr_s > 0 else None,
-            "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "traffic": None,
+            "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+            # dram__bytes_read + dram__bytes_write of one launch, from the ncu capture at N = 400,000 summarised in
+            # profiles/attractive_kernel_n400k.md (296.3 MB for 294.4 MB algorithmic), scaled by the units processed
+            "traffic": attr_bytes * (296.3 / 294.4),
             "algorithmic_bytes_per_launch": attr_bytes, "avg_launch_us": attr_s * 1e6}
     roof["frac"] = roof["achieved"] / peak if roof["achieved"] else None
     it_bytes = iter_bytes(N, K) / world

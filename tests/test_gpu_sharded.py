@@ -1,0 +1,84 @@
+"""GPU suite for the point-sharded path (needs 2 GPUs; skipped otherwise): two ranks, NCCL exchanges issued
+by the library, results against a single-GPU session on the same inputs."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from conftest import mixture, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank(rank, world, port, X, Y0, K, out):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        from tsne_cuda_b200 import distributed
+        s = distributed.open_session(X.shape[0], K, rank, rank, world)
+        s.affinities_from_points(X, 20.0, 1e-4)
+        P, ids = s.get_affinities()
+        s.set_schedule(200.0, 12.0, 250, 0.5, 0.8)
+        s.set_embedding(Y0)
+        s.run(1)
+        Y1 = s.get_embedding()
+        s.run(199)
+        Y200 = s.get_embedding()
+        st = s.stats()
+        s.close()
+        out.put((rank, "ok", P, ids, Y1, Y200, st["Z"]))
+    except Exception as e:  # report instead of leaving the peer in a collective
+        out.put((rank, "FAILED: %r" % (e,), None, None, None, None, None))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_match_one(engine, oracle_cpu):
+    torch = pytest.importorskip("torch")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    from tsne_cuda_b200.distributed import shard_rows
+    N, D, K = 3001, 24, 40          # N not divisible by the number of ranks
+    X = mixture(N, D, 3)
+    Y0 = (1e-4 * np.random.default_rng(0).standard_normal((2, N))).astype(np.float32)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank, args=(r, 2, port, X, Y0, K, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted([q.get(timeout=300) for _ in procs], key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+    assert [r[1] for r in res] == ["ok", "ok"], [r[1] for r in res]
+    with engine.Session(N, K) as s:
+        s.affinities_from_points(X, 20.0, 1e-4)
+        P1, ids1 = s.get_affinities()
+        s.set_schedule(200.0, 12.0, 250, 0.5, 0.8)
+        s.set_embedding(Y0)
+        s.run(1)
+        Y1 = s.get_embedding()
+        s.run(199)
+        Y200 = s.get_embedding()
+    for r in range(2):
+        lo, hi = shard_rows(N, 2, r)
+        assert np.array_equal(res[r][3], ids1[lo:hi])          # neighbour ids: exact after the sharded search + merge
+        assert np.array_equal(res[r][2], P1[lo:hi])            # P: same global maximum, same rows
+        assert rel_l2(res[r][4], Y1) < 1e-5                    # one iteration: forces agree (grid summed in another order)
+    assert np.array_equal(res[0][4], res[1][4]) and np.array_equal(res[0][5], res[1][5])   # ranks hold the same embedding
+    kl1 = oracle_cpu.kl_divergence(P1, ids1, Y200)
+    kl2 = oracle_cpu.kl_divergence(P1, ids1, res[0][5])
+    assert abs(kl1 - kl2) / kl1 < 0.02
