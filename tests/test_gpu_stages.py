@@ -24,6 +24,32 @@ def test_knn_bit_exact(engine, oracle_cpu, n, d, k):
     assert np.array_equal(d2, d2_o)
 
 
+@pytest.mark.parametrize("n,d,k", [(3000, 50, 90), (70000, 30, 150), (420000, 50, 90)])
+def test_knn_tensor_core_paths(engine, oracle_cpu, n, d, k):
+    """Online threshold (small), sample -> full (medium) and sample -> strided -> full (large) variants of the
+    tensor-core search: exact on sampled queries, and the SIMT fallback is only needed for a few rows."""
+    from tsne_cuda_b200 import datasets
+    X = datasets.gaussian_mixture(n, d, seed=n)
+    ids, d2 = engine.knn(X, k)
+    st = engine.knn_last_stats()
+    assert st["tensor_core"] == 1 and st["rows_recomputed"] <= 0.01 * n and st["filter_error_ratio"] < 0.5
+    lo = n // 3
+    ids_o, d2_o = oracle_cpu.knn(X, k, q_lo=lo, q_hi=lo + 64)
+    assert np.array_equal(ids[lo:lo + 64], ids_o) and np.array_equal(d2[lo:lo + 64], d2_o)
+    assert np.array_equal(ids[:, 0], np.arange(n)) and (np.diff(d2, axis=1) >= 0).all()
+
+
+def test_knn_tensor_core_matches_simt_everywhere(engine, monkeypatch):
+    X = mixture(9000, 40, 12)
+    X[100:140] = X[100]                      # a clump of identical points: ties the proof cannot certify
+    a = engine.knn(X, 60)
+    assert engine.knn_last_stats()["tensor_core"] == 1 and engine.knn_last_stats()["rows_recomputed"] >= 40
+    monkeypatch.setenv("B200TSNE_KNN", "simt")
+    b = engine.knn(X, 60)
+    assert engine.knn_last_stats()["tensor_core"] == 0
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
 def test_knn_ties_and_duplicates(engine, oracle_cpu):
     X = np.zeros((300, 4), np.float32)
     X[100:200] = 1.0

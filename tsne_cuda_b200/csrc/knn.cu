@@ -179,8 +179,9 @@ knn_exact_kernel(const float *__restrict__ XT, long long N, int D, int K, long l
                     const float cd = __shfl_sync(0xffffffffu, dl[c], src);
                     const int ci = (int)(p0 + src * 4 + c);
                     if (cd < td || (cd == td && ci < ti)) {   // the threshold may have moved since the ballot
-                        volatile float *ld = d2 + (gq - out_base) * K;
-                        volatile int32_t *li = ids + (gq - out_base) * K;
+                        const long long orow = (out_base < 0) ? (q0 + q) : (gq - out_base);   // out_base < 0: by list position
+                        volatile float *ld = d2 + orow * K;
+                        volatile int32_t *li = ids + orow * K;
                         warp_insert(ld, li, K, cd, ci, lane);
                         td = ld[K - 1];
                         ti = li[K - 1];
@@ -195,11 +196,12 @@ knn_exact_kernel(const float *__restrict__ XT, long long N, int D, int K, long l
 // Merge `parts` ascending lists per row (list p of row r at parts_base + p*part_stride + r*K) into the
 // K best by (distance, id).  One thread per row; used after a database-sharded search.
 __global__ void knn_merge_kernel(const int32_t *__restrict__ ids_parts, const float *__restrict__ d2_parts, int parts,
-                                 long long part_stride, long long n_rows, int K, int32_t *__restrict__ ids,
-                                 float *__restrict__ d2)
+                                 long long part_stride, long long n_rows, int K, const int *__restrict__ row_index,
+                                 long long out_base, int32_t *__restrict__ ids, float *__restrict__ d2)
 {
     const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n_rows) return;
+    const long long orow = row_index ? (row_index[r] - out_base) : r;   // where the merged list goes
     int head[16];
     for (int p = 0; p < 16; p++) head[p] = 0;
     for (int s = 0; s < K; s++) {
@@ -212,8 +214,8 @@ __global__ void knn_merge_kernel(const int32_t *__restrict__ ids_parts, const fl
             const float cd = d2_parts[o];
             if (best < 0 || cd < bd || (cd == bd && ci < bi)) { best = p; bd = cd; bi = ci; }
         }
-        ids[r * K + s] = bi;
-        d2[r * K + s] = bd;
+        ids[orow * K + s] = bi;
+        d2[orow * K + s] = bd;
         if (best >= 0) head[best]++;
     }
 }
@@ -224,7 +226,7 @@ __global__ void knn_init_rows_kernel(int32_t *ids, float *d2, const int *__restr
 {
     const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= nq * K) return;
-    const long long row = q_index[t / K] - out_base;
+    const long long row = (out_base < 0) ? (t / K) : (q_index[t / K] - out_base);
     ids[row * K + t % K] = INT_MAX;
     d2[row * K + t % K] = INFINITY;
 }
@@ -244,7 +246,7 @@ int launch_knn_merge(const int32_t *ids_parts, const float *d2_parts, int parts,
     if (n_rows <= 0) return 0;
     if (parts > 16) { set_error("knn merge: more than 16 partial lists"); return -4; }
     knn_merge_kernel<<<(unsigned)((n_rows + 127) / 128), 128, 0, st>>>(ids_parts, d2_parts, parts, part_stride, n_rows, K,
-                                                                      ids, d2);
+                                                                      nullptr, 0, ids, d2);
     B200_CUDA(cudaGetLastError());
     return 0;
 }
@@ -291,6 +293,31 @@ int launch_knn_exact_rows(const float *XT, int64_t N, int D, int K, const int *q
 }
 
 
+// SIMT search for a short list of rows.  A block serves 64 queries against the whole database, so a handful
+// of rows would occupy a handful of SMs for the whole scan: the database is cut into up to 16 slices searched
+// by separate blocks, and the partial lists are merged.
+static int knn_exact_few_rows(const float *XT, int64_t N, int D, int K, const int *rows, int64_t n_rows, int64_t out_base,
+                              int64_t db_lo, int64_t db_hi, int32_t *ids, float *d2, DeviceArena &tmp, cudaStream_t st)
+{
+    const int64_t span = db_hi - db_lo;
+    const int slices = (int)std::max<int64_t>(1, std::min<int64_t>(16, span / 8192));
+    if (slices == 1 || n_rows > 16384)
+        return launch_knn_exact_rows(XT, N, D, K, rows, n_rows, out_base, db_lo, db_hi, ids, d2, st);
+    int32_t *pi = nullptr;
+    float *pd = nullptr;
+    B200_TRY(tmp.alloc((void **)&pi, sizeof(int32_t) * (size_t)slices * n_rows * K));
+    B200_TRY(tmp.alloc((void **)&pd, sizeof(float) * (size_t)slices * n_rows * K));
+    const int64_t step = (span + slices - 1) / slices;
+    for (int s = 0; s < slices; s++) {
+        const int64_t lo = db_lo + s * step, hi = std::min(db_hi, lo + step);
+        B200_TRY(launch_knn_exact_rows(XT, N, D, K, rows, n_rows, -1, lo, hi, pi + (size_t)s * n_rows * K,
+                                       pd + (size_t)s * n_rows * K, st));
+    }
+    knn_merge_kernel<<<(unsigned)((n_rows + 127) / 128), 128, 0, st>>>(pi, pd, slices, n_rows * K, n_rows, K, rows, out_base, ids, d2);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
 // Exact search of queries [q_lo,q_hi) against database rows [db_lo,db_hi) of X ([N][D], device),
 // choosing the tensor-core path where it applies and falling back to the SIMT search for the rows it
 // cannot certify.  Unfilled slots keep (INT_MAX, +inf); see launch_knn_finalize.
@@ -335,7 +362,7 @@ int knn_search(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_
         stats->filter_error_ratio = std::max(stats->filter_error_ratio, ratio);
         if (n_failed > 0) {
             B200_TRY(ensure_xt());
-            B200_TRY(launch_knn_exact_rows(XT, N, D, K, failed_list, n_failed, b_lo, db_lo, db_hi, ids_b, d2_b, st));
+            B200_TRY(knn_exact_few_rows(XT, N, D, K, failed_list, n_failed, b_lo, db_lo, db_hi, ids_b, d2_b, tmp, st));
             B200_CUDA(cudaStreamSynchronize(st));   // the failed list lives in the workspace the next batch reuses
         }
     }

@@ -330,13 +330,14 @@ struct TcShared {
 // each are the L best keys in ascending order ((+inf, INT_MAX) where the database had fewer points).
 // FIXED = false: threshold maintained online, buffers of 32*EPL entries, database tiles dt_lo, dt_lo +
 // tile_stride, ...   FIXED = true: threshold tau[query] fixed, buffers of `cap` entries (row stride of
-// cand_key / cand_id in both modes), row_flags[query] set when a buffer overflows or ends with fewer than L.
+// cand_key / cand_id in both modes, two halves per query); counts[2*query + group] receives the number of
+// entries each epilogue group appended (bit 30 set if its half overflowed); knn_tc_select_kernel finishes.
 template <int EPL, bool FIXED>
 __global__ void __launch_bounds__(kTcThreads, 1)
 knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int Dp, long long qt_lo,
                      long long dt_lo, long long dt_hi, int tile_stride, long long q_lo, long long q_hi, long long db_lo,
                      long long db_hi, const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id,
-                     int *__restrict__ row_flags, int *error_flag)
+                     int *__restrict__ counts, int *error_flag)
 {
     constexpr int C = 32 * EPL;   // capacity handled by one compaction
     constexpr int L = 16 * EPL;
@@ -504,49 +505,25 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
         if (group < n_groups) { sh.cnt[group][row] = cnt; sh.overflow[group][row] = overflow ? 1 : 0; }
     }
     __syncthreads();   // every tile has been compared (or the block has given up)
-    if (warp < 8) {
-        // final selection: leave the L best, sorted, in front of every served query's buffer.  With two
-        // groups, group g selects for the queries whose TMEM lane has parity g.
-        const int group = warp >> 2, quarter = warp & 3;
-        const int n_groups = FIXED ? 2 : 1;
+    if (FIXED) {
+        // The final selection is a separate kernel (one warp per query, thousands in flight): it is a chain of
+        // dependent global round trips, which eight warps of this block would walk through one query at a time.
+        if (threadIdx.x < 2 * TM) {
+            const int g = threadIdx.x / TM, r = threadIdx.x % TM;
+            const long long gq2 = qt * TM + r;
+            if (gq2 >= q_lo && gq2 < q_hi) counts[(gq2 - q_lo) * 2 + g] = sh.cnt[g][r] | (sh.overflow[g][r] ? 0x40000000 : 0);
+        }
+    } else if (warp < 4) {
+        // online threshold (small databases): one last compaction leaves the L best, sorted, in front
+        const int quarter = warp & 3;
         const long long gq_lane = qt * TM + quarter * 32 + lane;
-        const bool mine = gq_lane >= q_lo && gq_lane < q_hi && group < n_groups && (lane % n_groups) == group;
-        unsigned m = __ballot_sync(0xffffffffu, mine);
+        unsigned m = __ballot_sync(0xffffffffu, gq_lane >= q_lo && gq_lane < q_hi);
         while (m) {
             const int owner = __ffs(m) - 1;
             m &= m - 1;
             const int orow = quarter * 32 + owner;
             const long long oq = qt * TM + orow - q_lo;
-            float *ok = cand_key + oq * cap;
-            int32_t *oi = cand_id + oq * cap;
-            int n = sh.cnt[0][orow];
-            bool ovf = sh.overflow[0][orow] != 0;
-            if (FIXED) {   // bring the second group's segment next to the first (moving down, 32 at a time)
-                const int n1 = sh.cnt[1][orow];
-                ovf = ovf || sh.overflow[1][orow] != 0;
-                for (int e0 = 0; e0 < n1; e0 += 32) {
-                    const int e = e0 + lane;
-                    float kk = 0.0f;
-                    int ii = 0;
-                    if (e < n1) { kk = __ldcg(ok + cap / 2 + e); ii = __ldcg(oi + cap / 2 + e); }
-                    __syncwarp();
-                    if (e < n1) { __stcg(ok + n + e, kk); __stcg(oi + n + e, ii); }
-                    __syncwarp();
-                }
-                n += n1;
-            }
-            const int first = min(n, C);
-            (void)warp_compact<EPL>(ok, oi, first, lane);
-            for (int pos = first; pos < n; pos += C - L) {     // fold the rest in, C - L at a time
-                const int chunk = min(C - L, n - pos);
-                for (int e = lane; e < chunk; e += 32) {
-                    __stcg(ok + L + e, __ldcg(ok + pos + e));
-                    __stcg(oi + L + e, __ldcg(oi + pos + e));
-                }
-                __syncwarp();
-                (void)warp_compact<EPL>(ok, oi, L + chunk, lane);
-            }
-            if (FIXED && lane == 0) row_flags[oq] = (ovf ? 1 : 0) | (n < L ? 2 : 0);   // bit 0: a buffer overflowed, bit 1: fewer than L candidates
+            (void)warp_compact<EPL>(cand_key + oq * cap, cand_id + oq * cap, min(sh.cnt[0][orow], C), lane);
         }
     }
     // ---------------- teardown ----------------
@@ -557,6 +534,51 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
+}
+
+// ------------------------------------------------------------------------------------------------
+// final selection after a fixed-threshold scan: one warp per query
+// ------------------------------------------------------------------------------------------------
+// Buffer of query q: two halves of cap/2 entries with counts[2q], counts[2q+1] valid entries.  Leaves the L
+// best (ascending) in front and sets row_flags[q]: bit 0 = a half overflowed (keys below tau were lost),
+// bit 1 = fewer than L candidates.
+template <int EPL>
+__global__ void __launch_bounds__(128)
+knn_tc_select_kernel(float *cand_key, int32_t *cand_id, int cap, const int *__restrict__ counts, long long nq,
+                     int *__restrict__ row_flags)
+{
+    constexpr int C = 32 * EPL, L = 16 * EPL;
+    const int lane = threadIdx.x & 31;
+    const long long q = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (q >= nq) return;
+    float *ok = cand_key + q * cap;
+    int32_t *oi = cand_id + q * cap;
+    const int c0 = counts[2 * q], c1 = counts[2 * q + 1];
+    const bool ovf = ((c0 | c1) & 0x40000000) != 0;
+    int n = c0 & 0x3fffffff;
+    const int n1 = c1 & 0x3fffffff;
+    for (int e0 = 0; e0 < n1; e0 += 32) {   // bring the second half next to the first (moving down, 32 at a time)
+        const int e = e0 + lane;
+        float kk = 0.0f;
+        int ii = 0;
+        if (e < n1) { kk = __ldcg(ok + cap / 2 + e); ii = __ldcg(oi + cap / 2 + e); }
+        __syncwarp();
+        if (e < n1) { __stcg(ok + n + e, kk); __stcg(oi + n + e, ii); }
+        __syncwarp();
+    }
+    n += n1;
+    const int first = min(n, C);
+    (void)warp_compact<EPL>(ok, oi, first, lane);
+    for (int pos = first; pos < n; pos += C - L) {     // fold the rest in, C - L at a time
+        const int chunk = min(C - L, n - pos);
+        for (int e = lane; e < chunk; e += 32) {
+            __stcg(ok + L + e, __ldcg(ok + pos + e));
+            __stcg(oi + L + e, __ldcg(oi + pos + e));
+        }
+        __syncwarp();
+        (void)warp_compact<EPL>(ok, oi, L + chunk, lane);
+    }
+    if (lane == 0) row_flags[q] = (ovf ? 1 : 0) | (n < L ? 2 : 0);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -754,7 +776,8 @@ bool knn_tc_supported(int64_t N, int D, int K)
     return N >= 2048;   // below this the SIMT search is faster than the set-up of this one
 }
 
-constexpr int kFixedCap = 1024;      // candidate buffer entries per query in the fixed-threshold pass
+// candidate buffer entries per query in a fixed-threshold pass: 8 L (two halves of 4 L for ~1.5 L expected each)
+static int fixed_cap(int K) { return (K + 32 <= 128) ? 1024 : 2048; }
 constexpr int kSampleStride = 16;    // the sample pass looks at every 16th database tile
 constexpr long long kTwoPassMinTiles = 512;   // below this many database tiles the online pass alone is used
 
@@ -769,8 +792,8 @@ size_t knn_tc_workspace_bytes(int64_t N, int D, int K, int64_t nq)
     b += sizeof(double) * (size_t)tiles * TM;       // exact norms
     b += (sizeof(float) + sizeof(int32_t)) * (size_t)nq * C;   // online / sample candidate buffers
     if (tiles >= kTwoPassMinTiles) {
-        b += (sizeof(float) + sizeof(int32_t)) * (size_t)nq * kFixedCap;   // fixed-threshold buffers
-        b += sizeof(float) * (size_t)nq + sizeof(int) * (size_t)nq;        // tau, row flags
+        b += (sizeof(float) + sizeof(int32_t)) * (size_t)nq * fixed_cap(K);   // fixed-threshold buffers
+        b += sizeof(float) * (size_t)nq + sizeof(int) * (size_t)nq * 3;    // tau, row flags, per-group counts
     }
     b += sizeof(int) * ((size_t)nq * 2 + 16);       // failed flags, failed list, counters
     return b + 4096;
@@ -792,6 +815,7 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     const int EPL = (K + 32 <= 128) ? 8 : 16, C = 32 * EPL, L = 16 * EPL;
     const long long qt_lo = q_lo / TM, qt_hi = (q_hi + TM - 1) / TM;
     const long long dt_lo = db_lo / TN, dt_hi = (db_hi + TN - 1) / TN;
+    const int kFixedCap = fixed_cap(K);
     const bool two_pass = (dt_hi - dt_lo) >= kTwoPassMinTiles && tiles >= kTwoPassMinTiles;
     char *p = static_cast<char *>(workspace);
     float *img_q = reinterpret_cast<float *>(p); p += (size_t)tiles * Dp * 1024;
@@ -801,12 +825,13 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     int32_t *cand_id = reinterpret_cast<int32_t *>(p); p += sizeof(int32_t) * (size_t)nq * C;
     float *fix_key = nullptr, *tau = nullptr;
     int32_t *fix_id = nullptr;
-    int *row_flags = nullptr;
+    int *row_flags = nullptr, *counts = nullptr;
     if (tiles >= kTwoPassMinTiles) {
         fix_key = reinterpret_cast<float *>(p); p += sizeof(float) * (size_t)nq * kFixedCap;
         fix_id = reinterpret_cast<int32_t *>(p); p += sizeof(int32_t) * (size_t)nq * kFixedCap;
         tau = reinterpret_cast<float *>(p); p += sizeof(float) * (size_t)nq;
         row_flags = reinterpret_cast<int *>(p); p += sizeof(int) * (size_t)nq;
+        counts = reinterpret_cast<int *>(p); p += sizeof(int) * (size_t)nq * 2;
     }
     int *failed = reinterpret_cast<int *>(p); p += sizeof(int) * (size_t)nq;
     int *flist = reinterpret_cast<int *>(p); p += sizeof(int) * (size_t)nq;
@@ -816,11 +841,11 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     B200_CUDA(cudaGetLastError());
     const size_t smem = (size_t)(1 + kBStages) * Dp * 1024;
     const unsigned grid = (unsigned)(qt_hi - qt_lo);
-#define B200_KNN_FILTER(EPL_, FIXED_, stride_, tau_, cap_, key_, id_, flags_)                                                   \
+#define B200_KNN_FILTER(EPL_, FIXED_, stride_, tau_, cap_, key_, id_, counts_)                                                   \
     do {                                                                                                                        \
         B200_CUDA(cudaFuncSetAttribute(knn_tc_filter_kernel<EPL_, FIXED_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
         knn_tc_filter_kernel<EPL_, FIXED_><<<grid, kTcThreads, smem, st>>>(img_q, img_db, Dp, qt_lo, dt_lo, dt_hi, stride_, q_lo, q_hi, \
-                                                                          db_lo, db_hi, tau_, cap_, key_, id_, flags_, counters + 0); \
+                                                                          db_lo, db_hi, tau_, cap_, key_, id_, counts_, counters + 0); \
         B200_CUDA(cudaGetLastError());                                                                                          \
     } while (0)
     const float *final_key = cand_key;
@@ -838,19 +863,39 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         const long long n_db_tiles = dt_hi - dt_lo;
         const double b_points = (double)((n_db_tiles + kSampleStride - 1) / kSampleStride) * TN;
         const long long db_n = db_hi - db_lo;
-        const int m_a = (int)std::min<long long>(db_n, std::min<long long>(16384, std::max<long long>(2048, (long long)(b_points / 32))));
+        // Up to ~400k points the sample of level A is large enough (16 N / 3L points, rank ~16) to fix the
+        // threshold of level C directly; beyond that level B refines it.
+        const bool direct = db_n <= 393216;
+        const int m_a = direct ? (int)std::min<long long>(16384, std::max<long long>(1024, 16 * db_n / (3 * L)))
+                               : (int)std::min<long long>(16384, std::max<long long>(2048, (long long)(b_points / 32)));
         const long long a_stride = std::max<long long>(1, db_n / m_a);
-        const int rank_a = std::min(15, std::max(4, (int)(300.0 * m_a / b_points + 0.5))) - 1;
+        const double a_target = direct ? 3.0 * L * m_a / (double)db_n : 300.0 * m_a / b_points;
+        const int rank_a = std::min(16, std::max(4, (int)(a_target + 0.5))) - 1;
         const int rank_b = std::max(4, (3 * L + kSampleStride - 1) / kSampleStride) - 1;
         knn_sample_tau_kernel<<<(unsigned)((nq + kTauThreads - 1) / kTauThreads), kTauThreads, 0, st>>>(X, D, q_lo, nq, db_lo, a_stride,
                                                                                                 m_a, rank_a, tau);
         B200_CUDA(cudaGetLastError());
-        if (EPL == 8) B200_KNN_FILTER(8, true, kSampleStride, tau, kFixedCap, fix_key, fix_id, row_flags);
-        else B200_KNN_FILTER(16, true, kSampleStride, tau, kFixedCap, fix_key, fix_id, row_flags);
-        knn_tc_tau_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(fix_key, fix_id, kFixedCap, rank_b, row_flags, nq, tau);
+        const unsigned sel_grid = (unsigned)((nq + 3) / 4);
+        if (!direct) {
+            if (EPL == 8) {
+                B200_KNN_FILTER(8, true, kSampleStride, tau, kFixedCap, fix_key, fix_id, counts);
+                knn_tc_select_kernel<8><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, row_flags);
+            } else {
+                B200_KNN_FILTER(16, true, kSampleStride, tau, kFixedCap, fix_key, fix_id, counts);
+                knn_tc_select_kernel<16><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, row_flags);
+            }
+            B200_CUDA(cudaGetLastError());
+            knn_tc_tau_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(fix_key, fix_id, kFixedCap, rank_b, row_flags, nq, tau);
+            B200_CUDA(cudaGetLastError());
+        }
+        if (EPL == 8) {
+            B200_KNN_FILTER(8, true, 1, tau, kFixedCap, fix_key, fix_id, counts);
+            knn_tc_select_kernel<8><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, row_flags);
+        } else {
+            B200_KNN_FILTER(16, true, 1, tau, kFixedCap, fix_key, fix_id, counts);
+            knn_tc_select_kernel<16><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, row_flags);
+        }
         B200_CUDA(cudaGetLastError());
-        if (EPL == 8) B200_KNN_FILTER(8, true, 1, tau, kFixedCap, fix_key, fix_id, row_flags);
-        else B200_KNN_FILTER(16, true, 1, tau, kFixedCap, fix_key, fix_id, row_flags);
         final_key = fix_key;
         final_id = fix_id;
         final_stride = kFixedCap;

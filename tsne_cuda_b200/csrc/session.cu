@@ -54,6 +54,8 @@ int Session::init(int64_t N_, int K_, int64_t lo, int64_t hi, int device_)
     if (N_ >= (int64_t)1 << 31) { set_error("session: more than 2^31-1 points are not supported (int32 ids)"); return -4; }
     N = N_; K = K_; row_lo = lo; row_hi = hi; device = device_;
     B200_CUDA(cudaSetDevice(device));
+    // (Stream priorities were measured both ways and change nothing: the attractive kernel and the grid
+    // pipeline compete for the same load/store units rather than for block slots.)
     B200_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
     B200_CUDA(cudaStreamCreateWithFlags(&stream2, cudaStreamNonBlocking));
     B200_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
