@@ -41,9 +41,9 @@ def test_knn_tensor_core_paths(engine, oracle_cpu, n, d, k):
 
 def test_knn_tensor_core_matches_simt_everywhere(engine, monkeypatch):
     X = mixture(9000, 40, 12)
-    X[100:140] = X[100]                      # a clump of identical points: ties the proof cannot certify
+    X[100:300] = X[100]                      # 200 identical points: more ties than candidates, the proof cannot close
     a = engine.knn(X, 60)
-    assert engine.knn_last_stats()["tensor_core"] == 1 and engine.knn_last_stats()["rows_recomputed"] >= 40
+    assert engine.knn_last_stats()["tensor_core"] == 1 and engine.knn_last_stats()["rows_recomputed"] >= 200
     monkeypatch.setenv("B200TSNE_KNN", "simt")
     b = engine.knn(X, 60)
     assert engine.knn_last_stats()["tensor_core"] == 0
