@@ -109,7 +109,9 @@ def run_ours(args):
     N, D = X.shape
     K = hp["num_neighbors"]
     lo, hi = distributed.shard_rows(N, world, rank)
+    t0 = time.time()
     s = distributed.open_session(N, K, rank, local_rank, world)
+    open_s = time.time() - t0
     t0 = time.time()
     s.affinities_from_points(X, hp["perplexity"], 1e-3)
     setup_s = time.time() - t0
@@ -164,7 +166,7 @@ def run_ours(args):
                                   (args.config, N, D, K, hp["perplexity"]),
                       "l2_policy": "inputs larger than L2 (P+ids = %.0f MB per iteration)" % (8.0 * N * K / 1e6),
                       "parallelism": "points sharded over %d GPU(s)" % world},
-           "gpu_launches": int(launches), "setup_s": setup_s, "stage_us_per_iteration": stage_us,
+           "gpu_launches": int(launches), "setup_s": setup_s, "open_session_s": open_s, "stage_us_per_iteration": stage_us,
            "roofline": roof, "clocks": clk.summary()}
 
     if rank == 0 and not multi and not args.no_e2e:
@@ -174,6 +176,7 @@ def run_ours(args):
     if rank == 0 and not multi and not args.no_cpu:
         out["cpu_baseline"] = cpu_baseline(X, hp, Y0, args)
     if multi:
+        distributed.release_communicators()
         dist.destroy_process_group()
     return out if rank == 0 else None
 
@@ -306,9 +309,19 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    # Libraries (NCCL's version banner for one) write to file descriptor 1; the contract is ONE JSON
+    # line on stdout, so everything written during the run goes to stderr instead.
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
     if out is not None:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
 
 
 if __name__ == "__main__":

@@ -200,9 +200,13 @@ const char *b200tsne_stage_name(int stage);
 int64_t b200tsne_session_launch_count(b200tsne_session *s);
 
 /* Multi-GPU: attach an NCCL communicator created from a unique id that rank 0 obtained from
- * b200tsne_comm_unique_id (128 bytes) and distributed to all ranks by any means. */
+ * b200tsne_comm_unique_id (128 bytes) and distributed to all ranks by any means.  Creating a
+ * communicator takes seconds, so the library keeps it for the life of the process: a later session
+ * attached with the same (id, rank, world_size) shares it.  b200tsne_comm_release_all destroys
+ * the cached communicators; every session that used one must have been destroyed before. */
 int b200tsne_comm_unique_id(void *id128);
 int b200tsne_session_attach_comm(b200tsne_session *s, const void *id128, int rank, int world_size);
+void b200tsne_comm_release_all(void);
 
 #ifdef __cplusplus
 }

@@ -69,6 +69,7 @@ SIGNATURES = {
     "b200tsne_session_launch_count": (_i64, [C.c_void_p]),
     "b200tsne_comm_unique_id": (C.c_int, [C.c_void_p]),
     "b200tsne_session_attach_comm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "b200tsne_comm_release_all": (None, []),
 }
 for _name, (_res, _args) in SIGNATURES.items():
     _fn = getattr(lib, _name)
@@ -280,3 +281,8 @@ def comm_unique_id():
     buf = C.create_string_buffer(128)
     check(lib.b200tsne_comm_unique_id(buf))
     return buf.raw
+
+
+def comm_release_all():
+    """Destroy the communicators the library cached (every session that used one must be closed)."""
+    lib.b200tsne_comm_release_all()

@@ -377,7 +377,9 @@ int b200tsne_session_attach_comm(b200tsne_session *h, const void *id128, int ran
         return B200TSNE_ERR_INVALID;
     }
     B200_CUDA(cudaSetDevice(s.device));
-    return comm_create(&s.comm, id128, rank, world_size);
+    return comm_acquire(&s.comm, id128, rank, world_size);
 }
+
+void b200tsne_comm_release_all(void) { comm_release_all(); }
 
 }  // extern "C"

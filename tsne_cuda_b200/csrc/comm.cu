@@ -1,8 +1,11 @@
 #include "comm.h"
 
 #include <dlfcn.h>
+#include <string.h>
 
+#include <mutex>
 #include <string>
+#include <vector>
 
 #include "common.cuh"
 
@@ -92,19 +95,39 @@ int comm_unique_id(void *id128)
     return 0;
 }
 
-int comm_create(Comm **out, const void *id128, int rank, int world)
+// Creating a communicator costs seconds (bootstrap, topology search, channel set-up), a session a few
+// milliseconds, so communicators are kept for the life of the process: a second session attached
+// with the same (unique id, rank, world size) gets the communicator of the first.
+namespace {
+struct Cached { nccl_unique_id id; Comm *comm; };
+std::mutex g_cache_mutex;
+std::vector<Cached> g_cache;
+}  // namespace
+
+int comm_acquire(Comm **out, const void *id128, int rank, int world)
 {
     Api *a = api();
     if (!a) return -5;
-    if (world < 1 || rank < 0 || rank >= world) { set_error("comm_create: bad rank/world_size"); return -1; }
+    if (world < 1 || rank < 0 || rank >= world) { set_error("comm_acquire: bad rank/world_size"); return -1; }
     nccl_unique_id id = *reinterpret_cast<const nccl_unique_id *>(id128);
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    for (const Cached &c : g_cache)
+        if (memcmp(&c.id, &id, sizeof(id)) == 0 && c.comm->rank == rank && c.comm->world == world) { *out = c.comm; return 0; }
     Comm *c = new Comm();
     c->rank = rank;
     c->world = world;
     int rc = a->comm_init_rank(&c->nccl, world, id, rank);
     if (rc != 0) { delete c; return nccl_fail(rc, "ncclCommInitRank"); }
+    g_cache.push_back({id, c});
     *out = c;
     return 0;
+}
+
+void comm_release_all()
+{
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    for (Cached &c : g_cache) { c.comm->destroy(); delete c.comm; }
+    g_cache.clear();
 }
 
 void Comm::destroy()

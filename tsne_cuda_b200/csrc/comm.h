@@ -22,6 +22,9 @@ struct Comm {
 };
 
 int comm_unique_id(void *id128);
-int comm_create(Comm **out, const void *id128, int rank, int world);
+// The communicator for (id, rank, world): created on first use, owned by a process-wide cache and
+// shared by later sessions; comm_release_all destroys them (no session may still be using one).
+int comm_acquire(Comm **out, const void *id128, int rank, int world);
+void comm_release_all();
 
 }  // namespace b200

@@ -102,7 +102,7 @@ void Session::destroy()
     cudaSetDevice(device);
     if (stream) cudaStreamSynchronize(stream);
     if (stream2) cudaStreamSynchronize(stream2);
-    if (comm) { comm->destroy(); delete comm; comm = nullptr; }
+    comm = nullptr;  // owned by the communicator cache (comm.h)
     arena.release();
     if (h_state) cudaFreeHost(h_state);
     if (ev_fork) cudaEventDestroy(ev_fork);
@@ -299,11 +299,17 @@ int Session::affinities_from_points(const float *X_host, int D, float perplexity
     B200_CUDA(cudaMemcpyAsync(X, X_host, sizeof(float) * N * D, cudaMemcpyHostToDevice, stream));
     B200_TRY(tmp.alloc((void **)&d2, sizeof(float) * std::max<int64_t>(chunk, 1) * K));
     B200_TRY(tmp.alloc((void **)&max_enc, sizeof(unsigned int)));
-    if (!multi) {
+    // Every rank holds all the points.  By default the QUERIES are sharded: a rank searches its own
+    // rows against the whole database and needs no exchange, and its cost falls as 1/world (the
+    // search costs about the same per query whatever the database size).  B200TSNE_KNN_SHARD=database
+    // shards the DATABASE instead, as a deployment whose points do not fit one GPU would: every rank
+    // searches all queries against its own rows, and the owners of the query rows receive the
+    // partial lists (all-to-all) and merge them.  Both give the same lists bit for bit.
+    const char *shard_env = getenv("B200TSNE_KNN_SHARD");
+    const bool db_sharded = multi && shard_env && strcmp(shard_env, "database") == 0;
+    if (!db_sharded) {
         B200_TRY(knn_search(X, N, D, K, row_lo, row_hi, 0, N, ids, d2, &knn_stats, stream));
     } else {
-        // database sharded by rows: every rank searches all queries against its own rows, the
-        // owners of the query rows receive the partial lists and merge them
         int32_t *part_i = nullptr, *recv_i = nullptr;
         float *part_d = nullptr, *recv_d = nullptr;
         B200_TRY(tmp.alloc((void **)&part_i, sizeof(int32_t) * npad * K));

@@ -4,9 +4,11 @@ only; the data-path collectives are NCCL calls issued by libtsnecuda.so on its o
 Sharding: rank r owns the contiguous rows [r*ceil(N/W), min(N, (r+1)*ceil(N/W))) of the points,
 of the fixed-width P, of gains and momentum, and produces those rows of the new embedding.  The
 embedding and the 390x390x4 grid are replicated.  Per iteration: all-reduce of the grid after the
-spread, all-reduce of sum Z_i after the gather, all-gather of the updated rows.  Set-up: database-
-sharded exact kNN with an all-to-all of the partial lists and a merge, max-distance all-reduce,
-all-gather of ids and conditional p for the symmetrisation.
+spread, all-reduce of sum Z_i after the gather, all-gather of the updated rows.  Set-up: exact kNN of the
+owned rows against all points (queries sharded, no exchange; B200TSNE_KNN_SHARD=database shards
+the database instead: every rank searches all queries against its own rows, then an all-to-all
+of the partial lists and a merge), max-distance all-reduce, all-gather of ids and conditional p
+for the symmetrisation.
 """
 import os
 
@@ -38,12 +40,27 @@ def share_unique_id(make_id, rank, world):
     return bytes(t.cpu().numpy().tobytes())
 
 
+_unique_ids = {}   # (rank, world) -> the id this process already built a communicator from
+
+
 def open_session(n, k, rank, local_rank, world):
-    """Session owning this rank's rows, with the NCCL communicator attached when world > 1."""
+    """Session owning this rank's rows, with the NCCL communicator attached when world > 1.  The
+    first call of a process creates the communicator (seconds, collective over all ranks); later
+    calls with the same rank and world size reuse it, as the library caches it by unique id."""
     from . import _lib
     lo, hi = shard_rows(n, world, rank)
     s = _lib.Session(n, k, lo, hi, device=local_rank)
     if world > 1:
-        uid = share_unique_id(_lib.comm_unique_id, rank, world)
-        s.attach_comm(uid, rank, world)
+        key = (rank, world)
+        if key not in _unique_ids:
+            _unique_ids[key] = share_unique_id(_lib.comm_unique_id, rank, world)
+        s.attach_comm(_unique_ids[key], rank, world)
     return s
+
+
+def release_communicators():
+    """Destroy the cached communicators (call once all sessions are closed, before the process
+    group is torn down)."""
+    from . import _lib
+    _unique_ids.clear()
+    _lib.comm_release_all()
