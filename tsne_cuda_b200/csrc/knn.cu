@@ -94,8 +94,16 @@ __device__ __forceinline__ void warp_insert(volatile float *ld, volatile int32_t
 __global__ void __launch_bounds__(kThreads, 2)
 knn_exact_kernel(const float *__restrict__ XT, long long N, int D, int K, long long q_lo, long long nq,
                  const int *__restrict__ q_index, long long out_base, long long db_lo, long long db_hi, int32_t *ids,
-                 float *d2)
+                 float *d2, long long slice_step, long long slice_out_stride)
 {
+    // slice_step > 0: block row y searches the database slice [db_lo + y * slice_step, ... + slice_step) and
+    // writes its lists slice_out_stride elements after those of row y - 1
+    if (slice_step > 0) {
+        db_lo += (long long)blockIdx.y * slice_step;
+        db_hi = min(db_hi, db_lo + slice_step);
+        ids += (long long)blockIdx.y * slice_out_stride;
+        d2 += (long long)blockIdx.y * slice_out_stride;
+    }
     extern __shared__ __align__(16) float sm[];
     float *Qs = sm;                          // [DCH][BQ]
     float *Ps = Qs + DCH * BQ;               // [DCH][BP]
@@ -220,6 +228,52 @@ __global__ void knn_merge_kernel(const int32_t *__restrict__ ids_parts, const fl
     }
 }
 
+// The same merge for many short lists (up to 1024 parts): one warp per row, lane l owns the parts
+// l, l + 32, ...; every round each lane offers the best head among its parts and the warp takes the
+// smallest offer by (distance, id).
+__global__ void __launch_bounds__(128)
+knn_merge_many_kernel(const int32_t *__restrict__ ids_parts, const float *__restrict__ d2_parts, int parts,
+                      long long part_stride, long long n_rows, int K, const int *__restrict__ row_index, long long out_base,
+                      int32_t *__restrict__ ids, float *__restrict__ d2)
+{
+    const int lane = threadIdx.x & 31;
+    const long long r = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const long long orow = row_index ? (row_index[r] - out_base) : r;
+    int head[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) head[j] = 0;
+    for (int s = 0; s < K; s++) {
+        float bd = INFINITY;
+        int bi = INT_MAX, bj = -1;
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const int p = lane + 32 * j;
+            if (p < parts && head[j] < K) {
+                const long long o = (long long)p * part_stride + r * K + head[j];
+                const float cd = d2_parts[o];
+                const int ci = ids_parts[o];
+                if (cd < bd || (cd == bd && ci < bi)) { bd = cd; bi = ci; bj = j; }
+            }
+        }
+        float wd = bd;
+        int wi = bi;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float od = __shfl_xor_sync(0xffffffffu, wd, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+            if (od < wd || (od == wd && oi < wi)) { wd = od; wi = oi; }
+        }
+        // ids are unique across the parts (disjoint database slices), so exactly one lane holds the winner
+        if (bj >= 0 && bd == wd && bi == wi) {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (j == bj) head[j]++;
+        }
+        if (lane == 0) { ids[orow * K + s] = wi; d2[orow * K + s] = wd; }
+    }
+}
+
 constexpr size_t kKnnSmem = sizeof(float) * (DCH * BQ + DCH * BP + BQ * DSTR + BQ) + sizeof(int) * 2 * BQ;
 
 __global__ void knn_init_rows_kernel(int32_t *ids, float *d2, const int *__restrict__ q_index, long long nq, long long out_base, int K)
@@ -271,7 +325,7 @@ int launch_knn_exact(const float *XT, int64_t N, int D, int K, int64_t q_lo, int
     B200_CUDA(cudaGetLastError());
     B200_CUDA(cudaFuncSetAttribute(knn_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKnnSmem));
     knn_exact_kernel<<<(unsigned)((nq + BQ - 1) / BQ), kThreads, kKnnSmem, st>>>(XT, N, D, K, q_lo, nq, nullptr, q_lo, db_lo, db_hi,
-                                                                                 ids, d2);
+                                                                                 ids, d2, 0, 0);
     B200_CUDA(cudaGetLastError());
     return 0;
 }
@@ -287,33 +341,37 @@ int launch_knn_exact_rows(const float *XT, int64_t N, int D, int K, const int *q
     B200_CUDA(cudaGetLastError());
     B200_CUDA(cudaFuncSetAttribute(knn_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKnnSmem));
     knn_exact_kernel<<<(unsigned)((nq + BQ - 1) / BQ), kThreads, kKnnSmem, st>>>(XT, N, D, K, 0, nq, q_index, out_base, db_lo, db_hi,
-                                                                                 ids, d2);
+                                                                                 ids, d2, 0, 0);
     B200_CUDA(cudaGetLastError());
     return 0;
 }
 
 
 // SIMT search for a short list of rows.  A block serves 64 queries against the whole database, so a handful
-// of rows would occupy a handful of SMs for the whole scan: the database is cut into up to 16 slices searched
-// by separate blocks, and the partial lists are merged.
+// of rows would occupy a handful of SMs for the whole scan: the database is cut into slices searched by
+// the block rows of one launch (enough of them to fill the GPU four times over), and the partial lists
+// are merged.
 static int knn_exact_few_rows(const float *XT, int64_t N, int D, int K, const int *rows, int64_t n_rows, int64_t out_base,
                               int64_t db_lo, int64_t db_hi, int32_t *ids, float *d2, DeviceArena &tmp, cudaStream_t st)
 {
     const int64_t span = db_hi - db_lo;
-    const int slices = (int)std::max<int64_t>(1, std::min<int64_t>(16, span / 8192));
-    if (slices == 1 || n_rows > 16384)
+    const int64_t q_blocks = (n_rows + BQ - 1) / BQ;
+    const int slices = (int)std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(span / 2048, 1024), 592 / q_blocks));
+    if (slices == 1)
         return launch_knn_exact_rows(XT, N, D, K, rows, n_rows, out_base, db_lo, db_hi, ids, d2, st);
     int32_t *pi = nullptr;
     float *pd = nullptr;
-    B200_TRY(tmp.alloc((void **)&pi, sizeof(int32_t) * (size_t)slices * n_rows * K));
-    B200_TRY(tmp.alloc((void **)&pd, sizeof(float) * (size_t)slices * n_rows * K));
+    const long long per_slice = (long long)n_rows * K;
+    B200_TRY(tmp.alloc((void **)&pi, sizeof(int32_t) * (size_t)slices * per_slice));
+    B200_TRY(tmp.alloc((void **)&pd, sizeof(float) * (size_t)slices * per_slice));
     const int64_t step = (span + slices - 1) / slices;
-    for (int s = 0; s < slices; s++) {
-        const int64_t lo = db_lo + s * step, hi = std::min(db_hi, lo + step);
-        B200_TRY(launch_knn_exact_rows(XT, N, D, K, rows, n_rows, -1, lo, hi, pi + (size_t)s * n_rows * K,
-                                       pd + (size_t)s * n_rows * K, st));
-    }
-    knn_merge_kernel<<<(unsigned)((n_rows + 127) / 128), 128, 0, st>>>(pi, pd, slices, n_rows * K, n_rows, K, rows, out_base, ids, d2);
+    knn_init_kernel<<<(unsigned)((slices * per_slice + 255) / 256), 256, 0, st>>>(pi, pd, slices * per_slice);
+    B200_CUDA(cudaGetLastError());
+    B200_CUDA(cudaFuncSetAttribute(knn_exact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKnnSmem));
+    knn_exact_kernel<<<dim3((unsigned)q_blocks, (unsigned)slices), kThreads, kKnnSmem, st>>>(XT, N, D, K, 0, n_rows, rows, -1, db_lo, db_hi,
+                                                                                            pi, pd, step, per_slice);
+    B200_CUDA(cudaGetLastError());
+    knn_merge_many_kernel<<<(unsigned)((n_rows + 3) / 4), 128, 0, st>>>(pi, pd, slices, per_slice, n_rows, K, rows, out_base, ids, d2);
     B200_CUDA(cudaGetLastError());
     return 0;
 }

@@ -40,10 +40,14 @@
 // min operations); only if that minimum beats the threshold, which becomes rare as the scan
 // proceeds, does it locate and append the survivors.
 //
-// Warp roles (320 threads): warps 0-7 epilogue in two groups of four (TMEM lane quarter = warp % 4),
-// warp 8 bulk-copy producer, warp 9 MMA issuer and TMEM owner.  Two B stages and two accumulator buffers, so the MMAs
-// of tile t+1 overlap the epilogue of tile t.  Every wait has a time limit; on expiry the kernel sets
-// an error flag, drains and frees its TMEM.
+// Warp roles: a block serves QH = 2 query tiles (256 queries; 1 when the operand images are too wide for
+// that) against every database tile, so a database image is fetched from L2 once per 256 queries.
+// Warps 0 .. 8 QH - 1 are the epilogue, in 2 QH groups of four (TMEM lane quarter = warp % 4), then the
+// bulk-copy producer warp and the MMA issuer / TMEM owner warp.  Two database stages and two accumulator
+// buffers (of QH tiles each), so the MMAs of tile t+1 overlap the epilogue of tile t.  Measured on the
+// full pass at N = 10^6, D = 50: with the epilogue's comparisons removed the kernel takes 89 % of its
+// time, i.e. it is bound by the tensor pipe (42 MMAs 128x128x8 per tile pair at ~105 cycles each).
+// Every wait has a time limit; on expiry the kernel sets an error flag, drains and frees its TMEM.
 #include <limits.h>
 #include <string.h>
 
@@ -58,9 +62,11 @@ constexpr int TM = 128;             // queries per block = accumulator rows = TM
 constexpr int TN = 128;             // database points per tile = accumulator columns
 constexpr int kBStages = 2;
 constexpr int kAccBufs = 2;
-constexpr int kTcThreads = 320;      // 8 epilogue warps (two groups of four), producer warp, MMA warp
-constexpr int kProducerWarp = 8, kMmaWarp = 9;
-constexpr uint32_t kTmemCols = 256;  // kAccBufs * TN
+// A block serves QH query tiles (QH = 2 when two query images and two database stages fit in shared
+// memory, else 1): every database tile is multiplied with each of them, so the database image is read
+// from L2 once per 128 * QH queries.  8 * QH epilogue warps, then the producer warp and the MMA warp;
+// TMEM columns = kAccBufs * QH * TN.
+constexpr int tc_threads(int QH) { return (8 * QH + 2) * 32; }
 
 // ------------------------------------------------------------------------------------------------
 // PTX helpers
@@ -159,6 +165,14 @@ __device__ __forceinline__ void tc_ld32_wait(uint32_t (&r)[32])
                    "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
                  :
                  : "memory");
+}
+
+// three-input minimum (one instruction on sm_100)
+__device__ __forceinline__ float min3(float a, float b, float c)
+{
+    float d;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 // Shared-memory matrix descriptor, K-major, no swizzle: core matrices of 8 rows x 16 bytes, the two
@@ -320,8 +334,6 @@ struct TcShared {
     uint64_t acc_empty[kAccBufs];
     uint32_t tmem_base;
     int abort_flag;
-    int cnt[2][TM];       // candidates appended per epilogue group and query
-    int overflow[2][TM];
 };
 
 // img_q / img_db: tile images of all points (query form, database form); query tiles [qt_lo, qt_hi), database tiles [dt_lo, dt_hi); only
@@ -332,8 +344,8 @@ struct TcShared {
 // tile_stride, ...   FIXED = true: threshold tau[query] fixed, buffers of `cap` entries (row stride of
 // cand_key / cand_id in both modes, two halves per query); counts[2*query + group] receives the number of
 // entries each epilogue group appended (bit 30 set if its half overflowed); knn_tc_select_kernel finishes.
-template <int EPL, bool FIXED>
-__global__ void __launch_bounds__(kTcThreads, 1)
+template <int EPL, bool FIXED, int QH>
+__global__ void __launch_bounds__(tc_threads(QH), 1)
 knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int Dp, long long qt_lo,
                      long long dt_lo, long long dt_hi, int tile_stride, long long q_lo, long long q_hi, long long db_lo,
                      long long db_hi, const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id,
@@ -341,21 +353,23 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
 {
     constexpr int C = 32 * EPL;   // capacity handled by one compaction
     constexpr int L = 16 * EPL;
-    extern __shared__ __align__(1024) unsigned char smem[];
+    constexpr int kProducerWarp = 8 * QH, kMmaWarp = 8 * QH + 1;
+    constexpr uint32_t kTmemCols = kAccBufs * QH * TN;
+    extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) TcShared sh;
     const uint32_t image_bytes = (uint32_t)Dp * 1024u;        // hi + lo
-    float *sA = reinterpret_cast<float *>(smem);
-    float *sB = reinterpret_cast<float *>(smem + image_bytes);  // [kBStages] images
+    float *sA = reinterpret_cast<float *>(smem);                          // [QH] images
+    float *sB = reinterpret_cast<float *>(smem + QH * image_bytes);       // [kBStages] images
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nks = Dp >> 3;
-    const long long qt = qt_lo + blockIdx.x;
+    const long long qt = qt_lo + (long long)blockIdx.x * QH;   // first query tile of the block
     const long long n_tiles = (dt_hi - dt_lo + tile_stride - 1) / tile_stride;
     volatile int *abort_flag = &sh.abort_flag;
 
     if (threadIdx.x == 0) {
         mbar_init(&sh.full_a, 1);
         for (int s = 0; s < kBStages; s++) { mbar_init(&sh.full_b[s], 1); mbar_init(&sh.empty_b[s], 1); }
-        for (int b = 0; b < kAccBufs; b++) { mbar_init(&sh.acc_full[b], 1); mbar_init(&sh.acc_empty[b], 4); }
+        for (int b = 0; b < kAccBufs; b++) { mbar_init(&sh.acc_full[b], 1); mbar_init(&sh.acc_empty[b], 4 * QH); }
         sh.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -374,8 +388,11 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
     if (warp == kProducerWarp) {
         // ---------------- producer: one bulk copy per tile image ----------------
         if (lane == 0) {
-            mbar_expect_tx(&sh.full_a, image_bytes);
-            bulk_load(sA, img_q + (size_t)qt * (image_bytes / 4), image_bytes, &sh.full_a);
+            // the images of the block's QH query tiles are adjacent (the image array is padded to a
+            // multiple of QH tiles)
+            mbar_expect_tx(&sh.full_a, QH * image_bytes);
+            for (int h = 0; h < QH; h++)
+                bulk_load(sA + (size_t)h * (image_bytes / 4), img_q + (size_t)(qt + h) * (image_bytes / 4), image_bytes, &sh.full_a);
             for (long long t = 0; t < n_tiles; t++) {
                 const int s = (int)(t % kBStages);
                 const uint32_t ph = (uint32_t)((t / kBStages) & 1);
@@ -389,7 +406,6 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             bool ok = mbar_wait(&sh.full_a, 0, abort_flag);
-            const uint32_t a_hi = smem_u32(sA), a_lo = a_hi + (uint32_t)nks * 4096u;
             for (long long t = 0; ok && t < n_tiles; t++) {
                 const int s = (int)(t % kBStages), b = (int)(t % kAccBufs);
                 const uint32_t ph_s = (uint32_t)((t / kBStages) & 1), ph_b = (uint32_t)((t / kAccBufs) & 1);
@@ -397,52 +413,59 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
                 if (!mbar_wait(&sh.full_b[s], ph_s, abort_flag)) break;
                 tc_fence_after();
                 const uint32_t b_hi = smem_u32(sB + (size_t)s * (image_bytes / 4)), b_lo = b_hi + (uint32_t)nks * 4096u;
-                const uint32_t d_tmem = tmem_base + (uint32_t)b * TN;
-                uint32_t acc = 0;
-                for (int ks = 0; ks < nks; ks++) {      // hi . hi
-                    tc_mma_tf32(d_tmem, make_desc(a_hi + ks * 4096u), make_desc(b_hi + ks * 4096u), kInstrDesc, acc);
-                    acc = 1;
+#pragma unroll 1
+                for (int h = 0; h < QH; h++) {
+                    const uint32_t a_hi = smem_u32(sA) + (uint32_t)h * image_bytes, a_lo = a_hi + (uint32_t)nks * 4096u;
+                    const uint32_t d_tmem = tmem_base + (uint32_t)((b * QH + h) * TN);
+                    uint32_t acc = 0;
+                    for (int ks = 0; ks < nks; ks++) {      // hi . hi
+                        tc_mma_tf32(d_tmem, make_desc(a_hi + ks * 4096u), make_desc(b_hi + ks * 4096u), kInstrDesc, acc);
+                        acc = 1;
+                    }
+                    for (int ks = 0; ks < nks; ks++)        // lo . hi
+                        tc_mma_tf32(d_tmem, make_desc(a_lo + ks * 4096u), make_desc(b_hi + ks * 4096u), kInstrDesc, 1);
+                    for (int ks = 0; ks < nks; ks++)        // hi . lo
+                        tc_mma_tf32(d_tmem, make_desc(a_hi + ks * 4096u), make_desc(b_lo + ks * 4096u), kInstrDesc, 1);
                 }
-                for (int ks = 0; ks < nks; ks++)        // lo . hi
-                    tc_mma_tf32(d_tmem, make_desc(a_lo + ks * 4096u), make_desc(b_hi + ks * 4096u), kInstrDesc, 1);
-                for (int ks = 0; ks < nks; ks++)        // hi . lo
-                    tc_mma_tf32(d_tmem, make_desc(a_hi + ks * 4096u), make_desc(b_lo + ks * 4096u), kInstrDesc, 1);
                 tc_commit(&sh.empty_b[s]);    // the stage may be refilled once these MMAs have read it
-                tc_commit(&sh.acc_full[b]);   // the accumulator tile is complete
+                tc_commit(&sh.acc_full[b]);   // the accumulator tiles are complete
             }
         }
     } else {
         // ---------------- epilogue: one query per thread ----------------
-        // Two groups of four warps; a warp reaches the TMEM lane quarter (warp % 4).  With a fixed
-        // threshold group g takes the tiles t = g, g+2, ... (always accumulator buffer g) and appends
-        // to its own half of the query's buffer, so the groups share nothing; with the online threshold
-        // (per-query state that cannot be shared) only group 0 works.
+        // 2 * QH groups of four warps; a warp reaches the TMEM lane quarter (warp % 4).  Group g belongs to
+        // query tile g % QH of the block.  With a fixed threshold it takes the database tiles
+        // t = buf, buf + 2, ... (buf = g / QH, always accumulator buffer buf) and appends to segment buf of
+        // the query's candidate buffer, so the groups share nothing; with the online threshold (per-query
+        // state that cannot be shared) only the groups with buf = 0 work, on every tile.
         const int group = warp >> 2, quarter = warp & 3;
-        const int n_groups = FIXED ? 2 : 1;
-        const int my_cap = FIXED ? cap / 2 : cap;
+        const int buf = group / QH, half = group % QH;
+        const bool active = FIXED || buf == 0;
+        const int seg_cap = FIXED ? cap / kAccBufs : cap;
         const int row = quarter * 32 + lane;                    // TMEM lane
-        const long long gq = qt * TM + row;
-        const bool serve = gq >= q_lo && gq < q_hi && group < n_groups;
-        float *bk = cand_key + (serve ? (gq - q_lo) : 0) * cap + group * my_cap;
-        int32_t *bi = cand_id + (serve ? (gq - q_lo) : 0) * cap + group * my_cap;
+        const long long gq = (qt + half) * TM + row;
+        const bool serve = gq >= q_lo && gq < q_hi && active;
+        float *bk = cand_key + (serve ? (gq - q_lo) : 0) * cap + (FIXED ? buf * seg_cap : 0);
+        int32_t *bi = cand_id + (serve ? (gq - q_lo) : 0) * cap + (FIXED ? buf * seg_cap : 0);
         float thr = serve ? (FIXED ? tau[gq - q_lo] : INFINITY) : -INFINITY;
         int cnt = 0;
         bool overflow = false;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * TN);
 
         // One chunk = 32 accumulator columns = 32 keys of this thread's query.  Fast path: a tree of
-        // independent min operations and one comparison.  Only if the minimum beats the threshold (rare
-        // once the scan is under way) are the quarters whose minimum does so compared element by element;
-        // everything is indexed statically, so the keys never leave the registers.
+        // independent three-input min operations and one comparison.  Only if the minimum beats the
+        // threshold (rare once the scan is under way) are the quarters whose minimum does so compared
+        // element by element; everything is indexed statically, so the keys never leave the registers.
         auto process_chunk = [&](const uint32_t (&r)[32], long long col0, bool tile_inside) {
-            float m16[16], m8[8], m4[4];
+            float m4[4];
 #pragma unroll
-            for (int k = 0; k < 16; k++) m16[k] = fminf(__uint_as_float(r[2 * k]), __uint_as_float(r[2 * k + 1]));
-#pragma unroll
-            for (int k = 0; k < 8; k++) m8[k] = fminf(m16[2 * k], m16[2 * k + 1]);
-#pragma unroll
-            for (int k = 0; k < 4; k++) m4[k] = fminf(m8[2 * k], m8[2 * k + 1]);
-            const float mn = fminf(fminf(m4[0], m4[1]), fminf(m4[2], m4[3]));
+            for (int q = 0; q < 4; q++) {
+                const float a = min3(__uint_as_float(r[8 * q]), __uint_as_float(r[8 * q + 1]), __uint_as_float(r[8 * q + 2]));
+                const float b = min3(__uint_as_float(r[8 * q + 3]), __uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
+                const float c = fminf(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+                m4[q] = min3(a, b, c);
+            }
+            const float mn = fminf(min3(m4[0], m4[1], m4[2]), m4[3]);
             if (mn < thr) {
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
@@ -464,14 +487,14 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
             }
             if (FIXED) {
                 // a chunk appends at most 32 entries: stop a buffer that could overflow in the next one
-                if (cnt > my_cap - 32) { overflow = true; thr = -INFINITY; }
+                if (cnt > seg_cap - 32) { overflow = true; thr = -INFINITY; }
             } else {
                 // a chunk appends at most 32 entries: compact every buffer that could overflow in the next one
                 unsigned full = __ballot_sync(0xffffffffu, cnt > C - 32);
                 while (full) {
                     const int owner = __ffs(full) - 1;
                     full &= full - 1;
-                    const long long oq = qt * TM + quarter * 32 + owner - q_lo;
+                    const long long oq = (qt + half) * TM + quarter * 32 + owner - q_lo;
                     const int n = __shfl_sync(0xffffffffu, cnt, owner);
                     const float nt = warp_compact<EPL>(cand_key + oq * cap, cand_id + oq * cap, n, lane);
                     if (lane == owner) { thr = nt; cnt = L; }
@@ -479,14 +502,14 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
             }
         };
 
-        for (long long t = group; t < n_tiles && group < n_groups; t += n_groups) {
+        for (long long t = FIXED ? buf : 0; t < n_tiles && active; t += FIXED ? kAccBufs : 1) {
             const int b = (int)(t % kAccBufs);
             const uint32_t ph_b = (uint32_t)((t / kAccBufs) & 1);
             if (!mbar_wait(&sh.acc_full[b], ph_b, abort_flag, 32)) break;
             tc_fence_after();
             const long long p0 = (dt_lo + t * tile_stride) * TN;
             const bool inside = p0 >= db_lo && p0 + TN <= db_hi;
-            const uint32_t tcol = lane_base + (uint32_t)(b * TN);
+            const uint32_t tcol = lane_base + (uint32_t)(b * QH * TN);
             // one copy of the chunk code, executed four times: the epilogue is issue- and
             // instruction-fetch-bound, so small code beats overlapping the (fast) TMEM reads
 #pragma unroll 1
@@ -502,28 +525,20 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
                 process_chunk(r, p0 + c0, inside);
             }
         }
-        if (group < n_groups) { sh.cnt[group][row] = cnt; sh.overflow[group][row] = overflow ? 1 : 0; }
-    }
-    __syncthreads();   // every tile has been compared (or the block has given up)
-    if (FIXED) {
-        // The final selection is a separate kernel (one warp per query, thousands in flight): it is a chain of
-        // dependent global round trips, which eight warps of this block would walk through one query at a time.
-        if (threadIdx.x < 2 * TM) {
-            const int g = threadIdx.x / TM, r = threadIdx.x % TM;
-            const long long gq2 = qt * TM + r;
-            if (gq2 >= q_lo && gq2 < q_hi) counts[(gq2 - q_lo) * 2 + g] = sh.cnt[g][r] | (sh.overflow[g][r] ? 0x40000000 : 0);
-        }
-    } else if (warp < 4) {
-        // online threshold (small databases): one last compaction leaves the L best, sorted, in front
-        const int quarter = warp & 3;
-        const long long gq_lane = qt * TM + quarter * 32 + lane;
-        unsigned m = __ballot_sync(0xffffffffu, gq_lane >= q_lo && gq_lane < q_hi);
-        while (m) {
-            const int owner = __ffs(m) - 1;
-            m &= m - 1;
-            const int orow = quarter * 32 + owner;
-            const long long oq = qt * TM + orow - q_lo;
-            (void)warp_compact<EPL>(cand_key + oq * cap, cand_id + oq * cap, min(sh.cnt[0][orow], C), lane);
+        if (FIXED) {
+            // The final selection is a separate kernel (one warp per query, thousands in flight): it is a chain of
+            // dependent global round trips, which the warps of this block would walk through one query at a time.
+            if (serve) counts[(gq - q_lo) * kAccBufs + buf] = cnt | (overflow ? 0x40000000 : 0);
+        } else if (active) {
+            // online threshold (small databases): one last compaction leaves the L best, sorted, in front
+            unsigned m = __ballot_sync(0xffffffffu, serve);
+            while (m) {
+                const int owner = __ffs(m) - 1;
+                m &= m - 1;
+                const long long oq = (qt + half) * TM + quarter * 32 + owner - q_lo;
+                const int n = __shfl_sync(0xffffffffu, cnt, owner);
+                (void)warp_compact<EPL>(cand_key + oq * cap, cand_id + oq * cap, min(n, C), lane);
+            }
         }
     }
     // ---------------- teardown ----------------
@@ -785,13 +800,13 @@ constexpr long long kTwoPassMinTiles = 512;   // below this many database tiles 
 size_t knn_tc_workspace_bytes(int64_t N, int D, int K, int64_t nq)
 {
     const int Dp = (D + 1 + 7) / 8 * 8;   // one extra inner column carries the norm
-    const int64_t tiles = (N + TM - 1) / TM;
+    const int64_t tiles = (N + TM - 1) / TM + 1;   // one padding tile: a block may hold two query tiles
     const int C = (K + 32 <= 128) ? 256 : 512;
     size_t b = 0;
     b += (size_t)tiles * Dp * 1024 * 2;             // query and database images
     b += sizeof(double) * (size_t)tiles * TM;       // exact norms
     b += (sizeof(float) + sizeof(int32_t)) * (size_t)nq * C;   // online / sample candidate buffers
-    if (tiles >= kTwoPassMinTiles) {
+    if (tiles - 1 >= kTwoPassMinTiles) {
         b += (sizeof(float) + sizeof(int32_t)) * (size_t)nq * fixed_cap(K);   // fixed-threshold buffers
         b += sizeof(float) * (size_t)nq + sizeof(int) * (size_t)nq * 3;    // tau, row flags, per-group counts
     }
@@ -817,10 +832,11 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     const long long dt_lo = db_lo / TN, dt_hi = (db_hi + TN - 1) / TN;
     const int kFixedCap = fixed_cap(K);
     const bool two_pass = (dt_hi - dt_lo) >= kTwoPassMinTiles && tiles >= kTwoPassMinTiles;
+    const long long tiles_pad = tiles + 1;   // images of one all-padding tile follow the last real one
     char *p = static_cast<char *>(workspace);
-    float *img_q = reinterpret_cast<float *>(p); p += (size_t)tiles * Dp * 1024;
-    float *img_db = reinterpret_cast<float *>(p); p += (size_t)tiles * Dp * 1024;
-    double *norms_exact = reinterpret_cast<double *>(p); p += sizeof(double) * (size_t)tiles * TM;
+    float *img_q = reinterpret_cast<float *>(p); p += (size_t)tiles_pad * Dp * 1024;
+    float *img_db = reinterpret_cast<float *>(p); p += (size_t)tiles_pad * Dp * 1024;
+    double *norms_exact = reinterpret_cast<double *>(p); p += sizeof(double) * (size_t)tiles_pad * TM;
     float *cand_key = reinterpret_cast<float *>(p); p += sizeof(float) * (size_t)nq * C;
     int32_t *cand_id = reinterpret_cast<int32_t *>(p); p += sizeof(int32_t) * (size_t)nq * C;
     float *fix_key = nullptr, *tau = nullptr;
@@ -837,16 +853,24 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     int *flist = reinterpret_cast<int *>(p); p += sizeof(int) * (size_t)nq;
     int *counters = reinterpret_cast<int *>(p);   // [0] wait time-out flag, [1] failed rows, [2] listed rows, [3] max error ratio (float bits)
     B200_CUDA(cudaMemsetAsync(counters, 0, sizeof(int) * 16, st));
-    knn_tc_prepare_kernel<<<(unsigned)tiles, 128, 0, st>>>(X, N, D, Dp, img_q, img_db, norms_exact);
+    knn_tc_prepare_kernel<<<(unsigned)tiles_pad, 128, 0, st>>>(X, N, D, Dp, img_q, img_db, norms_exact);
     B200_CUDA(cudaGetLastError());
-    const size_t smem = (size_t)(1 + kBStages) * Dp * 1024;
-    const unsigned grid = (unsigned)(qt_hi - qt_lo);
+    // two query tiles per block when their images and the database stages fit in shared memory
+    const int QH = ((size_t)(2 + kBStages) * Dp * 1024 + 1024 <= 227 * 1024) ? 2 : 1;
+#define B200_KNN_FILTER_V(EPL_, FIXED_, QH_, stride_, tau_, cap_, key_, id_, counts_)                                           \
+    do {                                                                                                                        \
+        const size_t smem_ = (size_t)(QH_ + kBStages) * Dp * 1024;                                                              \
+        B200_CUDA(cudaFuncSetAttribute(knn_tc_filter_kernel<EPL_, FIXED_, QH_>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                       (int)smem_));                                                                            \
+        knn_tc_filter_kernel<EPL_, FIXED_, QH_><<<(unsigned)((qt_hi - qt_lo + QH_ - 1) / QH_), tc_threads(QH_), smem_, st>>>(    \
+            img_q, img_db, Dp, qt_lo, dt_lo, dt_hi, stride_, q_lo, q_hi, db_lo, db_hi, tau_, cap_, key_, id_, counts_, counters + 0); \
+        B200_CUDA(cudaGetLastError());                                                                                          \
+    } while (0)
+    // the online threshold keeps one group per query busy: one query tile per block is enough there
 #define B200_KNN_FILTER(EPL_, FIXED_, stride_, tau_, cap_, key_, id_, counts_)                                                   \
     do {                                                                                                                        \
-        B200_CUDA(cudaFuncSetAttribute(knn_tc_filter_kernel<EPL_, FIXED_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        knn_tc_filter_kernel<EPL_, FIXED_><<<grid, kTcThreads, smem, st>>>(img_q, img_db, Dp, qt_lo, dt_lo, dt_hi, stride_, q_lo, q_hi, \
-                                                                          db_lo, db_hi, tau_, cap_, key_, id_, counts_, counters + 0); \
-        B200_CUDA(cudaGetLastError());                                                                                          \
+        if (!FIXED_ || QH == 1) B200_KNN_FILTER_V(EPL_, FIXED_, 1, stride_, tau_, cap_, key_, id_, counts_);                     \
+        else B200_KNN_FILTER_V(EPL_, FIXED_, (FIXED_ ? 2 : 1), stride_, tau_, cap_, key_, id_, counts_);                         \
     } while (0)
     const float *final_key = cand_key;
     const int32_t *final_id = cand_id;
@@ -901,6 +925,7 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         final_stride = kFixedCap;
     }
 #undef B200_KNN_FILTER
+#undef B200_KNN_FILTER_V
     // Error bound of the filter relative to (|x_i|^2 + d^2 + 1): 3xTF32 drops terms of order 2^-22 |x_i||x_j|
     // and the tensor-core accumulation is not IEEE; 2^-14 covers both with a wide margin, and the re-rank
     // checks the observed error of every candidate against half of it.
