@@ -80,7 +80,7 @@ int launch_knn_exact_rows(const float *XT, int64_t N, int D, int K, const int *q
                           int64_t db_lo, int64_t db_hi, int32_t *ids, float *d2, cudaStream_t st);
 // knn_tc.cu: tensor-core filter + exact re-rank + proof (D <= 64)
 bool knn_tc_supported(int64_t N, int D, int K);
-size_t knn_tc_workspace_bytes(int64_t N, int D, int K, int64_t nq);
+size_t knn_tc_workspace_bytes(int D, int K, int64_t nq, int64_t nd);
 int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_hi, int64_t db_lo, int64_t db_hi,
                   int32_t *ids, float *d2, void *workspace, int **failed_list, int *n_failed_host, float *err_ratio_host,
                   cudaStream_t st);

@@ -406,7 +406,7 @@ int knn_search(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_
     // bounded however large N is; the operand images are rebuilt per batch (a millisecond per million points).
     const int64_t batch = (int64_t)1 << 20;
     void *ws = nullptr;
-    B200_TRY(tmp.alloc(&ws, knn_tc_workspace_bytes(N, D, K, std::min(nq, batch))));
+    B200_TRY(tmp.alloc(&ws, knn_tc_workspace_bytes(D, K, std::min(nq, batch), db_hi - db_lo)));
     stats->tensor_core = 1;
     for (int64_t b_lo = q_lo; b_lo < q_hi; b_lo += batch) {
         const int64_t b_hi = std::min(q_hi, b_lo + batch);

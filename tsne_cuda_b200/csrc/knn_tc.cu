@@ -207,40 +207,154 @@ __device__ __forceinline__ size_t image_offset(int r, int k)
     return (size_t)(k >> 3) * 1024 + (size_t)(r >> 3) * 64 + (size_t)((k >> 2) & 1) * 32 + (size_t)(r & 7) * 4 + (k & 3);
 }
 
-// X [N][D] -> query images and database images, each [tiles][2 (hi, lo)][Dp/8][1024 floats], and the
-// exact squared norms (double).  Query rows are [x, 1, 0...], database rows [-2x, |x|^2, 0...]; rows
-// beyond N get zeros (queries) and a huge finite norm (database), so they never rank.
+// Rows of X named by `list` (-1 = padding) -> tile images [tiles][2 (hi, lo)][Dp/8][1024 floats] in query form
+// [x, 1, 0...] or database form [-2x, |x|^2, 0...]; a padding row is all zeros as a query and carries a huge
+// finite norm as a database point, so it never ranks.  norms (queries only): exact squared norms, double.
 __global__ void __launch_bounds__(128)
-knn_tc_prepare_kernel(const float *__restrict__ X, long long N, int D, int Dp, float *__restrict__ img_q,
-                      float *__restrict__ img_db, double *__restrict__ norms_exact)
+knn_tc_prepare_kernel(const float *__restrict__ X, const int *__restrict__ list, int D, int Dp, int db_form,
+                      float *__restrict__ img, double *__restrict__ norms)
 {
     const long long tile = blockIdx.x;
     const int r = threadIdx.x;
-    const long long i = tile * TM + r;
-    float *iq = img_q + (size_t)tile * 2 * Dp * 128;
-    float *id = img_db + (size_t)tile * 2 * Dp * 128;
+    const long long pos = tile * TM + r;
+    const int i = list[pos];
+    float *im = img + (size_t)tile * 2 * Dp * 128;
     const size_t part = (size_t)Dp * 128;
     double n2 = 0.0;
     for (int k = 0; k < D; k++) {
-        const float x = (i < N) ? X[i * D + k] : 0.0f;
+        const float x = (i >= 0) ? X[(long long)i * D + k] : 0.0f;
         n2 += (double)x * (double)x;
     }
     for (int k = 0; k < Dp; k++) {
-        float q = 0.0f, d = 0.0f;
+        float v = 0.0f;
         if (k < D) {
-            q = (i < N) ? X[i * D + k] : 0.0f;
-            d = -2.0f * q;
+            const float x = (i >= 0) ? X[(long long)i * D + k] : 0.0f;
+            v = db_form ? -2.0f * x : x;
         } else if (k == D) {
-            q = (i < N) ? 1.0f : 0.0f;
-            d = (i < N) ? (float)n2 : 3.0e38f;
+            v = db_form ? ((i >= 0) ? (float)n2 : 3.0e38f) : ((i >= 0) ? 1.0f : 0.0f);
         }
-        const float qh = to_tf32(q), dh = to_tf32(d);
-        iq[image_offset(r, k)] = qh;
-        iq[part + image_offset(r, k)] = to_tf32(q - qh);
-        id[image_offset(r, k)] = dh;
-        id[part + image_offset(r, k)] = to_tf32(d - dh);
+        const float vh = to_tf32(v);
+        im[image_offset(r, k)] = vh;
+        im[part + image_offset(r, k)] = to_tf32(v - vh);
     }
-    norms_exact[i] = n2;
+    if (norms) norms[pos] = n2;
+}
+
+// ------------------------------------------------------------------------------------------------
+// cells: a coarse partition of the points that lets a block skip database tiles no query of it can reach
+// ------------------------------------------------------------------------------------------------
+// Both the database rows and the queries of a search are visited in the order of a partition into at
+// most kMaxCells Voronoi cells around sample points ("centres").  Database cells start on tile
+// boundaries (padding rows in between), so a cell is a run of whole tiles; for every cell the largest
+// distance r_c of a member to its centre is known.  Once a query's threshold is fixed, no point of cell c
+// can pass it if  |x_q - centre_c| - r_c  exceeds the threshold distance (triangle inequality), and a block
+// skips the cells that none of its queries can reach.  On clustered data most tile pairs disappear; on
+// data without structure nothing is lost but the few milliseconds of these kernels.
+constexpr int kMaxCells = 64;
+constexpr int kCellThreads = 256;
+
+struct CellTable {
+    float centre[kMaxCells][64];      // zero beyond D
+    unsigned int radius_bits[kMaxCells];   // float bits of r_c (non-negative floats order like unsigned integers)
+    int db_count[kMaxCells], q_count[kMaxCells];
+    int db_start[kMaxCells + 1];      // first list position of the cell (multiple of TN); [cells] = end
+    int q_start[kMaxCells + 1];
+    int db_cursor[kMaxCells], q_cursor[kMaxCells];
+};
+
+__global__ void knn_cells_init_kernel(const float *__restrict__ X, int D, long long db_lo, long long nd, int cells, CellTable *tab)
+{
+    // centres = database rows spread evenly over the range
+    for (int idx = threadIdx.x; idx < cells * 64; idx += blockDim.x) {
+        const int c = idx >> 6, d = idx & 63;
+        const long long row = db_lo + (long long)(((double)c + 0.5) * (double)nd / (double)cells);
+        tab->centre[c][d] = (d < D) ? X[row * D + d] : 0.0f;
+    }
+    for (int c = threadIdx.x; c < kMaxCells; c += blockDim.x) {
+        tab->radius_bits[c] = 0u;
+        tab->db_count[c] = tab->q_count[c] = 0;
+        tab->db_cursor[c] = tab->q_cursor[c] = 0;
+    }
+}
+
+// cell[i] = nearest centre of row lo + i; counts the members and (for the database) maintains r_c
+__global__ void __launch_bounds__(kCellThreads)
+knn_cells_assign_kernel(const float *__restrict__ X, int D, long long lo, long long n, int cells, CellTable *tab, int is_db,
+                        unsigned char *__restrict__ cell)
+{
+    __shared__ float s_c[kMaxCells][65];
+    __shared__ int s_cnt[kMaxCells];
+    __shared__ unsigned int s_rad[kMaxCells];
+    for (int idx = threadIdx.x; idx < cells * 64; idx += kCellThreads) s_c[idx >> 6][idx & 63] = tab->centre[idx >> 6][idx & 63];
+    for (int c = threadIdx.x; c < kMaxCells; c += kCellThreads) { s_cnt[c] = 0; s_rad[c] = 0u; }
+    __syncthreads();
+    const long long i = (long long)blockIdx.x * kCellThreads + threadIdx.x;
+    if (i < n) {
+        float x[64];
+#pragma unroll
+        for (int d = 0; d < 64; d++) x[d] = (d < D) ? X[(lo + i) * D + d] : 0.0f;
+        float best = INFINITY;
+        int bc = 0;
+        for (int c = 0; c < cells; c++) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int d = 0; d < 64; d++) {
+                const float t = x[d] - s_c[c][d];
+                acc = fmaf(t, t, acc);
+            }
+            if (acc < best) { best = acc; bc = c; }
+        }
+        cell[i] = (unsigned char)bc;
+        atomicAdd(&s_cnt[bc], 1);
+        if (is_db) atomicMax(&s_rad[bc], __float_as_uint(sqrtf(best)));
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < cells; c += kCellThreads) {
+        if (s_cnt[c]) atomicAdd(is_db ? &tab->db_count[c] : &tab->q_count[c], s_cnt[c]);
+        if (is_db && s_rad[c]) atomicMax(&tab->radius_bits[c], s_rad[c]);
+    }
+}
+
+// list positions of the cells: database cells padded to whole tiles, query cells back to back
+__global__ void knn_cells_layout_kernel(int cells, CellTable *tab)
+{
+    if (threadIdx.x != 0) return;
+    int db = 0, q = 0;
+    for (int c = 0; c < cells; c++) {
+        tab->db_start[c] = db;
+        tab->q_start[c] = q;
+        db += (tab->db_count[c] + TN - 1) / TN * TN;
+        q += tab->q_count[c];
+    }
+    for (int c = cells; c <= kMaxCells; c++) { tab->db_start[c] = db; tab->q_start[c] = q; }
+}
+
+// list[start(cell) + rank within the cell] = row; the order inside a cell is arbitrary (it decides which
+// points share a tile, never the result)
+__global__ void __launch_bounds__(kCellThreads)
+knn_cells_scatter_kernel(const unsigned char *__restrict__ cell, long long lo, long long n, int cells, CellTable *tab, int is_db,
+                         int *__restrict__ list)
+{
+    __shared__ int s_cnt[kMaxCells], s_base[kMaxCells];
+    for (int c = threadIdx.x; c < kMaxCells; c += kCellThreads) s_cnt[c] = 0;
+    __syncthreads();
+    const long long i = (long long)blockIdx.x * kCellThreads + threadIdx.x;
+    int c = 0, local = 0;
+    if (i < n) {
+        c = cell[i];
+        local = atomicAdd(&s_cnt[c], 1);
+    }
+    __syncthreads();
+    for (int k = threadIdx.x; k < cells; k += kCellThreads)
+        if (s_cnt[k]) s_base[k] = atomicAdd(is_db ? &tab->db_cursor[k] : &tab->q_cursor[k], s_cnt[k]);
+    __syncthreads();
+    if (i < n) list[(is_db ? tab->db_start[c] : tab->q_start[c]) + s_base[c] + local] = (int)(lo + i);
+}
+
+__global__ void knn_iota_kernel(int *__restrict__ list, long long lo, long long n)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) list[i] = (int)(lo + i);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -323,6 +437,86 @@ __device__ __noinline__ float warp_compact(float *bk, int32_t *bi, int n, int la
     return __shfl_sync(0xffffffffu, k[EPL - 1], 15);   // element L-1 sits in lane 15, last register
 }
 
+// One block per filter block (qpc = its queries): which cells can hold a point that passes the threshold of
+// at least one of its queries?  Their tile ranges, merged where adjacent, are the block's segments.
+// Rounding: the fp32 distances carry a relative error below 1e-5 (sums of at most 64 squares), the
+// inequality is tested with margins ten times that; a comparison that involves a NaN keeps the cell.
+__global__ void __launch_bounds__(kCellThreads)
+knn_cells_segments_kernel(const float *__restrict__ X, int D, const int *__restrict__ qlist, long long nq, int qpc,
+                          const float *__restrict__ tau, const double *__restrict__ norms_q, int cells,
+                          const CellTable *__restrict__ tab, int2 *__restrict__ segs, int *__restrict__ nseg)
+{
+    __shared__ float s_c[kMaxCells][65];
+    __shared__ float s_r[kMaxCells];
+    __shared__ int s_keep[kMaxCells];
+    for (int idx = threadIdx.x; idx < cells * 64; idx += kCellThreads) s_c[idx >> 6][idx & 63] = tab->centre[idx >> 6][idx & 63];
+    for (int c = threadIdx.x; c < kMaxCells; c += kCellThreads) {
+        s_r[c] = __uint_as_float(tab->radius_bits[c]) * 1.00001f;
+        s_keep[c] = 0;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < qpc; j += kCellThreads) {
+        const long long q = (long long)blockIdx.x * qpc + j;
+        if (q >= nq) continue;
+        const double R2 = norms_q[q] + (double)tau[q];   // a point passes if its squared distance is below this
+        if (!(R2 <= 0.0)) {
+            const float R = (float)sqrt(R2) * 1.0001f;
+            const int i = qlist[q];
+            float x[64];
+#pragma unroll
+            for (int d = 0; d < 64; d++) x[d] = (d < D) ? X[(long long)i * D + d] : 0.0f;
+            for (int c = 0; c < cells; c++) {
+                float acc = 0.0f;
+#pragma unroll
+                for (int d = 0; d < 64; d++) {
+                    const float t = x[d] - s_c[c][d];
+                    acc = fmaf(t, t, acc);
+                }
+                const float lower = sqrtf(acc) * 0.99999f - s_r[c];
+                if (!(lower > R)) s_keep[c] = 1;
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int n = 0;
+        int2 *out = segs + (size_t)blockIdx.x * kMaxCells;
+        for (int c = 0; c < cells; c++) {
+            if (!s_keep[c] || tab->db_count[c] == 0) continue;
+            const int a = tab->db_start[c] / TN, b = tab->db_start[c + 1] / TN;
+            if (n > 0 && out[n - 1].y == a) out[n - 1].y = b;
+            else out[n++] = make_int2(a, b);
+        }
+        nseg[blockIdx.x] = n;
+    }
+}
+
+__global__ void knn_single_segment_kernel(int2 *segs, int *nseg, int tiles)
+{
+    segs[0] = make_int2(0, tiles);
+    nseg[0] = 1;
+}
+
+// The database tiles of a block in scan order: the tiles of its segments that are multiples of `stride`.
+// The producer, the MMA issuer and the epilogue each walk the same sequence.
+struct TileWalk {
+    const int2 *segs;
+    int nseg, stride, s, t, end;
+    __device__ TileWalk(const int2 *segs_, int nseg_, int stride_) : segs(segs_), nseg(nseg_), stride(stride_), s(-1), t(0), end(0) {}
+    __device__ bool next(int &tile)
+    {
+        while (t >= end) {
+            if (++s >= nseg) return false;
+            const int2 g = segs[s];
+            t = (g.x + stride - 1) / stride * stride;
+            end = g.y;
+        }
+        tile = t;
+        t += stride;
+        return true;
+    }
+};
+
 // ------------------------------------------------------------------------------------------------
 // filter kernel
 // ------------------------------------------------------------------------------------------------
@@ -336,20 +530,22 @@ struct TcShared {
     int abort_flag;
 };
 
-// img_q / img_db: tile images of all points (query form, database form); query tiles [qt_lo, qt_hi), database tiles [dt_lo, dt_hi); only
-// candidates with db_lo <= id < db_hi are kept, only queries in [q_lo, q_hi) are served.
-// cand_key / cand_id: [(q_hi - q_lo)][32*EPL] candidate buffers; on return the first L = 16*EPL entries of
-// each are the L best keys in ascending order ((+inf, INT_MAX) where the database had fewer points).
-// FIXED = false: threshold maintained online, buffers of 32*EPL entries, database tiles dt_lo, dt_lo +
-// tile_stride, ...   FIXED = true: threshold tau[query] fixed, buffers of `cap` entries (row stride of
-// cand_key / cand_id in both modes, two halves per query); counts[2*query + group] receives the number of
-// entries each epilogue group appended (bit 30 set if its half overflowed); knn_tc_select_kernel finishes.
+// img_q / img_db: tile images of the query list and of the database list.  A block serves the queries
+// [blockIdx.x * QH * 128, ...) of the list (nq in all) against the database tiles of its segments
+// (segs + blockIdx.x * seg_stride, nseg[blockIdx.x * (seg_stride != 0)] of them; seg_stride = 0: one list shared by
+// all blocks), taking every tile_stride-th tile.  Candidate ids are database list positions; positions from
+// nd_pos on are padding and never kept.
+// cand_key / cand_id: [nq][cap] candidate buffers.  FIXED = false: threshold maintained online, cap = 32*EPL;
+// on return the first L = 16*EPL entries of each are the L best keys in ascending order ((+inf, INT_MAX)
+// where the database had fewer points).  FIXED = true: threshold tau[query] fixed, two segments of cap/2
+// entries per query; counts[2*query + buffer] receives the number of entries appended to each (bit 30 set
+// if it overflowed); knn_tc_select_kernel finishes.
 template <int EPL, bool FIXED, int QH>
 __global__ void __launch_bounds__(tc_threads(QH), 1)
-knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int Dp, long long qt_lo,
-                     long long dt_lo, long long dt_hi, int tile_stride, long long q_lo, long long q_hi, long long db_lo,
-                     long long db_hi, const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id,
-                     int *__restrict__ counts, int *error_flag)
+knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int Dp, long long nq, long long nd_pos,
+                     const int2 *__restrict__ segs, const int *__restrict__ nseg, int seg_stride, int tile_stride,
+                     const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id, int *__restrict__ counts,
+                     int *error_flag)
 {
     constexpr int C = 32 * EPL;   // capacity handled by one compaction
     constexpr int L = 16 * EPL;
@@ -362,8 +558,9 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
     float *sB = reinterpret_cast<float *>(smem + QH * image_bytes);       // [kBStages] images
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nks = Dp >> 3;
-    const long long qt = qt_lo + (long long)blockIdx.x * QH;   // first query tile of the block
-    const long long n_tiles = (dt_hi - dt_lo + tile_stride - 1) / tile_stride;
+    const long long qt = (long long)blockIdx.x * QH;   // first query tile of the block
+    const int2 *my_segs = segs + (size_t)blockIdx.x * seg_stride;
+    const int my_nseg = nseg[seg_stride ? blockIdx.x : 0];
     volatile int *abort_flag = &sh.abort_flag;
 
     if (threadIdx.x == 0) {
@@ -393,20 +590,23 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
             mbar_expect_tx(&sh.full_a, QH * image_bytes);
             for (int h = 0; h < QH; h++)
                 bulk_load(sA + (size_t)h * (image_bytes / 4), img_q + (size_t)(qt + h) * (image_bytes / 4), image_bytes, &sh.full_a);
-            for (long long t = 0; t < n_tiles; t++) {
+            TileWalk walk(my_segs, my_nseg, tile_stride);
+            int tile;
+            for (long long t = 0; walk.next(tile); t++) {
                 const int s = (int)(t % kBStages);
                 const uint32_t ph = (uint32_t)((t / kBStages) & 1);
                 if (!mbar_wait(&sh.empty_b[s], ph ^ 1u, abort_flag)) break;
                 mbar_expect_tx(&sh.full_b[s], image_bytes);
-                bulk_load(sB + (size_t)s * (image_bytes / 4), img_db + (size_t)(dt_lo + t * tile_stride) * (image_bytes / 4), image_bytes,
-                          &sh.full_b[s]);
+                bulk_load(sB + (size_t)s * (image_bytes / 4), img_db + (size_t)tile * (image_bytes / 4), image_bytes, &sh.full_b[s]);
             }
         }
     } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             bool ok = mbar_wait(&sh.full_a, 0, abort_flag);
-            for (long long t = 0; ok && t < n_tiles; t++) {
+            TileWalk walk(my_segs, my_nseg, tile_stride);
+            int tile;
+            for (long long t = 0; ok && walk.next(tile); t++) {
                 const int s = (int)(t % kBStages), b = (int)(t % kAccBufs);
                 const uint32_t ph_s = (uint32_t)((t / kBStages) & 1), ph_b = (uint32_t)((t / kAccBufs) & 1);
                 if (!mbar_wait(&sh.acc_empty[b], ph_b ^ 1u, abort_flag)) break;
@@ -444,10 +644,10 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
         const int seg_cap = FIXED ? cap / kAccBufs : cap;
         const int row = quarter * 32 + lane;                    // TMEM lane
         const long long gq = (qt + half) * TM + row;
-        const bool serve = gq >= q_lo && gq < q_hi && active;
-        float *bk = cand_key + (serve ? (gq - q_lo) : 0) * cap + (FIXED ? buf * seg_cap : 0);
-        int32_t *bi = cand_id + (serve ? (gq - q_lo) : 0) * cap + (FIXED ? buf * seg_cap : 0);
-        float thr = serve ? (FIXED ? tau[gq - q_lo] : INFINITY) : -INFINITY;
+        const bool serve = gq < nq && active;
+        float *bk = cand_key + (serve ? gq : 0) * cap + (FIXED ? buf * seg_cap : 0);
+        int32_t *bi = cand_id + (serve ? gq : 0) * cap + (FIXED ? buf * seg_cap : 0);
+        float thr = serve ? (FIXED ? tau[gq] : INFINITY) : -INFINITY;
         int cnt = 0;
         bool overflow = false;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * TN);
@@ -475,7 +675,7 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
                             const int c = q * 8 + e;
                             const float key = __uint_as_float(r[c]);
                             const long long cid = col0 + c;
-                            const bool pass = key < thr && (tile_inside || (cid >= db_lo && cid < db_hi));
+                            const bool pass = key < thr && (tile_inside || cid < nd_pos);
                             if (pass) {
                                 __stcg(bk + cnt, key);
                                 __stcg(bi + cnt, (int32_t)cid);
@@ -494,7 +694,7 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
                 while (full) {
                     const int owner = __ffs(full) - 1;
                     full &= full - 1;
-                    const long long oq = (qt + half) * TM + quarter * 32 + owner - q_lo;
+                    const long long oq = (qt + half) * TM + quarter * 32 + owner;
                     const int n = __shfl_sync(0xffffffffu, cnt, owner);
                     const float nt = warp_compact<EPL>(cand_key + oq * cap, cand_id + oq * cap, n, lane);
                     if (lane == owner) { thr = nt; cnt = L; }
@@ -502,13 +702,16 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
             }
         };
 
-        for (long long t = FIXED ? buf : 0; t < n_tiles && active; t += FIXED ? kAccBufs : 1) {
+        TileWalk walk(my_segs, active ? my_nseg : 0, tile_stride);
+        int tile;
+        for (long long t = 0; walk.next(tile); t++) {
             const int b = (int)(t % kAccBufs);
+            if (FIXED && b != buf) continue;
             const uint32_t ph_b = (uint32_t)((t / kAccBufs) & 1);
             if (!mbar_wait(&sh.acc_full[b], ph_b, abort_flag, 32)) break;
             tc_fence_after();
-            const long long p0 = (dt_lo + t * tile_stride) * TN;
-            const bool inside = p0 >= db_lo && p0 + TN <= db_hi;
+            const long long p0 = (long long)tile * TN;
+            const bool inside = p0 + TN <= nd_pos;
             const uint32_t tcol = lane_base + (uint32_t)(b * QH * TN);
             // one copy of the chunk code, executed four times: the epilogue is issue- and
             // instruction-fetch-bound, so small code beats overlapping the (fast) TMEM reads
@@ -528,14 +731,14 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
         if (FIXED) {
             // The final selection is a separate kernel (one warp per query, thousands in flight): it is a chain of
             // dependent global round trips, which the warps of this block would walk through one query at a time.
-            if (serve) counts[(gq - q_lo) * kAccBufs + buf] = cnt | (overflow ? 0x40000000 : 0);
+            if (serve) counts[gq * kAccBufs + buf] = cnt | (overflow ? 0x40000000 : 0);
         } else if (active) {
             // online threshold (small databases): one last compaction leaves the L best, sorted, in front
             unsigned m = __ballot_sync(0xffffffffu, serve);
             while (m) {
                 const int owner = __ffs(m) - 1;
                 m &= m - 1;
-                const long long oq = (qt + half) * TM + quarter * 32 + owner - q_lo;
+                const long long oq = (qt + half) * TM + quarter * 32 + owner;
                 const int n = __shfl_sync(0xffffffffu, cnt, owner);
                 (void)warp_compact<EPL>(cand_key + oq * cap, cand_id + oq * cap, min(n, C), lane);
             }
@@ -612,10 +815,12 @@ __device__ __forceinline__ float canon_dist(const float *__restrict__ a, const f
 constexpr int kRerankWarps = 4;
 constexpr int kMaxL = 256;
 
-// One warp per query.  ids/d2 [nq][K] receive the K best candidates by (canonical distance, id);
-// failed[q] = 1 when the proof does not close for the row.
+// One warp per query of the list (query row qlist[q]; candidate ids are positions in dblist).  Row
+// (qlist[q] - out_base) of ids/d2 ([.][K]) receives the K best candidates by (canonical distance, row id);
+// failed[q] = 1 when the proof does not close for the query.
 __global__ void __launch_bounds__(kRerankWarps * 32)
-knn_tc_rerank_kernel(const float *__restrict__ X, int D, long long q_lo, long long nq, const float *__restrict__ cand_key,
+knn_tc_rerank_kernel(const float *__restrict__ X, int D, const int *__restrict__ qlist, const int *__restrict__ dblist,
+                     long long out_base, long long nq, const float *__restrict__ cand_key,
                      const int32_t *__restrict__ cand_id, int L, int C, int K, const double *__restrict__ norms_exact,
                      float err_scale, const int *__restrict__ row_flags, int32_t *__restrict__ ids, float *__restrict__ d2,
                      int *__restrict__ failed,
@@ -626,14 +831,17 @@ knn_tc_rerank_kernel(const float *__restrict__ X, int D, long long q_lo, long lo
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long q = (long long)blockIdx.x * kRerankWarps + w;
     if (q >= nq) return;
-    const long long gq = q_lo + q;
+    const long long gq = qlist[q];
+    const long long orow = gq - out_base;
     const float *xq = X + gq * D;
-    const double ni = norms_exact[gq];
+    const double ni = norms_exact[q];
     float worst = 0.0f;   // largest observed |filter distance - canonical distance| among the candidates
     float T = -INFINITY;
     int n_valid = 0;
     for (int e = lane; e < L; e += 32) {
-        const int id = cand_id[q * C + e];
+        const int pos = cand_id[q * C + e];
+        int id = (pos != INT_MAX) ? dblist[pos] : INT_MAX;
+        if (id < 0) id = INT_MAX;   // a padding position (never kept by a finite threshold)
         const float key = cand_key[q * C + e];
         float dist = INFINITY;
         if (id != INT_MAX) {
@@ -665,8 +873,8 @@ knn_tc_rerank_kernel(const float *__restrict__ X, int D, long long q_lo, long lo
             rank += (du < de || (du == de && iu < ie)) ? 1 : 0;
         }
         if (rank < K) {
-            ids[q * K + rank] = (ie == INT_MAX) ? -1 : ie;
-            d2[q * K + rank] = de;
+            ids[orow * K + rank] = (ie == INT_MAX) ? -1 : ie;
+            d2[orow * K + rank] = de;
         }
         if (rank == K - 1) dK = de;
     }
@@ -693,18 +901,19 @@ knn_tc_rerank_kernel(const float *__restrict__ X, int D, long long q_lo, long lo
 }
 
 // First threshold level on the CUDA cores: tau[q] = the key of rank `rank` (0-based, < 16) among m sample
-// points X[s_lo + k * s_stride + jitter_k], k = 0..m-1, for each of the nq queries starting at row q_lo.  Keys are
+// points X[s_lo + k * s_stride + jitter_k], k = 0..m-1, for each of the nq queries of the list.  Keys are
 // plain fp32 FMA sums: this threshold only has to be roughly right (it sizes the candidate set of the
 // next level).  One query per thread, held in registers; sample points staged 32 at a time in shared
 // memory and read as broadcast float4.
 constexpr int kTauThreads = 128;
 __global__ void __launch_bounds__(kTauThreads)
-knn_sample_tau_kernel(const float *__restrict__ X, int D, long long q_lo, long long nq, long long s_lo, long long s_stride,
+knn_sample_tau_kernel(const float *__restrict__ X, int D, const int *__restrict__ qlist, long long nq, long long s_lo, long long s_stride,
                       int m, int rank, float *__restrict__ tau)
 {
     __shared__ __align__(16) float s_pt[32][64];
     __shared__ float s_nrm[32];
     const long long q = (long long)blockIdx.x * kTauThreads + threadIdx.x;
+    const long long qrow = (q < nq) ? qlist[q] : 0;
     float4 qv[16];
 #pragma unroll
     for (int i = 0; i < 16; i++) {
@@ -712,7 +921,7 @@ knn_sample_tau_kernel(const float *__restrict__ X, int D, long long q_lo, long l
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int d = 4 * i + e;
-            v[e] = (q < nq && d < D) ? X[(q_lo + q) * D + d] : 0.0f;
+            v[e] = (q < nq && d < D) ? X[qrow * D + d] : 0.0f;
         }
         qv[i] = make_float4(v[0], v[1], v[2], v[3]);
     }
@@ -776,11 +985,11 @@ __global__ void knn_tc_tau_kernel(const float *__restrict__ sample_key, const in
     tau[q] = bad ? -INFINITY : sample_key[q * stride + rank];
 }
 
-__global__ void knn_tc_collect_failed_kernel(const int *__restrict__ failed, long long nq, long long q_lo, int *__restrict__ list,
+__global__ void knn_tc_collect_failed_kernel(const int *__restrict__ failed, long long nq, const int *__restrict__ qlist, int *__restrict__ list,
                                              int *__restrict__ count)
 {
     const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (q < nq && failed[q]) list[atomicAdd(count, 1)] = (int)(q_lo + q);
+    if (q < nq && failed[q]) list[atomicAdd(count, 1)] = qlist[q];
 }
 
 }  // namespace
@@ -796,23 +1005,64 @@ static int fixed_cap(int K) { return (K + 32 <= 128) ? 1024 : 2048; }
 constexpr int kSampleStride = 16;    // the sample pass looks at every 16th database tile
 constexpr long long kTwoPassMinTiles = 512;   // below this many database tiles the online pass alone is used
 
-// Workspace (device) needed by launch_knn_tc; all sizes in bytes.
-size_t knn_tc_workspace_bytes(int64_t N, int D, int K, int64_t nq)
+// Device workspace of launch_knn_tc, carved in this order.
+struct TcWorkspace {
+    int Dp, cells;
+    long long tq, td;          // tiles allocated for the query list / the database list
+    float *img_q, *img_db;
+    double *norms_q;
+    int *qlist, *dblist;
+    unsigned char *cell_q, *cell_db;
+    CellTable *tab;
+    int2 *segs;
+    int *nseg;
+    float *cand_key, *fix_key, *tau;
+    int32_t *cand_id, *fix_id;
+    int *row_flags, *counts, *failed, *flist, *counters;
+    size_t bytes;
+};
+
+static TcWorkspace tc_carve(void *base, int D, int K, long long nq, long long nd)
 {
-    const int Dp = (D + 1 + 7) / 8 * 8;   // one extra inner column carries the norm
-    const int64_t tiles = (N + TM - 1) / TM + 1;   // one padding tile: a block may hold two query tiles
+    TcWorkspace w;
+    w.Dp = (D + 1 + 7) / 8 * 8;   // one extra inner column carries the norm
+    const bool two_pass = nd >= kTwoPassMinTiles * TN;
+    // cells of at least 16384 points: the padding between them stays below 1 % of the database
+    w.cells = two_pass ? (int)std::min<long long>(kMaxCells, std::max<long long>(1, nd / 16384)) : 1;
+    w.tq = (nq + TM - 1) / TM + 1;                 // one padding tile: a block may hold two query tiles
+    w.td = (nd + TN - 1) / TN + w.cells;           // every cell may end in a partly filled tile
     const int C = (K + 32 <= 128) ? 256 : 512;
-    size_t b = 0;
-    b += (size_t)tiles * Dp * 1024 * 2;             // query and database images
-    b += sizeof(double) * (size_t)tiles * TM;       // exact norms
-    b += (sizeof(float) + sizeof(int32_t)) * (size_t)nq * C;   // online / sample candidate buffers
-    if (tiles - 1 >= kTwoPassMinTiles) {
-        b += (sizeof(float) + sizeof(int32_t)) * (size_t)nq * fixed_cap(K);   // fixed-threshold buffers
-        b += sizeof(float) * (size_t)nq + sizeof(int) * (size_t)nq * 3;    // tau, row flags, per-group counts
+    char *p = static_cast<char *>(base);
+    auto take = [&](size_t bytes) { char *r = p; p += (bytes + 255) / 256 * 256; return r; };
+    w.img_q = reinterpret_cast<float *>(take((size_t)w.tq * w.Dp * 1024));
+    w.img_db = reinterpret_cast<float *>(take((size_t)w.td * w.Dp * 1024));
+    w.norms_q = reinterpret_cast<double *>(take(sizeof(double) * (size_t)w.tq * TM));
+    w.qlist = reinterpret_cast<int *>(take(sizeof(int) * (size_t)w.tq * TM));
+    w.dblist = reinterpret_cast<int *>(take(sizeof(int) * (size_t)w.td * TN));
+    w.cell_q = reinterpret_cast<unsigned char *>(take((size_t)nq));
+    w.cell_db = reinterpret_cast<unsigned char *>(take((size_t)nd));
+    w.tab = reinterpret_cast<CellTable *>(take(sizeof(CellTable)));
+    w.segs = reinterpret_cast<int2 *>(take(sizeof(int2) * (size_t)w.tq * kMaxCells));
+    w.nseg = reinterpret_cast<int *>(take(sizeof(int) * (size_t)w.tq));
+    w.cand_key = reinterpret_cast<float *>(take(sizeof(float) * (size_t)nq * C));
+    w.cand_id = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * (size_t)nq * C));
+    w.fix_key = nullptr; w.fix_id = nullptr; w.tau = nullptr; w.row_flags = nullptr; w.counts = nullptr;
+    if (two_pass) {
+        w.fix_key = reinterpret_cast<float *>(take(sizeof(float) * (size_t)nq * fixed_cap(K)));
+        w.fix_id = reinterpret_cast<int32_t *>(take(sizeof(int32_t) * (size_t)nq * fixed_cap(K)));
+        w.tau = reinterpret_cast<float *>(take(sizeof(float) * (size_t)nq));
+        w.row_flags = reinterpret_cast<int *>(take(sizeof(int) * (size_t)nq));
+        w.counts = reinterpret_cast<int *>(take(sizeof(int) * (size_t)nq * 2));
     }
-    b += sizeof(int) * ((size_t)nq * 2 + 16);       // failed flags, failed list, counters
-    return b + 4096;
+    w.failed = reinterpret_cast<int *>(take(sizeof(int) * (size_t)nq));
+    w.flist = reinterpret_cast<int *>(take(sizeof(int) * (size_t)nq));
+    w.counters = reinterpret_cast<int *>(take(sizeof(int) * 16));   // [0] wait time-out flag, [1] failed rows, [2] listed rows, [3] max error ratio (float bits)
+    w.bytes = (size_t)(p - static_cast<char *>(base));
+    return w;
 }
+
+// Workspace (device, 256-byte aligned) needed by launch_knn_tc for nq queries against nd database rows.
+size_t knn_tc_workspace_bytes(int D, int K, int64_t nq, int64_t nd) { return tc_carve(nullptr, D, K, nq, nd).bytes; }
 
 // X: [N][D] row-major (device).  ids/d2: [(q_hi-q_lo)][K].  n_failed_host receives the number of rows
 // whose proof did not close; their global row indices are in failed_list (device, first n entries) and
@@ -822,48 +1072,65 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
                   int32_t *ids, float *d2, void *workspace, int **failed_list, int *n_failed_host, float *err_ratio_host,
                   cudaStream_t st)
 {
-    const long long nq = q_hi - q_lo;
+    (void)N;
+    const long long nq = q_hi - q_lo, nd = db_hi - db_lo;
     *n_failed_host = 0;
     if (nq <= 0) return 0;
-    const int Dp = (D + 1 + 7) / 8 * 8;
-    const long long tiles = (N + TM - 1) / TM;
+    TcWorkspace w = tc_carve(workspace, D, K, nq, nd);
+    const int Dp = w.Dp, cells = w.cells;
     const int EPL = (K + 32 <= 128) ? 8 : 16, C = 32 * EPL, L = 16 * EPL;
-    const long long qt_lo = q_lo / TM, qt_hi = (q_hi + TM - 1) / TM;
-    const long long dt_lo = db_lo / TN, dt_hi = (db_hi + TN - 1) / TN;
     const int kFixedCap = fixed_cap(K);
-    const bool two_pass = (dt_hi - dt_lo) >= kTwoPassMinTiles && tiles >= kTwoPassMinTiles;
-    const long long tiles_pad = tiles + 1;   // images of one all-padding tile follow the last real one
-    char *p = static_cast<char *>(workspace);
-    float *img_q = reinterpret_cast<float *>(p); p += (size_t)tiles_pad * Dp * 1024;
-    float *img_db = reinterpret_cast<float *>(p); p += (size_t)tiles_pad * Dp * 1024;
-    double *norms_exact = reinterpret_cast<double *>(p); p += sizeof(double) * (size_t)tiles_pad * TM;
-    float *cand_key = reinterpret_cast<float *>(p); p += sizeof(float) * (size_t)nq * C;
-    int32_t *cand_id = reinterpret_cast<int32_t *>(p); p += sizeof(int32_t) * (size_t)nq * C;
-    float *fix_key = nullptr, *tau = nullptr;
-    int32_t *fix_id = nullptr;
-    int *row_flags = nullptr, *counts = nullptr;
-    if (tiles >= kTwoPassMinTiles) {
-        fix_key = reinterpret_cast<float *>(p); p += sizeof(float) * (size_t)nq * kFixedCap;
-        fix_id = reinterpret_cast<int32_t *>(p); p += sizeof(int32_t) * (size_t)nq * kFixedCap;
-        tau = reinterpret_cast<float *>(p); p += sizeof(float) * (size_t)nq;
-        row_flags = reinterpret_cast<int *>(p); p += sizeof(int) * (size_t)nq;
-        counts = reinterpret_cast<int *>(p); p += sizeof(int) * (size_t)nq * 2;
-    }
-    int *failed = reinterpret_cast<int *>(p); p += sizeof(int) * (size_t)nq;
-    int *flist = reinterpret_cast<int *>(p); p += sizeof(int) * (size_t)nq;
-    int *counters = reinterpret_cast<int *>(p);   // [0] wait time-out flag, [1] failed rows, [2] listed rows, [3] max error ratio (float bits)
+    const bool two_pass = w.fix_key != nullptr;
+    float *cand_key = w.cand_key, *fix_key = w.fix_key, *tau = w.tau;
+    int32_t *cand_id = w.cand_id, *fix_id = w.fix_id;
+    int *row_flags = w.row_flags, *counts = w.counts, *failed = w.failed, *flist = w.flist, *counters = w.counters;
     B200_CUDA(cudaMemsetAsync(counters, 0, sizeof(int) * 16, st));
-    knn_tc_prepare_kernel<<<(unsigned)tiles_pad, 128, 0, st>>>(X, N, D, Dp, img_q, img_db, norms_exact);
+
+    // ---- visiting order of the queries and of the database, operand images ----
+    B200_CUDA(cudaMemsetAsync(w.qlist, 0xff, sizeof(int) * (size_t)w.tq * TM, st));    // -1 = padding
+    B200_CUDA(cudaMemsetAsync(w.dblist, 0xff, sizeof(int) * (size_t)w.td * TN, st));
+    long long nd_pos = nd;   // database list positions in use (an upper bound when the cells are padded)
+    if (cells > 1) {
+        const unsigned gq = (unsigned)((nq + kCellThreads - 1) / kCellThreads), gd = (unsigned)((nd + kCellThreads - 1) / kCellThreads);
+        knn_cells_init_kernel<<<1, 256, 0, st>>>(X, D, db_lo, nd, cells, w.tab);
+        knn_cells_assign_kernel<<<gd, kCellThreads, 0, st>>>(X, D, db_lo, nd, cells, w.tab, 1, w.cell_db);
+        knn_cells_assign_kernel<<<gq, kCellThreads, 0, st>>>(X, D, q_lo, nq, cells, w.tab, 0, w.cell_q);
+        knn_cells_layout_kernel<<<1, 32, 0, st>>>(cells, w.tab);
+        knn_cells_scatter_kernel<<<gd, kCellThreads, 0, st>>>(w.cell_db, db_lo, nd, cells, w.tab, 1, w.dblist);
+        knn_cells_scatter_kernel<<<gq, kCellThreads, 0, st>>>(w.cell_q, q_lo, nq, cells, w.tab, 0, w.qlist);
+        nd_pos = w.td * TN;
+    } else {
+        knn_iota_kernel<<<(unsigned)((nd + 255) / 256), 256, 0, st>>>(w.dblist, db_lo, nd);
+        knn_iota_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(w.qlist, q_lo, nq);
+    }
     B200_CUDA(cudaGetLastError());
+    knn_tc_prepare_kernel<<<(unsigned)w.tq, 128, 0, st>>>(X, w.qlist, D, Dp, 0, w.img_q, w.norms_q);
+    knn_tc_prepare_kernel<<<(unsigned)w.td, 128, 0, st>>>(X, w.dblist, D, Dp, 1, w.img_db, nullptr);
+    B200_CUDA(cudaGetLastError());
+
     // two query tiles per block when their images and the database stages fit in shared memory
     const int QH = ((size_t)(2 + kBStages) * Dp * 1024 + 1024 <= 227 * 1024) ? 2 : 1;
+    const long long q_tiles = (nq + TM - 1) / TM;
+    // Segments of the blocks: all database tiles (one shared list) unless the cells prune (per block).
+    // The blocks of an online pass hold one query tile, those of a fixed-threshold pass QH.
+    knn_single_segment_kernel<<<1, 1, 0, st>>>(w.segs, w.nseg, (int)((nd + TN - 1) / TN));
+    B200_CUDA(cudaGetLastError());
+    int seg_stride = 0;
+    auto prune = [&]() -> int {   // segments from the current thresholds
+        if (cells <= 1) return 0;
+        knn_cells_segments_kernel<<<(unsigned)((q_tiles + QH - 1) / QH), kCellThreads, 0, st>>>(X, D, w.qlist, nq, QH * TM, tau, w.norms_q,
+                                                                                              cells, w.tab, w.segs, w.nseg);
+        B200_CUDA(cudaGetLastError());
+        seg_stride = kMaxCells;
+        return 0;
+    };
 #define B200_KNN_FILTER_V(EPL_, FIXED_, QH_, stride_, tau_, cap_, key_, id_, counts_)                                           \
     do {                                                                                                                        \
         const size_t smem_ = (size_t)(QH_ + kBStages) * Dp * 1024;                                                              \
         B200_CUDA(cudaFuncSetAttribute(knn_tc_filter_kernel<EPL_, FIXED_, QH_>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
                                        (int)smem_));                                                                            \
-        knn_tc_filter_kernel<EPL_, FIXED_, QH_><<<(unsigned)((qt_hi - qt_lo + QH_ - 1) / QH_), tc_threads(QH_), smem_, st>>>(    \
-            img_q, img_db, Dp, qt_lo, dt_lo, dt_hi, stride_, q_lo, q_hi, db_lo, db_hi, tau_, cap_, key_, id_, counts_, counters + 0); \
+        knn_tc_filter_kernel<EPL_, FIXED_, QH_><<<(unsigned)((q_tiles + QH_ - 1) / QH_), tc_threads(QH_), smem_, st>>>(          \
+            w.img_q, w.img_db, Dp, nq, nd_pos, w.segs, w.nseg, seg_stride, stride_, tau_, cap_, key_, id_, counts_, counters + 0); \
         B200_CUDA(cudaGetLastError());                                                                                          \
     } while (0)
     // the online threshold keeps one group per query busy: one query tile per block is enough there
@@ -884,9 +1151,11 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         //     chosen so that ~300 points of sample B beat it;
         //  B  every kSampleStride-th tile against tau_A;
         //  C  everything against tau_B = the key of rank ~3L/kSampleStride in sample B: ~3L points beat it.
-        const long long n_db_tiles = dt_hi - dt_lo;
+        // Before each scan the cells are tested against the thresholds it will use; a skipped cell holds no
+        // point below them, so the candidate sets (and the sample statistics) are those of a full scan.
+        const long long n_db_tiles = (nd + TN - 1) / TN;
         const double b_points = (double)((n_db_tiles + kSampleStride - 1) / kSampleStride) * TN;
-        const long long db_n = db_hi - db_lo;
+        const long long db_n = nd;
         // Up to ~400k points the sample of level A is large enough (16 N / 3L points, rank ~16) to fix the
         // threshold of level C directly; beyond that level B refines it.
         const bool direct = db_n <= 393216;
@@ -896,9 +1165,10 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         const double a_target = direct ? 3.0 * L * m_a / (double)db_n : 300.0 * m_a / b_points;
         const int rank_a = std::min(16, std::max(4, (int)(a_target + 0.5))) - 1;
         const int rank_b = std::max(4, (3 * L + kSampleStride - 1) / kSampleStride) - 1;
-        knn_sample_tau_kernel<<<(unsigned)((nq + kTauThreads - 1) / kTauThreads), kTauThreads, 0, st>>>(X, D, q_lo, nq, db_lo, a_stride,
+        knn_sample_tau_kernel<<<(unsigned)((nq + kTauThreads - 1) / kTauThreads), kTauThreads, 0, st>>>(X, D, w.qlist, nq, db_lo, a_stride,
                                                                                                 m_a, rank_a, tau);
         B200_CUDA(cudaGetLastError());
+        B200_TRY(prune());
         const unsigned sel_grid = (unsigned)((nq + 3) / 4);
         if (!direct) {
             if (EPL == 8) {
@@ -911,6 +1181,7 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
             B200_CUDA(cudaGetLastError());
             knn_tc_tau_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(fix_key, fix_id, kFixedCap, rank_b, row_flags, nq, tau);
             B200_CUDA(cudaGetLastError());
+            B200_TRY(prune());
         }
         if (EPL == 8) {
             B200_KNN_FILTER(8, true, 1, tau, kFixedCap, fix_key, fix_id, counts);
@@ -931,10 +1202,10 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     // checks the observed error of every candidate against half of it.
     const float err_scale = 6.103515625e-05f;   // 2^-14
     knn_tc_rerank_kernel<<<(unsigned)((nq + kRerankWarps - 1) / kRerankWarps), kRerankWarps * 32, 0, st>>>(
-        X, D, q_lo, nq, final_key, final_id, L, final_stride, K, norms_exact, err_scale, two_pass ? row_flags : nullptr, ids, d2,
+        X, D, w.qlist, w.dblist, q_lo, nq, final_key, final_id, L, final_stride, K, w.norms_q, err_scale, two_pass ? row_flags : nullptr, ids, d2,
         failed, counters + 1, reinterpret_cast<float *>(counters + 3));
     B200_CUDA(cudaGetLastError());
-    knn_tc_collect_failed_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(failed, nq, q_lo, flist, counters + 2);
+    knn_tc_collect_failed_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(failed, nq, w.qlist, flist, counters + 2);
     B200_CUDA(cudaGetLastError());
     int h[4] = {0, 0, 0, 0};
     B200_CUDA(cudaMemcpyAsync(h, counters, sizeof(h), cudaMemcpyDeviceToHost, st));
