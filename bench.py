@@ -188,11 +188,16 @@ def e2e_ours(X, hp, Y0, args):
     t = TSNE(perplexity=hp["perplexity"], num_neighbors=hp["num_neighbors"], learning_rate=hp["learning_rate"],
              early_exaggeration=hp["early_exaggeration"], n_iter=n_iter, perplexity_epsilon=1e-3)
     y0 = np.asfortranarray(Y0.T)
+    # one untimed call first (20 iterations): the first call of a process pays the lazy loading of every
+    # kernel it uses and the first large device allocations
+    warm = TSNE(perplexity=hp["perplexity"], num_neighbors=hp["num_neighbors"], learning_rate=hp["learning_rate"],
+                early_exaggeration=hp["early_exaggeration"], n_iter=20, perplexity_epsilon=1e-3)
+    warm.fit_transform(X, y0)
     t0 = time.time()
     Y = t.fit_transform(X, y0)
     T = time.time() - t0
     assert np.isfinite(Y).all()
-    return {"value": n_iter / T, "unit": "iterations/s", "fit_transform_s": T, "iterations": n_iter,
+    return {"value": n_iter / T, "unit": "iterations/s", "fit_transform_s": T, "iterations": n_iter, "warmup_calls": 1,
             "h2d_bytes_per_step": (X.nbytes + Y0.nbytes) / n_iter, "d2h_bytes_per_step": Y0.nbytes / n_iter,
             "api": "tsne_cuda_b200.TSNE.fit_transform -> pymodule_tsne"}
 
@@ -203,25 +208,31 @@ def e2e_sharded(X, hp, Y0, args, rank, local_rank, world):
     import torch.distributed as dist
     from tsne_cuda_b200 import distributed
     n_iter = args.e2e_iters
+
+    def fit(iters):
+        s = distributed.open_session(X.shape[0], hp["num_neighbors"], rank, local_rank, world)
+        s.affinities_from_points(X, hp["perplexity"], 1e-3)
+        s.set_schedule(hp["learning_rate"], hp["early_exaggeration"], 250, 0.5, 0.8)
+        s.set_embedding(Y0)
+        s.run(iters)
+        y = s.get_embedding()
+        dist.barrier()
+        s.close()
+        return y
+
+    fit(20)   # one untimed call, as on a single GPU
     dist.barrier()
     torch.cuda.synchronize()
     t0 = time.time()
-    s = distributed.open_session(X.shape[0], hp["num_neighbors"], rank, local_rank, world)
-    s.affinities_from_points(X, hp["perplexity"], 1e-3)
-    s.set_schedule(hp["learning_rate"], hp["early_exaggeration"], 250, 0.5, 0.8)
-    s.set_embedding(Y0)
-    s.run(n_iter)
-    Y = s.get_embedding()
-    dist.barrier()
+    Y = fit(n_iter)
     T = time.time() - t0
-    s.close()
     t = torch.tensor([T], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     T = float(t.item())
     assert np.isfinite(Y).all()
     return {"value": n_iter / T, "unit": "iterations/s", "fit_transform_s": T, "iterations": n_iter,
             "h2d_bytes_per_step": (X.nbytes + Y0.nbytes) / n_iter, "d2h_bytes_per_step": Y0.nbytes / n_iter,
-            "api": "b200tsne_session_* on every rank"}
+            "warmup_calls": 1, "api": "b200tsne_session_* on every rank"}
 
 
 def cpu_baseline(X, hp, Y0, args, budget_s=20.0):

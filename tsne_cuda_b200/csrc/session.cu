@@ -73,6 +73,7 @@ int Session::init(int64_t N_, int K_, int64_t lo, int64_t hi, int device_)
     B200_TRY(arena.alloc((void **)&box_hist, sizeof(int32_t) * kBoxes * kBoxes));
     B200_TRY(launch_order_identity(order, rows(), stream));
     if (const char *e = getenv("B200TSNE_ORDER_REFRESH")) order_refresh = atoi(e);
+    if (const char *e = getenv("B200TSNE_ORDER_REFRESH_EARLY")) order_refresh_early = std::max(1, atoi(e));
     B200_TRY(arena.alloc((void **)&Y2, sizeof(float2) * npad));
     B200_TRY(arena.alloc((void **)&Fattr, sizeof(float2) * npad));
     B200_TRY(arena.alloc((void **)&Frep, sizeof(float2) * npad));
@@ -193,7 +194,7 @@ int Session::one_iteration(bool want_norm)
     // The embedding reshuffles quickly while it is being exaggerated and slowly afterwards: sort every
     // iteration early, every order_refresh iterations later.
     const bool settling = step < force_magnify_iters + 50;
-    if (order_refresh > 0 && (settling || step % order_refresh == 0)) {
+    if (order_refresh > 0 && step % (settling ? order_refresh_early : order_refresh) == 0) {
         clk.begin(stream);
         B200_TRY(launch_order_refresh(Y2, row_lo, row_hi, order, order_alt, order_keys, box_hist, state, slot, stream));
         std::swap(order, order_alt);

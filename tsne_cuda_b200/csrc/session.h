@@ -41,6 +41,7 @@ struct Session {
     float2 *u = nullptr;      // [rows]
     float *soa_tmp = nullptr; // [2N] staging for SoA <-> AoS conversion
     int32_t *order = nullptr, *order_alt = nullptr, *order_keys = nullptr, *box_hist = nullptr;  // spread order (owned rows)
+    int order_refresh_early = 1;  // the same while the embedding is still being exaggerated (and 50 iterations after)
     int order_refresh = 8;    // iterations between two counting sorts of the spread order once the embedding has settled (0 = natural order)
     // grid
     float4 *w = nullptr;      // [G][G]
