@@ -146,40 +146,77 @@ __device__ __forceinline__ int axis_box(float c, const GridGeom &g)
     return min(kBoxes - 1, idx);
 }
 
+// A lane takes kSpreadPerLane consecutive points of the order.  While they stay in one box it sums their 36
+// contributions in registers; a box change inside the lane sends the finished sum to the grid directly.  The
+// lane's last (open) run is then combined with those of its neighbours as described above, so the 180
+// shuffles of the segmented reduction are paid once per 32 * kSpreadPerLane points.
+constexpr int kSpreadPerLane = 4;
+
+__device__ __forceinline__ void spread_flush(float4 *__restrict__ w, int bx, int by, const float (&v)[kInterp][kInterp][4])
+{
+#pragma unroll
+    for (int a = 0; a < kInterp; a++)
+#pragma unroll
+        for (int b = 0; b < kInterp; b++) {
+            float4 *dst = w + (size_t)(bx * kInterp + a) * kG + (by * kInterp + b);
+            atomicAdd(dst, make_float4(v[a][b][0], v[a][b][1], v[a][b][2], v[a][b][3]));
+        }
+}
+
 __global__ void __launch_bounds__(256)
 spread_kernel(const float2 *__restrict__ Y2, long long row_lo, long long n_rows, const int32_t *__restrict__ order,
               const IterState *state, int slot, InterpConsts ic, float4 *__restrict__ w)
 {
-    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long t0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * kSpreadPerLane;
     const int lane = threadIdx.x & 31;
-    const bool valid = t < n_rows;
     const GridGeom g = load_geom(state, slot);
     int key = -1, bx = 0, by = 0;
     float v[kInterp][kInterp][4];
-    if (valid) {
-        const long long r = order ? (long long)order[t] : t;
-        const float2 y = Y2[row_lo + r];
+#pragma unroll
+    for (int a = 0; a < kInterp; a++)
+#pragma unroll
+        for (int b = 0; b < kInterp; b++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) v[a][b][c] = 0.0f;
+    // all loads of the lane first: they are independent of each other
+    float2 ys[kSpreadPerLane];
+#pragma unroll
+    for (int p = 0; p < kSpreadPerLane; p++) {
+        const long long t = t0 + p;
+        if (t < n_rows) {
+            const long long r = order ? (long long)order[t] : t;
+            ys[p] = Y2[row_lo + r];
+        }
+    }
+#pragma unroll
+    for (int p = 0; p < kSpreadPerLane; p++) {
+        if (t0 + p >= n_rows) break;
+        const float2 y = ys[p];
+        int kx, ky;
         float Lx[kInterp], Ly[kInterp];
-        axis_weights(y.x, g, ic, bx, Lx);
-        axis_weights(y.y, g, ic, by, Ly);
-        key = by * kBoxes + bx;
+        axis_weights(y.x, g, ic, kx, Lx);
+        axis_weights(y.y, g, ic, ky, Ly);
+        const int k = ky * kBoxes + kx;
+        if (k != key && key >= 0) {
+            spread_flush(w, bx, by, v);
+#pragma unroll
+            for (int a = 0; a < kInterp; a++)
+#pragma unroll
+                for (int b = 0; b < kInterp; b++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++) v[a][b][c] = 0.0f;
+        }
+        key = k; bx = kx; by = ky;
         const float c3 = y.x * y.x + y.y * y.y;
 #pragma unroll
         for (int a = 0; a < kInterp; a++)
 #pragma unroll
             for (int b = 0; b < kInterp; b++) {
                 const float l = Lx[a] * Ly[b];
-                v[a][b][0] = l * y.x; v[a][b][1] = l * y.y; v[a][b][2] = l; v[a][b][3] = l * c3;  // (x, y, count, r^2)
+                v[a][b][0] += l * y.x; v[a][b][1] += l * y.y; v[a][b][2] += l; v[a][b][3] += l * c3;  // (x, y, count, r^2)
             }
-    } else {
-#pragma unroll
-        for (int a = 0; a < kInterp; a++)
-#pragma unroll
-            for (int b = 0; b < kInterp; b++)
-#pragma unroll
-                for (int c = 0; c < 4; c++) v[a][b][c] = 0.0f;
     }
-    // runs of equal keys among neighbouring lanes
+    // runs of equal keys among neighbouring lanes (their open runs)
     const int prev = __shfl_up_sync(0xffffffffu, key, 1);
     const bool head = (lane == 0) || (key != prev);
     const unsigned heads = __ballot_sync(0xffffffffu, head);
@@ -200,15 +237,7 @@ spread_kernel(const float2 *__restrict__ Y2, long long row_lo, long long n_rows,
                     }
         }
     }
-    if (head && key >= 0) {
-#pragma unroll
-        for (int a = 0; a < kInterp; a++)
-#pragma unroll
-            for (int b = 0; b < kInterp; b++) {
-                float4 *dst = w + (size_t)(bx * kInterp + a) * kG + (by * kInterp + b);
-                atomicAdd(dst, make_float4(v[a][b][0], v[a][b][1], v[a][b][2], v[a][b][3]));
-            }
-    }
+    if (head && key >= 0) spread_flush(w, bx, by, v);
 }
 
 // ---- counting sort of the owned points by box (order[t] = local row index) ----
@@ -218,46 +247,79 @@ __global__ void order_identity_kernel(int32_t *order, long long n)
     if (t < n) order[t] = (int32_t)t;
 }
 
-// keys[t] = box of point order[t]; hist[box] += 1 (one atomic per group of equal keys in a warp)
+// Both passes of the counting sort give a thread kOrderPerThread consecutive entries of the previous order,
+// so that it has that many independent loads and atomics in flight (a pass is a chain of dependent L2
+// round trips).  Atomics are combined across the warp: for each of its entries in turn, the lanes that
+// hold the same key elect a leader that adds their number.  The points of a box are (nearly) contiguous in
+// the previous order, so a warp sees few distinct keys.
+constexpr int kOrderPerThread = 4;
+
+__device__ __forceinline__ int point_key(const float2 *__restrict__ Y2, long long row, const GridGeom &g)
+{
+    const float2 y = Y2[row];
+    return axis_box(y.y, g) * kBoxes + axis_box(y.x, g);
+}
+
+// keys[t] = box of point order[t]; hist[box] += 1
 __global__ void __launch_bounds__(256)
 order_histogram_kernel(const float2 *__restrict__ Y2, long long row_lo, long long n_rows, const int32_t *__restrict__ order,
                        const IterState *state, int slot, int32_t *__restrict__ keys, int32_t *__restrict__ hist)
 {
-    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long t0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * kOrderPerThread;
     const int lane = threadIdx.x & 31;
-    int key = -1;
-    if (t < n_rows) {
-        const GridGeom g = load_geom(state, slot);
-        const float2 y = Y2[row_lo + order[t]];
-        key = axis_box(y.y, g) * kBoxes + axis_box(y.x, g);
-        keys[t] = key;
+    const GridGeom g = load_geom(state, slot);
+    int k[kOrderPerThread] = {-1, -1, -1, -1};
+    if (t0 + kOrderPerThread <= n_rows) {
+        const int4 o = *reinterpret_cast<const int4 *>(order + t0);
+        k[0] = point_key(Y2, row_lo + o.x, g);
+        k[1] = point_key(Y2, row_lo + o.y, g);
+        k[2] = point_key(Y2, row_lo + o.z, g);
+        k[3] = point_key(Y2, row_lo + o.w, g);
+        *reinterpret_cast<int4 *>(keys + t0) = make_int4(k[0], k[1], k[2], k[3]);
+    } else {
+#pragma unroll
+        for (int p = 0; p < kOrderPerThread; p++)
+            if (t0 + p < n_rows) {
+                k[p] = point_key(Y2, row_lo + order[t0 + p], g);
+                keys[t0 + p] = k[p];
+            }
     }
-    const unsigned same = __match_any_sync(0xffffffffu, key);
-    if (key >= 0 && lane == __ffs(same) - 1) atomicAdd(hist + key, __popc(same));
+#pragma unroll
+    for (int p = 0; p < kOrderPerThread; p++) {
+        const unsigned same = __match_any_sync(0xffffffffu, k[p]);
+        if (k[p] >= 0 && lane == __ffs(same) - 1) atomicAdd(hist + k[p], __popc(same));
+    }
 }
 
-// exclusive scan of the kBoxes^2 counters in place (one block: serial within a thread, shuffles within
-// a warp, one pass over the 32 warp totals)
+// exclusive scan of the kBoxes^2 counters in place: one block, warp w owns the contiguous bins
+// [w * kPerWarp, (w + 1) * kPerWarp) and walks them 32 at a time (coalesced), carrying its running total;
+// one pass over the 32 warp totals gives every warp its offset
 __global__ void __launch_bounds__(1024) order_scan_kernel(int32_t *hist)
 {
     constexpr int kBins = kBoxes * kBoxes;
-    constexpr int kPer = (kBins + 1023) / 1024;
+    constexpr int kPerWarp = (kBins + 31) / 32;
+    constexpr int kRounds = (kPerWarp + 31) / 32;
     __shared__ int warp_tot[32];
     const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
-    const int base = threadIdx.x * kPer;
-    int local[kPer], sum = 0;
+    int v[kRounds], excl[kRounds];
 #pragma unroll
-    for (int k = 0; k < kPer; k++) {
-        local[k] = (base + k < kBins) ? hist[base + k] : 0;
-        sum += local[k];
+    for (int j = 0; j < kRounds; j++) {
+        const int off = j * 32 + lane, idx = wi * kPerWarp + off;
+        v[j] = (off < kPerWarp && idx < kBins) ? hist[idx] : 0;
     }
-    int incl = sum;
+    int carry = 0;
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        const int o = __shfl_up_sync(0xffffffffu, incl, d);
-        if (lane >= d) incl += o;
+    for (int j = 0; j < kRounds; j++) {
+        int incl = v[j];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += o;
+        }
+        excl[j] = carry + incl - v[j];
+        carry += __shfl_sync(0xffffffffu, incl, 31);
     }
-    if (lane == 31) warp_tot[wi] = incl;
+    if (lane == 0) warp_tot[wi] = carry;
     __syncthreads();
     if (wi == 0) {
         int t = warp_tot[lane];
@@ -269,11 +331,11 @@ __global__ void __launch_bounds__(1024) order_scan_kernel(int32_t *hist)
         warp_tot[lane] = t;   // inclusive totals of the warps
     }
     __syncthreads();
-    int run = incl - sum + (wi > 0 ? warp_tot[wi - 1] : 0);
+    const int offset = wi > 0 ? warp_tot[wi - 1] : 0;
 #pragma unroll
-    for (int k = 0; k < kPer; k++) {
-        if (base + k < kBins) hist[base + k] = run;
-        run += local[k];
+    for (int j = 0; j < kRounds; j++) {
+        const int off = j * 32 + lane, idx = wi * kPerWarp + off;
+        if (off < kPerWarp && idx < kBins) hist[idx] = excl[j] + offset;
     }
 }
 
@@ -281,15 +343,32 @@ __global__ void __launch_bounds__(256)
 order_scatter_kernel(const int32_t *__restrict__ order_in, const int32_t *__restrict__ keys, long long n_rows,
                      int32_t *__restrict__ cursor, int32_t *__restrict__ order_out)
 {
-    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long t0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * kOrderPerThread;
     const int lane = threadIdx.x & 31;
-    const int key = (t < n_rows) ? keys[t] : -1;
-    const unsigned same = __match_any_sync(0xffffffffu, key);
-    const int leader = __ffs(same) - 1;
-    int basepos = 0;
-    if (key >= 0 && lane == leader) basepos = atomicAdd(cursor + key, __popc(same));
-    basepos = __shfl_sync(0xffffffffu, basepos, leader);
-    if (key >= 0) order_out[basepos + __popc(same & ((1u << lane) - 1u))] = order_in[t];
+    int k[kOrderPerThread] = {-1, -1, -1, -1}, o[kOrderPerThread] = {0, 0, 0, 0};
+    if (t0 + kOrderPerThread <= n_rows) {
+        const int4 kk = *reinterpret_cast<const int4 *>(keys + t0);
+        const int4 oo = *reinterpret_cast<const int4 *>(order_in + t0);
+        k[0] = kk.x; k[1] = kk.y; k[2] = kk.z; k[3] = kk.w;
+        o[0] = oo.x; o[1] = oo.y; o[2] = oo.z; o[3] = oo.w;
+    } else {
+#pragma unroll
+        for (int p = 0; p < kOrderPerThread; p++)
+            if (t0 + p < n_rows) { k[p] = keys[t0 + p]; o[p] = order_in[t0 + p]; }
+    }
+    unsigned same[kOrderPerThread];
+    int base[kOrderPerThread];
+#pragma unroll
+    for (int p = 0; p < kOrderPerThread; p++) {   // all the atomics first: their round trips overlap
+        same[p] = __match_any_sync(0xffffffffu, k[p]);
+        base[p] = 0;
+        if (k[p] >= 0 && lane == __ffs(same[p]) - 1) base[p] = atomicAdd(cursor + k[p], __popc(same[p]));
+    }
+#pragma unroll
+    for (int p = 0; p < kOrderPerThread; p++) {
+        const int b = __shfl_sync(0xffffffffu, base[p], __ffs(same[p]) - 1);
+        if (k[p] >= 0) order_out[b + __popc(same[p] & ((1u << lane) - 1u))] = o[p];
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -662,7 +741,7 @@ int launch_spread(const float2 *Y2, int64_t row_lo, int64_t row_hi, const int32_
 {
     const long long n = row_hi - row_lo;
     if (n <= 0) return 0;
-    spread_kernel<<<nblk(n, 256), 256, 0, st>>>(Y2, row_lo, n, order, state, slot, ic, w);
+    spread_kernel<<<nblk((n + kSpreadPerLane - 1) / kSpreadPerLane, 256), 256, 0, st>>>(Y2, row_lo, n, order, state, slot, ic, w);
     B200_CUDA(cudaGetLastError());
     return 0;
 }
@@ -683,11 +762,12 @@ int launch_order_refresh(const float2 *Y2, int64_t row_lo, int64_t row_hi, const
     const long long n = row_hi - row_lo;
     if (n <= 0) return 0;
     B200_CUDA(cudaMemsetAsync(hist, 0, sizeof(int32_t) * kBoxes * kBoxes, st));
-    order_histogram_kernel<<<nblk(n, 256), 256, 0, st>>>(Y2, row_lo, n, order_in, state, slot, keys, hist);
+    const long long n_thr = (n + kOrderPerThread - 1) / kOrderPerThread;
+    order_histogram_kernel<<<nblk(n_thr, 256), 256, 0, st>>>(Y2, row_lo, n, order_in, state, slot, keys, hist);
     B200_CUDA(cudaGetLastError());
     order_scan_kernel<<<1, 1024, 0, st>>>(hist);
     B200_CUDA(cudaGetLastError());
-    order_scatter_kernel<<<nblk(n, 256), 256, 0, st>>>(order_in, keys, n, hist, order_out);
+    order_scatter_kernel<<<nblk(n_thr, 256), 256, 0, st>>>(order_in, keys, n, hist, order_out);
     B200_CUDA(cudaGetLastError());
     return 0;
 }
