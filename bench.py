@@ -209,15 +209,23 @@ def e2e_sharded(X, hp, Y0, args, rank, local_rank, world):
     from tsne_cuda_b200 import distributed
     n_iter = args.e2e_iters
 
+    phases = {}
+
     def fit(iters):
+        t = [time.time()]
         s = distributed.open_session(X.shape[0], hp["num_neighbors"], rank, local_rank, world)
+        t.append(time.time())
         s.affinities_from_points(X, hp["perplexity"], 1e-3)
+        t.append(time.time())
         s.set_schedule(hp["learning_rate"], hp["early_exaggeration"], 250, 0.5, 0.8)
         s.set_embedding(Y0)
         s.run(iters)
+        t.append(time.time())
         y = s.get_embedding()
         dist.barrier()
         s.close()
+        t.append(time.time())
+        phases.update(open_s=t[1] - t[0], affinities_s=t[2] - t[1], iterations_s=t[3] - t[2], fetch_close_s=t[4] - t[3])
         return y
 
     fit(20)   # one untimed call, as on a single GPU
@@ -232,7 +240,7 @@ def e2e_sharded(X, hp, Y0, args, rank, local_rank, world):
     assert np.isfinite(Y).all()
     return {"value": n_iter / T, "unit": "iterations/s", "fit_transform_s": T, "iterations": n_iter,
             "h2d_bytes_per_step": (X.nbytes + Y0.nbytes) / n_iter, "d2h_bytes_per_step": Y0.nbytes / n_iter,
-            "warmup_calls": 1, "api": "b200tsne_session_* on every rank"}
+            "warmup_calls": 1, "phases_rank0": phases, "api": "b200tsne_session_* on every rank"}
 
 
 def cpu_baseline(X, hp, Y0, args, budget_s=20.0):

@@ -207,6 +207,13 @@ int64_t b200tsne_session_launch_count(b200tsne_session *s);
 int b200tsne_comm_unique_id(void *id128);
 int b200tsne_session_attach_comm(b200tsne_session *s, const void *id128, int rank, int world_size);
 void b200tsne_comm_release_all(void);
+/* How the session exchanges data per iteration: 0 = single GPU, nothing to exchange; 1 = NCCL collectives
+ * (grid all-reduce, normalisation all-reduce, embedding all-gather); 2 = peer memory: the ranks map each
+ * other's buffers (CUDA IPC), sum the partial grids with peer loads, evaluate the normalisation on the
+ * summed grid and store updated rows into every rank's embedding.  attach_comm selects 2 when every rank
+ * could map all others and the environment does not say B200TSNE_EXCHANGE=nccl (set alike on all
+ * ranks).  With mode 2, destroying the session is collective: all ranks must call it. */
+int b200tsne_session_exchange_mode(b200tsne_session *s);
 
 #ifdef __cplusplus
 }

@@ -19,16 +19,17 @@ def _free_port():
     return p
 
 
-def _rank(rank, world, port, X, Y0, K, knn_shard, out):
+def _rank(rank, world, port, X, Y0, K, knn_shard, exchange, out):
     import torch
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
-                      B200TSNE_KNN_SHARD=knn_shard)
+                      B200TSNE_KNN_SHARD=knn_shard, B200TSNE_EXCHANGE=exchange)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world)
     from tsne_cuda_b200 import distributed
     try:
         s = distributed.open_session(X.shape[0], K, rank, rank, world)
+        mode = s.exchange_mode()
         s.affinities_from_points(X, 20.0, 1e-4)
         P, ids = s.get_affinities()
         s.set_schedule(200.0, 12.0, 250, 0.5, 0.8)
@@ -39,7 +40,7 @@ def _rank(rank, world, port, X, Y0, K, knn_shard, out):
         Y200 = s.get_embedding()
         st = s.stats()
         s.close()
-        out.put((rank, "ok", P, ids, Y1, Y200, st["Z"]))
+        out.put((rank, "ok", P, ids, Y1, Y200, mode))
     except Exception as e:  # report instead of leaving the peer in a collective
         out.put((rank, "FAILED: %r" % (e,), None, None, None, None, None))
     finally:
@@ -47,8 +48,8 @@ def _rank(rank, world, port, X, Y0, K, knn_shard, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("knn_shard", ["queries", "database"])
-def test_two_ranks_match_one(engine, oracle_cpu, knn_shard):
+@pytest.mark.parametrize("knn_shard,exchange", [("queries", "p2p"), ("queries", "nccl"), ("database", "p2p")])
+def test_two_ranks_match_one(engine, oracle_cpu, knn_shard, exchange):
     torch = pytest.importorskip("torch")
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
@@ -60,13 +61,14 @@ def test_two_ranks_match_one(engine, oracle_cpu, knn_shard):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank, args=(r, 2, port, X, Y0, K, knn_shard, q)) for r in range(2)]
+    procs = [ctx.Process(target=_rank, args=(r, 2, port, X, Y0, K, knn_shard, exchange, q)) for r in range(2)]
     for p in procs:
         p.start()
     res = sorted([q.get(timeout=300) for _ in procs], key=lambda t: t[0])
     for p in procs:
         p.join(timeout=60)
     assert [r[1] for r in res] == ["ok", "ok"], [r[1] for r in res]
+    assert [r[6] for r in res] == [2 if exchange == "p2p" else 1] * 2   # the exchange under test is the one that ran
     with engine.Session(N, K) as s:
         s.affinities_from_points(X, 20.0, 1e-4)
         P1, ids1 = s.get_affinities()

@@ -70,6 +70,7 @@ SIGNATURES = {
     "b200tsne_comm_unique_id": (C.c_int, [C.c_void_p]),
     "b200tsne_session_attach_comm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "b200tsne_comm_release_all": (None, []),
+    "b200tsne_session_exchange_mode": (C.c_int, [C.c_void_p]),
 }
 for _name, (_res, _args) in SIGNATURES.items():
     _fn = getattr(lib, _name)
@@ -271,6 +272,10 @@ class Session(object):
 
     def launch_count(self):
         return lib.b200tsne_session_launch_count(self._h)
+
+    def exchange_mode(self):
+        """0 single GPU, 1 NCCL collectives, 2 peer memory (see include/tsnecuda_b200.h)."""
+        return lib.b200tsne_session_exchange_mode(self._h)
 
     def attach_comm(self, unique_id, rank, world_size):
         buf = C.create_string_buffer(bytes(unique_id), 128)

@@ -193,7 +193,7 @@ int b200tsne_repulsive(const float *Y, int64_t N, float *Frep, float *Z, float *
     B200_TRY(launch_spread(dY2, 0, N, nullptr, st, 0, ic, dw, sg.st));
     if (w_out) B200_TRY(down(w_out, reinterpret_cast<float *>(dw), (size_t)kG * kG * 4, sg.st));
     B200_TRY(launch_convolve(dw, dyt, st, 0, ws, false, sg.st));
-    B200_TRY(launch_gather(dY2, 0, N, st, 0, ic, dyt, dF2, sg.st));
+    B200_TRY(launch_gather(dY2, 0, N, st, 0, ic, dyt, dF2, true, sg.st));
     B200_TRY(launch_aos_to_soa(dF2, dF, N, sg.st));
     B200_TRY(down(Frep, dF, (size_t)2 * N, sg.st));
     if (ytilde_out) B200_TRY(down(ytilde_out, reinterpret_cast<float *>(dyt), (size_t)kG * kG * 4, sg.st));
@@ -377,9 +377,16 @@ int b200tsne_session_attach_comm(b200tsne_session *h, const void *id128, int ran
         return B200TSNE_ERR_INVALID;
     }
     B200_CUDA(cudaSetDevice(s.device));
-    return comm_acquire(&s.comm, id128, rank, world_size);
+    B200_TRY(comm_acquire(&s.comm, id128, rank, world_size));
+    return s.attach_peer_exchange();
 }
 
 void b200tsne_comm_release_all(void) { comm_release_all(); }
+
+int b200tsne_session_exchange_mode(b200tsne_session *h)
+{
+    if (!h || !h->s.comm || h->s.comm->world < 2) return 0;
+    return h->s.px ? 2 : 1;
+}
 
 }  // extern "C"

@@ -1,4 +1,5 @@
 #include "comm.h"
+#include "peer.h"
 
 #include <dlfcn.h>
 #include <string.h>
@@ -126,7 +127,11 @@ int comm_acquire(Comm **out, const void *id128, int rank, int world)
 void comm_release_all()
 {
     std::lock_guard<std::mutex> lock(g_cache_mutex);
-    for (Cached &c : g_cache) { c.comm->destroy(); delete c.comm; }
+    for (Cached &c : g_cache) {
+        if (c.comm->px_idle) { peer_exchange_destroy(c.comm->px_idle, c.comm, nullptr); c.comm->px_idle = nullptr; }
+        c.comm->destroy();
+        delete c.comm;
+    }
     g_cache.clear();
 }
 

@@ -8,9 +8,15 @@
 
 namespace b200 {
 
+struct PeerExchange;   // peer.h
+
 struct Comm {
     void *nccl = nullptr;   // ncclComm_t
     int rank = 0, world = 1;
+    // Mapping the peers' memory costs hundreds of milliseconds (the first mapping enables peer access), so
+    // the exchange block of the last sharded session stays with the communicator and the next session of
+    // the same size takes it over.
+    PeerExchange *px_idle = nullptr;
     int all_reduce_sum_f32(float *buf, size_t n, cudaStream_t st);
     int all_reduce_sum_f64(double *buf, size_t n, cudaStream_t st);
     int all_reduce_max_u32(unsigned int *buf, size_t n, cudaStream_t st);

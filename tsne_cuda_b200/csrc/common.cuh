@@ -129,12 +129,19 @@ int launch_order_refresh(const float2 *Y2, int64_t row_lo, int64_t row_hi, const
                          int32_t *keys, int32_t *hist, const IterState *state, int slot, cudaStream_t st);
 int launch_convolve(float4 *w, float4 *ytilde, const IterState *state, int slot, const FftWorkspace &ws, bool zero_w,
                     cudaStream_t st);
+// sum_z: add the rows' Z_i to state->zsum[slot] (off when the caller evaluates the sum on the grid)
 int launch_gather(const float2 *Y2, int64_t row_lo, int64_t row_hi, IterState *state, int slot, InterpConsts ic,
-                  const float4 *ytilde, float2 *Frep2, cudaStream_t st);
+                  const float4 *ytilde, float2 *Frep2, bool sum_z, cudaStream_t st);
 
 // update.cu
-int launch_update(float2 *Y2, const float2 *Fattr2, const float2 *Frep2, float2 *gains2, float2 *u2, int64_t N,
-                  int64_t row_lo, int64_t row_hi, IterState *state, int slot, float eta, float momentum,
+// where the updated rows go: one array (in place) or the embedding copy of every rank (peer memory)
+constexpr int kMaxUpdateTargets = 16;
+struct UpdateTargets {
+    float2 *p[kMaxUpdateTargets];
+    int n;
+};
+int launch_update(const float2 *Y2, const UpdateTargets &dst, const float2 *Fattr2, const float2 *Frep2, float2 *gains2, float2 *u2,
+                  int64_t N, int64_t row_lo, int64_t row_hi, IterState *state, int slot, float eta, float momentum,
                   float exaggeration, int want_norm, cudaStream_t st);
 int launch_apply_forces_soa(float *Y, float *attr, float *rep, float *gains, float *old_forces, float eta, float Z,
                             float momentum, float exaggeration, int64_t N, cudaStream_t st);

@@ -1,0 +1,261 @@
+#include "peer.h"
+
+#include <string.h>
+#include <time.h>
+
+#include <string>
+#include <vector>
+
+#include "comm.h"
+
+namespace b200 {
+
+namespace {
+constexpr size_t kAlign = 256;
+size_t round_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+struct Layout {
+    size_t w[2], y[2], flags, total;
+};
+Layout block_layout(int64_t npad)
+{
+    Layout l;
+    size_t o = 0;
+    for (int b = 0; b < 2; b++) { l.w[b] = o; o += round_up(sizeof(float4) * (size_t)kG * kG); }
+    for (int b = 0; b < 2; b++) { l.y[b] = o; o += round_up(sizeof(float2) * (size_t)npad); }
+    l.flags = o;
+    o += round_up(sizeof(unsigned int) * 2 * kMaxPeers);
+    l.total = o;
+    return l;
+}
+
+__device__ __forceinline__ unsigned long long peer_global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// one warp: lane r publishes `value` in this rank's slot of rank r's flag array
+__global__ void peer_signal_kernel(PeerTable tab, int kind, unsigned int value)
+{
+    __threadfence_system();   // everything this stream wrote before (kernel boundary) is ordered before the flag
+    const int lane = threadIdx.x;
+    if (lane < tab.world) {
+        unsigned int *f = tab.flags[lane] + kind * kMaxPeers + tab.rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(value) : "memory");
+    }
+}
+
+// one warp: lane r waits until rank r's slot of the local flag array has reached `value`; gives up after 2 s
+__global__ void peer_wait_kernel(const unsigned int *flags, int kind, int world, unsigned int value, int *err)
+{
+    const int lane = threadIdx.x;
+    if (lane < world) {
+        const unsigned int *f = flags + kind * kMaxPeers + lane;
+        const unsigned long long t0 = peer_global_ns();
+        int spins = 0;
+        for (;;) {
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if ((int)(v - value) >= 0) break;
+            if ((++spins & 255) == 0 && peer_global_ns() - t0 > 2000000000ull) {
+                atomicExch(err, 1);
+                break;
+            }
+        }
+    }
+    __syncwarp();
+    __threadfence_system();
+}
+
+struct GridSources {
+    const float4 *p[kMaxPeers];
+    int world;
+};
+
+__global__ void __launch_bounds__(256)
+peer_grid_reduce_kernel(GridSources src, float4 *__restrict__ w_sum)
+{
+    const int n = kG * kG;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        float4 v[kMaxPeers];
+#pragma unroll
+        for (int s = 0; s < kMaxPeers; s++)
+            if (s < src.world) v[s] = src.p[s][i];   // all loads first: the peer round trips overlap
+        float4 acc = v[0];
+#pragma unroll
+        for (int s = 1; s < kMaxPeers; s++)
+            if (s < src.world) { acc.x += v[s].x; acc.y += v[s].y; acc.z += v[s].z; acc.w += v[s].w; }
+        w_sum[i] = acc;
+    }
+}
+
+// sum_i Z_i with Z_i = (1 + |y_i|^2) phi_count(y_i) - 2 (x_i phi_x(y_i) + y_i phi_y(y_i)) + phi_r2(y_i) and every
+// phi interpolated from the node potentials with the weights that spread the charges: summing over the
+// points first turns it into  sum_nodes  pot.count * (w.count + w.r2) - 2 (pot.x * w.x + pot.y * w.y) + pot.r2 * w.count.
+// Node layout (x, y, count, r^2) for charges and potentials alike.
+__global__ void __launch_bounds__(256)
+grid_z_kernel(const float4 *__restrict__ w_sum, const float4 *__restrict__ ytilde, IterState *state, int slot)
+{
+    const int n = kG * kG;
+    double z = 0.0;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float4 q = w_sum[i], p = ytilde[i];
+        z += (double)p.z * ((double)q.z + (double)q.w) - 2.0 * ((double)p.x * (double)q.x + (double)p.y * (double)q.y) +
+             (double)p.w * (double)q.z;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+    __shared__ double sz[8];
+    if ((threadIdx.x & 31) == 0) sz[threadIdx.x >> 5] = z;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int k = 0; k < 8; k++) t += sz[k];
+        atomicAdd(&state->zsum[slot], t);
+    }
+}
+}  // namespace
+
+void peer_exchange_release(PeerExchange *px, Comm *comm)
+{
+    if (!px) return;
+    if (comm && !comm->px_idle) comm->px_idle = px;   // every rank releases and acquires in the same order
+    else peer_exchange_destroy(px, comm, nullptr);
+}
+
+int peer_exchange_acquire(PeerExchange **out, Comm *comm, int64_t npad, cudaStream_t st)
+{
+    *out = nullptr;
+    if (!comm || comm->world < 2 || comm->world > kMaxPeers) return 0;
+    if (comm->px_idle) {
+        PeerExchange *idle = comm->px_idle;
+        comm->px_idle = nullptr;
+        if (idle->npad == npad) {
+            // the grids must start empty; nobody reads them before this rank's next spread signal
+            for (int b = 0; b < 2; b++) B200_CUDA(cudaMemsetAsync(idle->w_local(b), 0, sizeof(float4) * kG * kG, st));
+            *out = idle;
+            return 0;
+        }
+        peer_exchange_destroy(idle, comm, st);   // another problem size: all ranks get here together
+    }
+    const int W = comm->world, me = comm->rank;
+    const Layout lay = block_layout(npad);
+    PeerExchange *px = new PeerExchange();
+    px->npad = npad;
+    for (int r = 0; r < kMaxPeers; r++) px->mapped[r] = nullptr;
+    struct Fail { PeerExchange *px; bool armed = true; ~Fail() { if (armed) { if (px->local) cudaFree(px->local); if (px->err) cudaFree(px->err); delete px; } } } fail{px};
+    B200_CUDA(cudaMalloc(&px->local, lay.total));
+    B200_CUDA(cudaMalloc((void **)&px->err, sizeof(int) * 4));
+    B200_CUDA(cudaMemsetAsync(px->local, 0, lay.total, st));
+    B200_CUDA(cudaMemsetAsync(px->err, 0, sizeof(int) * 4, st));
+
+    // handles of all ranks, gathered through the communicator
+    cudaIpcMemHandle_t mine;
+    int local_fail = cudaIpcGetMemHandle(&mine, px->local) == cudaSuccess ? 0 : 1;
+    if (local_fail) { (void)cudaGetLastError(); memset(&mine, 0, sizeof(mine)); }
+    unsigned char *d_handles = nullptr;
+    B200_CUDA(cudaMalloc((void **)&d_handles, sizeof(cudaIpcMemHandle_t) * W + sizeof(unsigned int)));
+    struct FreeTmp { void *p; ~FreeTmp() { cudaFree(p); } } free_tmp{d_handles};
+    B200_CUDA(cudaMemcpyAsync(d_handles + sizeof(cudaIpcMemHandle_t) * me, &mine, sizeof(mine), cudaMemcpyHostToDevice, st));
+    B200_TRY(comm->all_gather_inplace(d_handles, sizeof(cudaIpcMemHandle_t), st));
+    std::vector<cudaIpcMemHandle_t> all(W);
+    B200_CUDA(cudaMemcpyAsync(all.data(), d_handles, sizeof(cudaIpcMemHandle_t) * W, cudaMemcpyDeviceToHost, st));
+    B200_CUDA(cudaStreamSynchronize(st));
+    for (int r = 0; r < W && !local_fail; r++) {
+        if (r == me) continue;
+        if (cudaIpcOpenMemHandle(&px->mapped[r], all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            (void)cudaGetLastError();
+            px->mapped[r] = nullptr;
+            local_fail = 1;
+        }
+    }
+    // all ranks take the same decision
+    unsigned int *d_flag = reinterpret_cast<unsigned int *>(d_handles + sizeof(cudaIpcMemHandle_t) * W);
+    unsigned int h_flag = (unsigned int)local_fail;
+    B200_CUDA(cudaMemcpyAsync(d_flag, &h_flag, sizeof(h_flag), cudaMemcpyHostToDevice, st));
+    B200_TRY(comm->all_reduce_max_u32(d_flag, 1, st));
+    B200_CUDA(cudaMemcpyAsync(&h_flag, d_flag, sizeof(h_flag), cudaMemcpyDeviceToHost, st));
+    B200_CUDA(cudaStreamSynchronize(st));
+    if (h_flag) {
+        for (int r = 0; r < W; r++)
+            if (px->mapped[r]) cudaIpcCloseMemHandle(px->mapped[r]);
+        return 0;   // `fail` frees the rest; the caller keeps the collectives
+    }
+    px->tab.world = W;
+    px->tab.rank = me;
+    for (int r = 0; r < kMaxPeers; r++) {
+        char *base = (r == me) ? static_cast<char *>(px->local) : (r < W ? static_cast<char *>(px->mapped[r]) : nullptr);
+        for (int b = 0; b < 2; b++) {
+            px->tab.w[b][r] = base ? reinterpret_cast<float4 *>(base + lay.w[b]) : nullptr;
+            px->tab.y[b][r] = base ? reinterpret_cast<float2 *>(base + lay.y[b]) : nullptr;
+        }
+        px->tab.flags[r] = base ? reinterpret_cast<unsigned int *>(base + lay.flags) : nullptr;
+    }
+    fail.armed = false;
+    *out = px;
+    return 0;
+}
+
+void peer_exchange_destroy(PeerExchange *px, Comm *comm, cudaStream_t st)
+{
+    if (!px) return;
+    cudaStreamSynchronize(st);
+    for (int r = 0; r < kMaxPeers; r++)
+        if (px->mapped[r]) cudaIpcCloseMemHandle(px->mapped[r]);
+    // Nobody may free a block that a peer still has mapped: meet the other ranks first.  The wait is
+    // bounded (10 s) so that a rank whose peer has died does not hang; it then leaks its block instead.
+    bool met = false;
+    if (comm) {
+        unsigned int *d = reinterpret_cast<unsigned int *>(px->err) + 1;
+        if (comm->all_reduce_max_u32(d, 1, st) == 0) {
+            for (int i = 0; i < 10000; i++) {
+                const cudaError_t q = cudaStreamQuery(st);
+                if (q == cudaSuccess) { met = true; break; }
+                if (q != cudaErrorNotReady) break;
+                struct timespec ts = {0, 1000000};
+                nanosleep(&ts, nullptr);
+            }
+        }
+        (void)cudaGetLastError();
+    }
+    if (met) {
+        cudaFree(px->local);
+        cudaFree(px->err);
+    }
+    delete px;
+}
+
+int launch_peer_signal(PeerExchange *px, int kind, unsigned int value, cudaStream_t st)
+{
+    peer_signal_kernel<<<1, 32, 0, st>>>(px->tab, kind, value);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_peer_wait(PeerExchange *px, int kind, unsigned int value, cudaStream_t st)
+{
+    peer_wait_kernel<<<1, 32, 0, st>>>(px->tab.flags[px->tab.rank], kind, px->tab.world, value, px->err);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_peer_grid_reduce(PeerExchange *px, int buf, float4 *w_sum, cudaStream_t st)
+{
+    GridSources src;
+    src.world = px->tab.world;
+    for (int r = 0; r < kMaxPeers; r++) src.p[r] = px->tab.w[buf][r];
+    peer_grid_reduce_kernel<<<148 * 2, 256, 0, st>>>(src, w_sum);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_grid_z(const float4 *w_sum, const float4 *ytilde, IterState *state, int slot, cudaStream_t st)
+{
+    grid_z_kernel<<<148, 256, 0, st>>>(w_sum, ytilde, state, slot);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace b200

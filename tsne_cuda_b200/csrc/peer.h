@@ -1,0 +1,71 @@
+// Per-iteration exchanges of a sharded run over peer memory (NVLink loads and stores issued by this
+// library's own kernels) instead of collectives.
+//
+// Every rank allocates one block with the same layout (two partial grids, two copies of the embedding,
+// flag words) and maps the blocks of all other ranks through CUDA IPC.  An iteration then needs
+//   * one reduction of the partial grids: each rank reads the W partial grids (its own and W - 1 peers')
+//     node by node in rank order and keeps the sum, so all ranks hold bit-identical grids;
+//   * no exchange for the normalisation: sum_i Z_i is a bilinear form of the summed grid and the
+//     potentials, which every rank evaluates locally;
+//   * no all-gather: the update kernel stores each new coordinate pair into the embedding copy of every
+//     rank.
+// Ranks meet twice per iteration ("all spreads done", "all updates done") through flag words: a one-warp
+// kernel stores the iteration's epoch into its slot of every rank's flag array (release, system scope),
+// another polls the local array until all slots carry it (acquire).  The polls are bounded (2 s); on
+// expiry an error word is set that the host reads when the run returns.
+//
+// Buffers are double-buffered by iteration parity so that a fast rank never overwrites what a slow rank
+// still reads: grid buffer b is written by the spread of iterations with parity b and read by the peers in
+// the same iteration; embedding buffer b is read in iterations with parity b and written, by all ranks,
+// in the iteration before.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+struct Comm;
+
+constexpr int kMaxPeers = 16;
+enum PeerFlag { kFlagSpread = 0, kFlagUpdate = 1 };
+
+// pointer table handed to kernels by value
+struct PeerTable {
+    int world, rank;
+    float4 *w[2][kMaxPeers];     // [buffer][rank] partial grids
+    float2 *y[2][kMaxPeers];     // [buffer][rank] embedding copies
+    unsigned int *flags[kMaxPeers];   // [rank] flag words: [kind * kMaxPeers + writer rank]
+};
+
+struct PeerExchange {
+    PeerTable tab;
+    void *local = nullptr;       // this rank's block
+    void *mapped[kMaxPeers];     // peers' blocks as mapped here (null for this rank)
+    int *err = nullptr;          // device word: a bounded wait expired
+    unsigned int epoch = 0;      // last epoch signalled (one per iteration, never reset)
+    int parity = 0;              // which of the two buffers holds the current embedding / grid (alike on all ranks)
+    int64_t npad = 0;
+
+    float4 *w_local(int b) { return tab.w[b][tab.rank]; }
+    float2 *y_local(int b) { return tab.y[b][tab.rank]; }
+};
+
+// Collective over the communicator: takes over the communicator's idle block if it has the right size, else
+// allocates, exchanges the IPC handles and maps the peers.  *out stays null (and 0 is returned) when any rank
+// could not map a peer; the caller then keeps using the collectives.
+int peer_exchange_acquire(PeerExchange **out, Comm *comm, int64_t npad, cudaStream_t st);
+// Hands the block back to the communicator (local; the mappings stay).
+void peer_exchange_release(PeerExchange *px, Comm *comm);
+// Collective: unmaps the peers, meets the other ranks, then frees the local block.
+void peer_exchange_destroy(PeerExchange *px, Comm *comm, cudaStream_t st);
+
+int launch_peer_signal(PeerExchange *px, int kind, unsigned int value, cudaStream_t st);
+int launch_peer_wait(PeerExchange *px, int kind, unsigned int value, cudaStream_t st);
+// w_sum[node] = sum over ranks (in rank order) of their partial grid `buf`
+int launch_peer_grid_reduce(PeerExchange *px, int buf, float4 *w_sum, cudaStream_t st);
+// state->zsum[slot] += sum over nodes of the bilinear form of charges w_sum and potentials ytilde
+int launch_grid_z(const float4 *w_sum, const float4 *ytilde, IterState *state, int slot, cudaStream_t st);
+
+}  // namespace b200

@@ -376,7 +376,7 @@ order_scatter_kernel(const int32_t *__restrict__ order_in, const int32_t *__rest
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 gather_kernel(const float2 *__restrict__ Y2, long long row_lo, long long n_rows, IterState *state, int slot,
-              InterpConsts ic, const float4 *__restrict__ ytilde, float2 *__restrict__ Frep2)
+              InterpConsts ic, const float4 *__restrict__ ytilde, float2 *__restrict__ Frep2, int sum_z)
 {
     const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     float zi = 0.0f;
@@ -410,7 +410,7 @@ gather_kernel(const float2 *__restrict__ Y2, long long row_lo, long long n_rows,
     if (threadIdx.x == 0) {
         double t = 0.0;
         for (int k = 0; k < 8; k++) t += sz[k];
-        atomicAdd(&state->zsum[slot], t);
+        if (sum_z) atomicAdd(&state->zsum[slot], t);
         if (blockIdx.x == 0) {  // recycle the other slot's min/max for this iteration's update
             state->min_enc[slot ^ 1] = 0xffffffffu;
             state->max_enc[slot ^ 1] = 0u;
@@ -787,11 +787,11 @@ int launch_convolve(float4 *w, float4 *ytilde, const IterState *state, int slot,
 }
 
 int launch_gather(const float2 *Y2, int64_t row_lo, int64_t row_hi, IterState *state, int slot, InterpConsts ic,
-                  const float4 *ytilde, float2 *Frep2, cudaStream_t st)
+                  const float4 *ytilde, float2 *Frep2, bool sum_z, cudaStream_t st)
 {
     const long long n = row_hi - row_lo;
     // an empty shard still runs one block: it recycles the other slot's min/max
-    gather_kernel<<<n > 0 ? nblk(n, 256) : 1, 256, 0, st>>>(Y2, row_lo, n, state, slot, ic, ytilde, Frep2);
+    gather_kernel<<<n > 0 ? nblk(n, 256) : 1, 256, 0, st>>>(Y2, row_lo, n, state, slot, ic, ytilde, Frep2, sum_z ? 1 : 0);
     B200_CUDA(cudaGetLastError());
     return 0;
 }

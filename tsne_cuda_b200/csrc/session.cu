@@ -17,6 +17,7 @@
 #include <string>
 
 #include "comm.h"
+#include "peer.h"
 
 namespace b200 {
 
@@ -86,6 +87,8 @@ int Session::init(int64_t N_, int K_, int64_t lo, int64_t hi, int device_)
     B200_TRY(arena.alloc((void **)&state, sizeof(IterState)));
     B200_CUDA(cudaMallocHost((void **)&h_state, sizeof(IterState)));
     B200_TRY(fft_workspace_init(&fft, fft_mem, stream));
+    Y2_own = Y2;
+    w_own = w;
     ic = make_interp_consts();
     B200_CUDA(cudaMemsetAsync(w, 0, sizeof(float4) * kG * kG, stream));
     B200_CUDA(cudaMemsetAsync(Y2, 0, sizeof(float2) * npad, stream));
@@ -103,6 +106,7 @@ void Session::destroy()
     cudaSetDevice(device);
     if (stream) cudaStreamSynchronize(stream);
     if (stream2) cudaStreamSynchronize(stream2);
+    if (px) { peer_exchange_release(px, comm); px = nullptr; }
     comm = nullptr;  // owned by the communicator cache (comm.h)
     arena.release();
     if (h_state) cudaFreeHost(h_state);
@@ -180,8 +184,16 @@ int Session::one_iteration(bool want_norm)
     const float momentum = late ? post_momentum : pre_momentum;
     const float exag = late ? 1.0f : exaggeration;
     const bool multi = comm && comm->world > 1;
+    const bool p2p = multi && px != nullptr;   // exchanges over peer memory instead of collectives
     StageClock clk(this);
     cudaStream_t sa = stage_timers ? stream : stream2;  // attractive stream
+    unsigned int epoch = 0;
+    if (p2p) {
+        epoch = ++px->epoch;
+        // the grid buffer of the next iteration: the peers finished reading it before they signalled the
+        // update this rank waited for at the end of the previous iteration
+        B200_CUDA(cudaMemsetAsync(px->w_local(px->parity ^ 1), 0, sizeof(float4) * kG * kG, stream));
+    }
 
     if (!stage_timers) {
         B200_CUDA(cudaEventRecord(ev_fork, stream));
@@ -203,18 +215,29 @@ int Session::one_iteration(bool want_norm)
     clk.begin(stream);
     B200_TRY(launch_spread(Y2, row_lo, row_hi, order_refresh > 0 ? order : nullptr, state, slot, ic, w, stream));
     clk.end(stream, kStSpread, 1);
-    if (multi) {
+    if (p2p) {
+        clk.begin(stream);
+        B200_TRY(launch_peer_signal(px, kFlagSpread, epoch, stream));
+        B200_TRY(launch_peer_wait(px, kFlagSpread, epoch, stream));
+        B200_TRY(launch_peer_grid_reduce(px, px->parity, w_sum, stream));
+        clk.end(stream, kStExchange, 3);
+    } else if (multi) {
         clk.begin(stream);
         B200_TRY(comm->all_reduce_sum_f32(reinterpret_cast<float *>(w), (size_t)kG * kG * 4, stream));
         clk.end(stream, kStExchange, 0);
     }
     clk.begin(stream);
-    B200_TRY(launch_convolve(w, ytilde, state, slot, fft, true, stream));
+    B200_TRY(launch_convolve(p2p ? w_sum : w, ytilde, state, slot, fft, !p2p, stream));
     clk.end(stream, kStConvolve, 3);
     clk.begin(stream);
-    B200_TRY(launch_gather(Y2, row_lo, row_hi, state, slot, ic, ytilde, Frep, stream));
+    B200_TRY(launch_gather(Y2, row_lo, row_hi, state, slot, ic, ytilde, Frep, !p2p, stream));
     clk.end(stream, kStGather, 1);
-    if (multi) {
+    if (p2p) {
+        // sum of Z_i over ALL points from the summed grid: no exchange
+        clk.begin(stream);
+        B200_TRY(launch_grid_z(w_sum, ytilde, state, slot, stream));
+        clk.end(stream, kStGather, 1);
+    } else if (multi) {
         clk.begin(stream);
         B200_TRY(comm->all_reduce_sum_f64(&state->zsum[slot], 1, stream));
         clk.end(stream, kStExchange, 0);
@@ -227,10 +250,26 @@ int Session::one_iteration(bool want_norm)
         B200_CUDA(cudaStreamWaitEvent(stream, ev_join, 0));
     }
     clk.begin(stream);
-    B200_TRY(launch_update(Y2, Fattr, Frep, gains, u, N, row_lo, row_hi, state, slot, eta, momentum, exag,
+    UpdateTargets dst;
+    dst.n = 1;
+    dst.p[0] = Y2;
+    if (p2p) {   // the new rows go straight into the next embedding buffer of every rank
+        dst.n = comm->world;
+        for (int r = 0; r < comm->world; r++) dst.p[r] = px->tab.y[px->parity ^ 1][r];
+    }
+    B200_TRY(launch_update(Y2, dst, Fattr, Frep, gains, u, N, row_lo, row_hi, state, slot, eta, momentum, exag,
                            want_norm ? 1 : 0, stream));
     clk.end(stream, kStUpdate, 1);
-    if (multi) {
+    if (p2p) {
+        clk.begin(stream);
+        B200_TRY(launch_peer_signal(px, kFlagUpdate, epoch, stream));
+        B200_TRY(launch_peer_wait(px, kFlagUpdate, epoch, stream));
+        px->parity ^= 1;
+        Y2 = px->y_local(px->parity);
+        w = px->w_local(px->parity);
+        B200_TRY(launch_minmax_init(Y2, N, state, slot ^ 1, stream));
+        clk.end(stream, kStExchange, 4);
+    } else if (multi) {
         clk.begin(stream);
         const int64_t chunk = (N + comm->world - 1) / comm->world;
         B200_TRY(comm->all_gather_inplace(Y2, sizeof(float2) * (size_t)chunk, stream));
@@ -276,6 +315,27 @@ int Session::iterate(int n_iters, float min_gradient_norm, float *elapsed_ms, in
     if (done > 0) last_Z = (float)h_state->zsum[(step - 1) & 1] - (float)N;
     if (want_norm && !early_stop && done > 0) last_unorm = (float)sqrt(h_state->unorm2);
     if (h_state->bad) { set_error("non-finite coordinates in the embedding"); return -3; }
+    if (px) {
+        int expired = 0;
+        B200_CUDA(cudaMemcpy(&expired, px->err, sizeof(int), cudaMemcpyDeviceToHost));
+        if (expired) { set_error("peer exchange: a rank did not arrive within 2 s"); return -5; }
+    }
+    return 0;
+}
+
+int Session::attach_peer_exchange()
+{
+    if (!comm || comm->world < 2 || px) return 0;
+    const char *e = getenv("B200TSNE_EXCHANGE");   // "nccl": collectives only (must be set alike on all ranks)
+    if (e && strcmp(e, "nccl") == 0) return 0;
+    B200_CUDA(cudaSetDevice(device));
+    B200_TRY(peer_exchange_acquire(&px, comm, N + 16, stream));
+    if (!px) return 0;
+    B200_TRY(arena.alloc((void **)&w_sum, sizeof(float4) * kG * kG));
+    B200_CUDA(cudaMemcpyAsync(px->y_local(px->parity), Y2_own, sizeof(float2) * (size_t)N, cudaMemcpyDeviceToDevice, stream));
+    B200_CUDA(cudaStreamSynchronize(stream));
+    Y2 = px->y_local(px->parity);
+    w = px->w_local(px->parity);
     return 0;
 }
 

@@ -8,7 +8,8 @@
 
 namespace b200 {
 
-struct Comm;  // comm.h
+struct Comm;          // comm.h
+struct PeerExchange;  // peer.h
 
 enum Stage { kStSpread = 0, kStConvolve, kStGather, kStAttractive, kStUpdate, kStExchange, kStKnn, kStAffinities, kStOrder };
 
@@ -67,6 +68,13 @@ struct Session {
 
     KnnStats knn_stats;    // of the last affinities_from_points
     Comm *comm = nullptr;  // null on a single GPU
+    // Sharded runs exchange over peer memory when every rank could map the others (peer.h); Y2 and w then
+    // point into the exchange block and alternate between its two buffers, w_sum holds the reduced grid.
+    PeerExchange *px = nullptr;
+    float2 *Y2_own = nullptr;   // the session's own allocations, used whenever px is null
+    float4 *w_own = nullptr;
+    float4 *w_sum = nullptr;
+    int attach_peer_exchange();   // collective, after comm is set
 
     int64_t rows() const { return row_hi - row_lo; }
     int init(int64_t N, int K, int64_t row_lo, int64_t row_hi, int device);

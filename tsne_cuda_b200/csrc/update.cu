@@ -28,12 +28,14 @@ __device__ __forceinline__ void step_point(float2 &y, const float2 fa, const flo
     y.y += u.y;
 }
 
-// Rows [row_lo, row_lo+n_rows) of the embedding are updated in place.  Reads the normalisation
+// Rows [row_lo, row_lo+n_rows) of the embedding are updated: read from Y2, written to every array of
+// `dst` (in place: Y2 itself; sharded over peer memory: the next embedding buffer of every rank, which
+// replaces an all-gather).  Reads the normalisation
 // from state->zsum[slot] (sum of Z_i; Z = sum - n_total as in src/kernels/rep_forces.cu:51-54),
 // accumulates min/max of the new coordinates into slot^1 and clears zsum[slot^1] for the next
 // iteration's gather.
 __global__ void __launch_bounds__(256)
-update_kernel(float2 *__restrict__ Y2, const float2 *__restrict__ Fa, const float2 *__restrict__ Fr,
+update_kernel(const float2 *Y2, UpdateTargets dst, const float2 *__restrict__ Fa, const float2 *__restrict__ Fr,
               float2 *__restrict__ gains, float2 *__restrict__ u2, long long row_lo, long long n_rows,
               long long n_total, IterState *state, int slot, float eta, float momentum, float exaggeration,
               int want_norm)
@@ -47,7 +49,9 @@ update_kernel(float2 *__restrict__ Y2, const float2 *__restrict__ Fa, const floa
         float2 y = Y2[i], g = gains[r], u = u2[r];
         const float2 fa = __ldcs(Fa + i), fr = __ldcs(Fr + i);
         step_point(y, fa, fr, g, u, eta, Z, momentum, exaggeration);
-        Y2[i] = y;
+#pragma unroll
+        for (int t = 0; t < kMaxUpdateTargets; t++)
+            if (t < dst.n) dst.p[t][i] = y;
         gains[r] = g;
         u2[r] = u;
         mn = fminf(y.x, y.y);
@@ -117,14 +121,14 @@ __global__ void fill_kernel(float *p, float v, long long n)
 inline unsigned nblk(long long n, int t) { return (unsigned)((n + t - 1) / t); }
 }  // namespace
 
-int launch_update(float2 *Y2, const float2 *Fattr2, const float2 *Frep2, float2 *gains2, float2 *u2, int64_t N,
-                  int64_t row_lo, int64_t row_hi, IterState *state, int slot, float eta, float momentum,
+int launch_update(const float2 *Y2, const UpdateTargets &dst, const float2 *Fattr2, const float2 *Frep2, float2 *gains2, float2 *u2,
+                  int64_t N, int64_t row_lo, int64_t row_hi, IterState *state, int slot, float eta, float momentum,
                   float exaggeration, int want_norm, cudaStream_t st)
 {
     const long long n_rows = row_hi - row_lo;
     // even an empty shard must run one block so that the state slots are recycled
     const unsigned blocks = n_rows > 0 ? nblk(n_rows, 256) : 1;
-    update_kernel<<<blocks, 256, 0, st>>>(Y2, Fattr2, Frep2, gains2, u2, row_lo, n_rows, N, state, slot, eta, momentum,
+    update_kernel<<<blocks, 256, 0, st>>>(Y2, dst, Fattr2, Frep2, gains2, u2, row_lo, n_rows, N, state, slot, eta, momentum,
                                           exaggeration, want_norm);
     B200_CUDA(cudaGetLastError());
     return 0;
