@@ -24,7 +24,7 @@ Layout block_layout(int64_t npad)
     for (int b = 0; b < 2; b++) { l.w[b] = o; o += round_up(sizeof(float4) * (size_t)kG * kG); }
     for (int b = 0; b < 2; b++) { l.y[b] = o; o += round_up(sizeof(float2) * (size_t)npad); }
     l.flags = o;
-    o += round_up(sizeof(unsigned int) * 2 * kMaxPeers);
+    o += round_up(sizeof(unsigned int) * 4 * kMaxPeers);   // epochs [2][ranks], min/max [ranks][2]
     l.total = o;
     return l;
 }
@@ -36,36 +36,60 @@ __device__ __forceinline__ unsigned long long peer_global_ns()
     return t;
 }
 
-// one warp: lane r publishes `value` in this rank's slot of rank r's flag array
-__global__ void peer_signal_kernel(PeerTable tab, int kind, unsigned int value)
+// Flag words of a rank: [kind][writer rank] epochs, then [writer rank][2] the writers' min/max encodings.
+constexpr int kMinMaxOffset = 2 * kMaxPeers;
+
+// One warp, one launch per meeting: lane r publishes `value` in this rank's slot of rank r's flag array, then
+// waits until rank r's slot of the local array has reached it; gives up after 2 s.  With `state` the ranks also
+// exchange the min/max of the rows they have just updated (IterState slot mm_slot) and leave the global
+// min/max there, which replaces a pass over the whole embedding.
+__global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int value, IterState *state, int mm_slot, int *err)
 {
-    __threadfence_system();   // everything this stream wrote before (kernel boundary) is ordered before the flag
     const int lane = threadIdx.x;
+    unsigned int my_min = 0, my_max = 0;
+    if (state) { my_min = state->min_enc[mm_slot]; my_max = state->max_enc[mm_slot]; }
+    __threadfence_system();   // everything this stream wrote before (kernel boundary) is ordered before the flag
     if (lane < tab.world) {
-        unsigned int *f = tab.flags[lane] + kind * kMaxPeers + tab.rank;
+        unsigned int *base = tab.flags[lane];
+        if (state) {
+            base[kMinMaxOffset + 2 * tab.rank] = my_min;
+            base[kMinMaxOffset + 2 * tab.rank + 1] = my_max;
+        }
+        unsigned int *f = base + kind * kMaxPeers + tab.rank;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(value) : "memory");
     }
-}
-
-// one warp: lane r waits until rank r's slot of the local flag array has reached `value`; gives up after 2 s
-__global__ void peer_wait_kernel(const unsigned int *flags, int kind, int world, unsigned int value, int *err)
-{
-    const int lane = threadIdx.x;
-    if (lane < world) {
-        const unsigned int *f = flags + kind * kMaxPeers + lane;
+    unsigned int mn = 0xffffffffu, mx = 0u;
+    if (lane < tab.world) {
+        const unsigned int *mine = tab.flags[tab.rank];
+        const unsigned int *f = mine + kind * kMaxPeers + lane;
         const unsigned long long t0 = peer_global_ns();
         int spins = 0;
+        bool ok = true;
         for (;;) {
             unsigned int v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
             if ((int)(v - value) >= 0) break;
             if ((++spins & 255) == 0 && peer_global_ns() - t0 > 2000000000ull) {
                 atomicExch(err, 1);
+                ok = false;
                 break;
             }
         }
+        if (state && ok) {
+            // written by rank `lane` before its release store, read after the acquire load that saw it
+            mn = *reinterpret_cast<const volatile unsigned int *>(mine + kMinMaxOffset + 2 * lane);
+            mx = *reinterpret_cast<const volatile unsigned int *>(mine + kMinMaxOffset + 2 * lane + 1);
+        }
     }
     __syncwarp();
+    if (state) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        if (lane == 0) { state->min_enc[mm_slot] = mn; state->max_enc[mm_slot] = mx; }
+    }
     __threadfence_system();
 }
 
@@ -227,16 +251,9 @@ void peer_exchange_destroy(PeerExchange *px, Comm *comm, cudaStream_t st)
     delete px;
 }
 
-int launch_peer_signal(PeerExchange *px, int kind, unsigned int value, cudaStream_t st)
+int launch_peer_barrier(PeerExchange *px, int kind, unsigned int value, IterState *state, int mm_slot, cudaStream_t st)
 {
-    peer_signal_kernel<<<1, 32, 0, st>>>(px->tab, kind, value);
-    B200_CUDA(cudaGetLastError());
-    return 0;
-}
-
-int launch_peer_wait(PeerExchange *px, int kind, unsigned int value, cudaStream_t st)
-{
-    peer_wait_kernel<<<1, 32, 0, st>>>(px->tab.flags[px->tab.rank], kind, px->tab.world, value, px->err);
+    peer_barrier_kernel<<<1, 32, 0, st>>>(px->tab, kind, value, state, mm_slot, px->err);
     B200_CUDA(cudaGetLastError());
     return 0;
 }

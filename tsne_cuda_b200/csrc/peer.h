@@ -10,9 +10,10 @@
 //   * no all-gather: the update kernel stores each new coordinate pair into the embedding copy of every
 //     rank.
 // Ranks meet twice per iteration ("all spreads done", "all updates done") through flag words: a one-warp
-// kernel stores the iteration's epoch into its slot of every rank's flag array (release, system scope),
-// another polls the local array until all slots carry it (acquire).  The polls are bounded (2 s); on
-// expiry an error word is set that the host reads when the run returns.
+// kernel stores the iteration's epoch into its slot of every rank's flag array (release, system scope) and
+// then polls the local array until all slots carry it (acquire).  The polls are bounded (2 s); on expiry
+// an error word is set that the host reads when the run returns.  The second meeting also carries the
+// min/max of each rank's new rows, so the bounding box of the next grid needs no pass over the embedding.
 //
 // Buffers are double-buffered by iteration parity so that a fast rank never overwrites what a slow rank
 // still reads: grid buffer b is written by the spread of iterations with parity b and read by the peers in
@@ -36,7 +37,7 @@ struct PeerTable {
     int world, rank;
     float4 *w[2][kMaxPeers];     // [buffer][rank] partial grids
     float2 *y[2][kMaxPeers];     // [buffer][rank] embedding copies
-    unsigned int *flags[kMaxPeers];   // [rank] flag words: [kind * kMaxPeers + writer rank]
+    unsigned int *flags[kMaxPeers];   // [rank] flag words: [kind * kMaxPeers + writer rank], then min/max per writer
 };
 
 struct PeerExchange {
@@ -61,8 +62,9 @@ void peer_exchange_release(PeerExchange *px, Comm *comm);
 // Collective: unmaps the peers, meets the other ranks, then frees the local block.
 void peer_exchange_destroy(PeerExchange *px, Comm *comm, cudaStream_t st);
 
-int launch_peer_signal(PeerExchange *px, int kind, unsigned int value, cudaStream_t st);
-int launch_peer_wait(PeerExchange *px, int kind, unsigned int value, cudaStream_t st);
+// All ranks meet: publish `value` for `kind` everywhere, wait (bounded) until every rank has.  With `state`, the
+// ranks' min/max encodings in IterState slot mm_slot are combined across the ranks on the way.
+int launch_peer_barrier(PeerExchange *px, int kind, unsigned int value, IterState *state, int mm_slot, cudaStream_t st);
 // w_sum[node] = sum over ranks (in rank order) of their partial grid `buf`
 int launch_peer_grid_reduce(PeerExchange *px, int buf, float4 *w_sum, cudaStream_t st);
 // state->zsum[slot] += sum over nodes of the bilinear form of charges w_sum and potentials ytilde

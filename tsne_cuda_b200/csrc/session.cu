@@ -217,10 +217,9 @@ int Session::one_iteration(bool want_norm)
     clk.end(stream, kStSpread, 1);
     if (p2p) {
         clk.begin(stream);
-        B200_TRY(launch_peer_signal(px, kFlagSpread, epoch, stream));
-        B200_TRY(launch_peer_wait(px, kFlagSpread, epoch, stream));
+        B200_TRY(launch_peer_barrier(px, kFlagSpread, epoch, nullptr, 0, stream));
         B200_TRY(launch_peer_grid_reduce(px, px->parity, w_sum, stream));
-        clk.end(stream, kStExchange, 3);
+        clk.end(stream, kStExchange, 2);
     } else if (multi) {
         clk.begin(stream);
         B200_TRY(comm->all_reduce_sum_f32(reinterpret_cast<float *>(w), (size_t)kG * kG * 4, stream));
@@ -262,13 +261,12 @@ int Session::one_iteration(bool want_norm)
     clk.end(stream, kStUpdate, 1);
     if (p2p) {
         clk.begin(stream);
-        B200_TRY(launch_peer_signal(px, kFlagUpdate, epoch, stream));
-        B200_TRY(launch_peer_wait(px, kFlagUpdate, epoch, stream));
+        // the update kernel left this rank's min/max in slot^1; the meeting makes them global
+        B200_TRY(launch_peer_barrier(px, kFlagUpdate, epoch, state, slot ^ 1, stream));
         px->parity ^= 1;
         Y2 = px->y_local(px->parity);
         w = px->w_local(px->parity);
-        B200_TRY(launch_minmax_init(Y2, N, state, slot ^ 1, stream));
-        clk.end(stream, kStExchange, 4);
+        clk.end(stream, kStExchange, 1);
     } else if (multi) {
         clk.begin(stream);
         const int64_t chunk = (N + comm->world - 1) / comm->world;
