@@ -50,6 +50,21 @@ def test_knn_tensor_core_matches_simt_everywhere(engine, monkeypatch):
     assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
 
 
+def test_knn_tensor_core_windows_and_cells(engine, monkeypatch):
+    """The fixed-threshold scans split into database windows (as for a database image much larger than L2), on
+    queries and database ranges that differ and are visited by cells: same lists as the SIMT search."""
+    from tsne_cuda_b200 import datasets
+    X = datasets.gaussian_mixture(150000, 24, seed=5)
+    monkeypatch.setenv("B200TSNE_KNN_WINDOW_TILES", "37")
+    a = engine.knn(X, 50, q_lo=1000, q_hi=40000, db_lo=5000, db_hi=149000)
+    assert engine.knn_last_stats()["tensor_core"] == 1
+    monkeypatch.delenv("B200TSNE_KNN_WINDOW_TILES")
+    monkeypatch.setenv("B200TSNE_KNN", "simt")
+    b = engine.knn(X, 50, q_lo=1000, q_hi=40000, db_lo=5000, db_hi=149000)
+    assert engine.knn_last_stats()["tensor_core"] == 0
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
 def test_knn_ties_and_duplicates(engine, oracle_cpu):
     X = np.zeros((300, 4), np.float32)
     X[100:200] = 1.0

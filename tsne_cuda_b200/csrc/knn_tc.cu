@@ -50,6 +50,7 @@
 // Every wait has a time limit; on expiry the kernel sets an error flag, drains and frees its TMEM.
 #include <limits.h>
 #include <string.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -264,10 +265,14 @@ struct CellTable {
 
 __global__ void knn_cells_init_kernel(const float *__restrict__ X, int D, long long db_lo, long long nd, int cells, CellTable *tab)
 {
-    // centres = database rows spread evenly over the range
+    // centres = database rows, one from each of `cells` equal stretches of the range at a hashed offset (an
+    // even spacing would alias with any periodic ordering of the data and could leave whole clusters
+    // without a centre)
     for (int idx = threadIdx.x; idx < cells * 64; idx += blockDim.x) {
         const int c = idx >> 6, d = idx & 63;
-        const long long row = db_lo + (long long)(((double)c + 0.5) * (double)nd / (double)cells);
+        const long long stretch = nd / cells;
+        const unsigned long long h = ((unsigned long long)(c + 1) * 0x9E3779B97F4A7C15ull) >> 20;
+        const long long row = db_lo + (long long)c * stretch + (long long)(h % (unsigned long long)stretch);
         tab->centre[c][d] = (d < D) ? X[row * D + d] : 0.0f;
     }
     for (int c = threadIdx.x; c < kMaxCells; c += blockDim.x) {
@@ -497,19 +502,21 @@ __global__ void knn_single_segment_kernel(int2 *segs, int *nseg, int tiles)
     nseg[0] = 1;
 }
 
-// The database tiles of a block in scan order: the tiles of its segments that are multiples of `stride`.
+// The database tiles of a block in scan order: the tiles of its segments that are multiples of `stride` and lie
+// in the window [win_lo, win_hi) of the launch.
 // The producer, the MMA issuer and the epilogue each walk the same sequence.
 struct TileWalk {
     const int2 *segs;
-    int nseg, stride, s, t, end;
-    __device__ TileWalk(const int2 *segs_, int nseg_, int stride_) : segs(segs_), nseg(nseg_), stride(stride_), s(-1), t(0), end(0) {}
+    int nseg, stride, win_lo, win_hi, s, t, end;
+    __device__ TileWalk(const int2 *segs_, int nseg_, int stride_, int win_lo_, int win_hi_)
+        : segs(segs_), nseg(nseg_), stride(stride_), win_lo(win_lo_), win_hi(win_hi_), s(-1), t(0), end(0) {}
     __device__ bool next(int &tile)
     {
         while (t >= end) {
             if (++s >= nseg) return false;
             const int2 g = segs[s];
-            t = (g.x + stride - 1) / stride * stride;
-            end = g.y;
+            t = (max(g.x, win_lo) + stride - 1) / stride * stride;
+            end = min(g.y, win_hi);
         }
         tile = t;
         t += stride;
@@ -543,8 +550,8 @@ struct TcShared {
 template <int EPL, bool FIXED, int QH>
 __global__ void __launch_bounds__(tc_threads(QH), 1)
 knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int Dp, long long nq, long long nd_pos,
-                     const int2 *__restrict__ segs, const int *__restrict__ nseg, int seg_stride, int tile_stride,
-                     const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id, int *__restrict__ counts,
+                     const int2 *__restrict__ segs, const int *__restrict__ nseg, int seg_stride, int tile_stride, int win_lo,
+                     int win_hi, const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id, int *counts,
                      int *error_flag)
 {
     constexpr int C = 32 * EPL;   // capacity handled by one compaction
@@ -561,6 +568,11 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
     const long long qt = (long long)blockIdx.x * QH;   // first query tile of the block
     const int2 *my_segs = segs + (size_t)blockIdx.x * seg_stride;
     const int my_nseg = nseg[seg_stride ? blockIdx.x : 0];
+    {   // nothing of this block's segments in the window: leave before any barrier or TMEM is set up
+        TileWalk probe(my_segs, my_nseg, tile_stride, win_lo, win_hi);
+        int first;
+        if (!probe.next(first)) return;
+    }
     volatile int *abort_flag = &sh.abort_flag;
 
     if (threadIdx.x == 0) {
@@ -590,7 +602,7 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
             mbar_expect_tx(&sh.full_a, QH * image_bytes);
             for (int h = 0; h < QH; h++)
                 bulk_load(sA + (size_t)h * (image_bytes / 4), img_q + (size_t)(qt + h) * (image_bytes / 4), image_bytes, &sh.full_a);
-            TileWalk walk(my_segs, my_nseg, tile_stride);
+            TileWalk walk(my_segs, my_nseg, tile_stride, win_lo, win_hi);
             int tile;
             for (long long t = 0; walk.next(tile); t++) {
                 const int s = (int)(t % kBStages);
@@ -604,7 +616,7 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             bool ok = mbar_wait(&sh.full_a, 0, abort_flag);
-            TileWalk walk(my_segs, my_nseg, tile_stride);
+            TileWalk walk(my_segs, my_nseg, tile_stride, win_lo, win_hi);
             int tile;
             for (long long t = 0; ok && walk.next(tile); t++) {
                 const int s = (int)(t % kBStages), b = (int)(t % kAccBufs);
@@ -648,8 +660,16 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
         float *bk = cand_key + (serve ? gq : 0) * cap + (FIXED ? buf * seg_cap : 0);
         int32_t *bi = cand_id + (serve ? gq : 0) * cap + (FIXED ? buf * seg_cap : 0);
         float thr = serve ? (FIXED ? tau[gq] : INFINITY) : -INFINITY;
+        // a fixed-threshold scan may be split into several launches (windows of the database): a launch
+        // continues the buffers where the previous one stopped (counts are zeroed before the first)
         int cnt = 0;
         bool overflow = false;
+        if (FIXED && serve) {
+            const int c0 = counts[gq * kAccBufs + buf];
+            cnt = c0 & 0x3fffffff;
+            overflow = (c0 & 0x40000000) != 0;
+            if (overflow) thr = -INFINITY;
+        }
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * TN);
 
         // One chunk = 32 accumulator columns = 32 keys of this thread's query.  Fast path: a tree of
@@ -702,7 +722,7 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
             }
         };
 
-        TileWalk walk(my_segs, active ? my_nseg : 0, tile_stride);
+        TileWalk walk(my_segs, active ? my_nseg : 0, tile_stride, win_lo, win_hi);
         int tile;
         for (long long t = 0; walk.next(tile); t++) {
             const int b = (int)(t % kAccBufs);
@@ -1124,14 +1144,27 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         seg_stride = kMaxCells;
         return 0;
     };
+    // A database image much larger than L2 is scanned in windows of tiles, one launch per window: the blocks
+    // that run at the same time then read the same ~60 MB, which stays in L2.  In one launch the blocks
+    // drift apart until each streams its own copy from HBM with only one 56 KB stage in flight, and the
+    // scan becomes latency-bound (measured at 10^7 rows: 3.85 s per 2^20 queries against 1.3 s of MMAs).
+    const long long db_image_bytes = (long long)w.td * Dp * 1024;
+    int window_tiles = db_image_bytes > (512ll << 20) ? (int)((60ll << 20) / ((long long)Dp * 1024)) : INT_MAX;
+    if (const char *e = getenv("B200TSNE_KNN_WINDOW_TILES")) window_tiles = std::max(1, atoi(e));   // for tests
 #define B200_KNN_FILTER_V(EPL_, FIXED_, QH_, stride_, tau_, cap_, key_, id_, counts_)                                           \
     do {                                                                                                                        \
         const size_t smem_ = (size_t)(QH_ + kBStages) * Dp * 1024;                                                              \
         B200_CUDA(cudaFuncSetAttribute(knn_tc_filter_kernel<EPL_, FIXED_, QH_>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
                                        (int)smem_));                                                                            \
-        knn_tc_filter_kernel<EPL_, FIXED_, QH_><<<(unsigned)((q_tiles + QH_ - 1) / QH_), tc_threads(QH_), smem_, st>>>(          \
-            w.img_q, w.img_db, Dp, nq, nd_pos, w.segs, w.nseg, seg_stride, stride_, tau_, cap_, key_, id_, counts_, counters + 0); \
-        B200_CUDA(cudaGetLastError());                                                                                          \
+        if (FIXED_) B200_CUDA(cudaMemsetAsync(counts_, 0, sizeof(int) * (size_t)nq * kAccBufs, st));                            \
+        const long long win_ = FIXED_ ? (long long)window_tiles * (stride_) : (long long)INT_MAX;                               \
+        for (long long lo_ = 0; lo_ < w.td; lo_ += win_) {                                                                      \
+            const int hi_ = (int)std::min<long long>(w.td, lo_ + win_);                                                         \
+            knn_tc_filter_kernel<EPL_, FIXED_, QH_><<<(unsigned)((q_tiles + QH_ - 1) / QH_), tc_threads(QH_), smem_, st>>>(      \
+                w.img_q, w.img_db, Dp, nq, nd_pos, w.segs, w.nseg, seg_stride, stride_, (int)lo_, hi_, tau_, cap_, key_, id_,   \
+                counts_, counters + 0);                                                                                         \
+            B200_CUDA(cudaGetLastError());                                                                                      \
+        }                                                                                                                       \
     } while (0)
     // the online threshold keeps one group per query busy: one query tile per block is enough there
 #define B200_KNN_FILTER(EPL_, FIXED_, stride_, tau_, cap_, key_, id_, counts_)                                                   \
