@@ -193,11 +193,15 @@ def e2e_ours(X, hp, Y0, args):
     warm = TSNE(perplexity=hp["perplexity"], num_neighbors=hp["num_neighbors"], learning_rate=hp["learning_rate"],
                 early_exaggeration=hp["early_exaggeration"], n_iter=20, perplexity_epsilon=1e-3)
     warm.fit_transform(X, y0)
-    t0 = time.time()
-    Y = t.fit_transform(X, y0)
-    T = time.time() - t0
-    assert np.isfinite(Y).all()
-    return {"value": n_iter / T, "unit": "iterations/s", "fit_transform_s": T, "iterations": n_iter, "warmup_calls": 1,
+    times = []
+    for _ in range(3):   # median of three calls: allocation and page-fault noise of a call is +-10 %
+        t0 = time.time()
+        Y = t.fit_transform(X, y0)
+        times.append(time.time() - t0)
+        assert np.isfinite(Y).all()
+    T = sorted(times)[1]
+    return {"value": n_iter / T, "unit": "iterations/s", "fit_transform_s": T, "fit_transform_s_calls": times,
+            "iterations": n_iter, "warmup_calls": 1,
             "h2d_bytes_per_step": (X.nbytes + Y0.nbytes) / n_iter, "d2h_bytes_per_step": Y0.nbytes / n_iter,
             "api": "tsne_cuda_b200.TSNE.fit_transform -> pymodule_tsne"}
 
@@ -229,11 +233,14 @@ def e2e_sharded(X, hp, Y0, args, rank, local_rank, world):
         return y
 
     fit(20)   # one untimed call, as on a single GPU
-    dist.barrier()
-    torch.cuda.synchronize()
-    t0 = time.time()
-    Y = fit(n_iter)
-    T = time.time() - t0
+    times = []
+    for _ in range(3):   # median of three calls, as on a single GPU
+        dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.time()
+        Y = fit(n_iter)
+        times.append(time.time() - t0)
+    T = sorted(times)[1]
     t = torch.tensor([T], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     T = float(t.item())

@@ -5,6 +5,7 @@
 // "_time_*" lines printed at verbosity > 0 (which the reference's tuning harness parses) are kept;
 // everything between host X and host Y stays on the device.
 #include <chrono>
+#include <thread>
 #include <fstream>
 #include <iostream>
 #include <random>
@@ -105,9 +106,20 @@ int run(Options &opt, GpuOptions &gpu_opt)
     t_init = timer.lap();
 
     if (verbose) std::cout << "done.\nKNN Computation... " << std::flush;
+    // The initial embedding is drawn on the host (the reference's generator and draw order, 4N normal
+    // draws): a host thread does that while the device searches the neighbours.
+    std::vector<float> y0;
+    std::string y0_error;
+    int y0_rc = 0;
+    std::thread y0_thread([&]() {
+        y0_rc = initial_embedding(opt, y0);
+        if (y0_rc != 0) y0_error = b200::last_error();
+    });
     // kNN, max-normalisation, perplexity search and symmetrisation run back to back on the device;
     // the split between the two printed phases is only meaningful with stage timers on.
-    B200_TRY(s.affinities_from_points(opt.points, opt.num_dims, opt.perplexity, opt.perplexity_search_epsilon));
+    const int aff_rc = s.affinities_from_points(opt.points, opt.num_dims, opt.perplexity, opt.perplexity_search_epsilon);
+    y0_thread.join();
+    if (aff_rc != 0) return aff_rc;
     if (verbose) std::cout << "done.\nComputing Pij matrix... " << std::endl;
     const double t_aff = timer.lap();
     if (s.stage_timers) {
@@ -118,8 +130,7 @@ int run(Options &opt, GpuOptions &gpu_opt)
     }
 
     if (verbose) std::cout << "done.\nInitializing low dim points... " << std::flush;
-    std::vector<float> y0;
-    B200_TRY(initial_embedding(opt, y0));
+    if (y0_rc != 0) { b200::set_error(y0_error); return y0_rc; }
     B200_TRY(s.set_embedding_soa(y0.data(), true));
     t_lowdim = timer.lap();
     if (verbose) std::cout << "done.\nInitializing CUDA memory... " << std::flush;
