@@ -65,6 +65,21 @@ def test_knn_tensor_core_windows_and_cells(engine, monkeypatch):
     assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
 
 
+@pytest.mark.parametrize("n,d,k", [(20000, 100, 40), (30000, 784, 90), (17000, 65, 150)])
+def test_knn_tensor_core_wide_points(engine, monkeypatch, n, d, k):
+    """More inner dimensions than one shared-memory image holds: the chunked tensor-core kernel, same lists as the
+    SIMT search on every row."""
+    from tsne_cuda_b200 import datasets
+    X = datasets.mnist_shaped(n, d, seed=n) if d == 784 else datasets.gaussian_mixture(n, d, seed=n)
+    a = engine.knn(X, k)
+    st = engine.knn_last_stats()
+    assert st["tensor_core"] == 1 and st["rows_recomputed"] <= 0.02 * n and st["filter_error_ratio"] < 0.5
+    monkeypatch.setenv("B200TSNE_KNN", "simt")
+    b = engine.knn(X, k)
+    assert engine.knn_last_stats()["tensor_core"] == 0
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
 def test_knn_ties_and_duplicates(engine, oracle_cpu):
     X = np.zeros((300, 4), np.float32)
     X[100:200] = 1.0

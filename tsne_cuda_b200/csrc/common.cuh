@@ -78,8 +78,8 @@ int launch_knn_exact(const float *XT, int64_t N, int D, int K, int64_t q_lo, int
                      int64_t db_hi, int32_t *ids, float *d2, cudaStream_t st);   // ids/d2 keep (INT_MAX,+inf) in unfilled slots
 int launch_knn_exact_rows(const float *XT, int64_t N, int D, int K, const int *q_index, int64_t nq, int64_t out_base,
                           int64_t db_lo, int64_t db_hi, int32_t *ids, float *d2, cudaStream_t st);
-// knn_tc.cu: tensor-core filter + exact re-rank + proof (D <= 64)
-bool knn_tc_supported(int64_t N, int D, int K);
+// knn_tc.cu: tensor-core filter + exact re-rank + proof (nd = database rows to scan)
+bool knn_tc_supported(int64_t nd, int D, int K);
 size_t knn_tc_workspace_bytes(int D, int K, int64_t nq, int64_t nd);
 int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_hi, int64_t db_lo, int64_t db_hi,
                   int32_t *ids, float *d2, void *workspace, int **failed_list, int *n_failed_host, float *err_ratio_host,

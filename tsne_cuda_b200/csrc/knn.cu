@@ -388,7 +388,7 @@ int knn_search(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_
     const int64_t nq = q_hi - q_lo;
     if (nq <= 0) return 0;
     const char *force = getenv("B200TSNE_KNN");
-    const bool want_tc = knn_tc_supported(N, D, K) && !(force && strcmp(force, "simt") == 0);
+    const bool want_tc = knn_tc_supported(db_hi - db_lo, D, K) && !(force && strcmp(force, "simt") == 0);
     DeviceArena tmp;
     float *XT = nullptr;
     auto ensure_xt = [&]() -> int {

@@ -208,19 +208,20 @@ __device__ __forceinline__ size_t image_offset(int r, int k)
     return (size_t)(k >> 3) * 1024 + (size_t)(r >> 3) * 64 + (size_t)((k >> 2) & 1) * 32 + (size_t)(r & 7) * 4 + (k & 3);
 }
 
-// Rows of X named by `list` (-1 = padding) -> tile images [tiles][2 (hi, lo)][Dp/8][1024 floats] in query form
+// Rows of X named by `list` (-1 = padding) -> tile images [tiles][Dp/KC chunks][2 (hi, lo)][KC/8][1024 floats] (the
+// narrow path has one chunk, KC = Dp; the wide path chunks of kWideKC inner dimensions) in query form
 // [x, 1, 0...] or database form [-2x, |x|^2, 0...]; a padding row is all zeros as a query and carries a huge
 // finite norm as a database point, so it never ranks.  norms (queries only): exact squared norms, double.
 __global__ void __launch_bounds__(128)
-knn_tc_prepare_kernel(const float *__restrict__ X, const int *__restrict__ list, int D, int Dp, int db_form,
+knn_tc_prepare_kernel(const float *__restrict__ X, const int *__restrict__ list, int D, int Dp, int KC, int db_form,
                       float *__restrict__ img, double *__restrict__ norms)
 {
     const long long tile = blockIdx.x;
     const int r = threadIdx.x;
     const long long pos = tile * TM + r;
     const int i = list[pos];
-    float *im = img + (size_t)tile * 2 * Dp * 128;
-    const size_t part = (size_t)Dp * 128;
+    float *im_tile = img + (size_t)tile * 2 * Dp * 128;
+    const size_t part = (size_t)KC * 128;
     double n2 = 0.0;
     for (int k = 0; k < D; k++) {
         const float x = (i >= 0) ? X[(long long)i * D + k] : 0.0f;
@@ -235,8 +236,9 @@ knn_tc_prepare_kernel(const float *__restrict__ X, const int *__restrict__ list,
             v = db_form ? ((i >= 0) ? (float)n2 : 3.0e38f) : ((i >= 0) ? 1.0f : 0.0f);
         }
         const float vh = to_tf32(v);
-        im[image_offset(r, k)] = vh;
-        im[part + image_offset(r, k)] = to_tf32(v - vh);
+        float *im = im_tile + (size_t)(k / KC) * 2 * part;
+        im[image_offset(r, k % KC)] = vh;
+        im[part + image_offset(r, k % KC)] = to_tf32(v - vh);
     }
     if (norms) norms[pos] = n2;
 }
@@ -775,6 +777,209 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
 }
 
 // ------------------------------------------------------------------------------------------------
+// filter kernel for wide points (D + 1 > 64): the inner dimension no longer fits in shared memory at once
+// ------------------------------------------------------------------------------------------------
+// A block multiplies two query tiles with two database tiles (a "unit" of 256 database rows) at a time,
+// walking the inner dimension in chunks of kWideKC: a stage holds the chunk images of the four tiles
+// (4 x 24 KB), two stages alternate, the four 128 x 128 accumulators fill the 512 TMEM columns.  Operand
+// bytes per MMA are those of the narrow kernel with two query tiles, but the query images are streamed
+// again for every unit, so the kernel leans on L2 bandwidth (24 KB per tile pair and chunk).  After the
+// last chunk of a unit the sixteen epilogue warps (query tile x database tile x TMEM lane quarter) compare
+// the keys with the fixed thresholds exactly as in the narrow kernel; the next unit's MMAs wait until the
+// accumulators have been read.  Fixed thresholds only (a small database goes to the SIMT search).
+constexpr int kWideKC = 24;                       // inner dimensions per chunk = 3 MMA K steps
+constexpr uint32_t kWideChunkBytes = kWideKC * 1024;   // hi + lo of one tile and chunk
+constexpr int kWideStages = 2;
+constexpr int kWideUnit = 2 * TN;                 // database rows per unit
+
+struct WideShared {
+    uint64_t full[kWideStages];
+    uint64_t empty[kWideStages];
+    uint64_t acc_full;
+    uint64_t acc_empty;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int EPL>
+__global__ void __launch_bounds__(tc_threads(2), 1)
+knn_tc_wide_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int n_chunks, long long nq,
+                   const int2 *__restrict__ segs, const int *__restrict__ nseg, int seg_stride, int unit_stride, int win_lo,
+                   int win_hi, const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id, int *counts,
+                   int *error_flag)
+{
+    constexpr int kProducerWarp = 16, kMmaWarp = 17;
+    constexpr uint32_t kTmemCols = 512;
+    constexpr int kSteps = kWideKC / 8;
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) WideShared sh;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long qt = (long long)blockIdx.x * 2;   // first query tile of the block
+    const int2 *my_segs = segs + (size_t)blockIdx.x * seg_stride;
+    const int my_nseg = nseg[seg_stride ? blockIdx.x : 0];
+    {   // nothing of this block's segments in the window
+        TileWalk probe(my_segs, my_nseg, unit_stride, win_lo, win_hi);
+        int first;
+        if (!probe.next(first)) return;
+    }
+    volatile int *abort_flag = &sh.abort_flag;
+    const size_t tile_floats = (size_t)n_chunks * (kWideChunkBytes / 4);   // one tile's image, all chunks
+    // stage layout: [A0 chunk][A1 chunk][B0 chunk][B1 chunk], each hi then lo
+    auto stage_ptr = [&](int s, int which) { return smem + ((size_t)s * 4 + which) * kWideChunkBytes; };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kWideStages; s++) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
+        mbar_init(&sh.acc_full, 1);
+        mbar_init(&sh.acc_empty, 16);
+        sh.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh.tmem_base;
+
+    if (warp == kProducerWarp) {
+        if (lane == 0) {
+            TileWalk walk(my_segs, my_nseg, unit_stride, win_lo, win_hi);
+            int unit;
+            long long it = 0;   // stage counter over (unit, chunk)
+            bool ok = true;
+            while (ok && walk.next(unit)) {
+                for (int c = 0; c < n_chunks; c++, it++) {
+                    const int s = (int)(it % kWideStages);
+                    const uint32_t ph = (uint32_t)((it / kWideStages) & 1);
+                    if (!mbar_wait(&sh.empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(&sh.full[s], 4 * kWideChunkBytes);
+                    const size_t coff = (size_t)c * (kWideChunkBytes / 4);
+                    bulk_load(stage_ptr(s, 0), img_q + (size_t)qt * tile_floats + coff, kWideChunkBytes, &sh.full[s]);
+                    bulk_load(stage_ptr(s, 1), img_q + (size_t)(qt + 1) * tile_floats + coff, kWideChunkBytes, &sh.full[s]);
+                    bulk_load(stage_ptr(s, 2), img_db + (size_t)(2 * (long long)unit) * tile_floats + coff, kWideChunkBytes, &sh.full[s]);
+                    bulk_load(stage_ptr(s, 3), img_db + (size_t)(2 * (long long)unit + 1) * tile_floats + coff, kWideChunkBytes,
+                              &sh.full[s]);
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        if (lane == 0) {
+            TileWalk walk(my_segs, my_nseg, unit_stride, win_lo, win_hi);
+            int unit;
+            long long it = 0, n_unit = 0;
+            bool ok = true;
+            while (ok && walk.next(unit)) {
+                // the accumulators of the previous unit must have been read
+                if (!mbar_wait(&sh.acc_empty, (uint32_t)((n_unit & 1) ^ 1), abort_flag)) break;
+                for (int c = 0; c < n_chunks; c++, it++) {
+                    const int s = (int)(it % kWideStages);
+                    const uint32_t ph = (uint32_t)((it / kWideStages) & 1);
+                    if (!mbar_wait(&sh.full[s], ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int pair = 0; pair < 4; pair++) {
+                        const int h = pair >> 1, g = pair & 1;
+                        const uint32_t a_hi = smem_u32(stage_ptr(s, h)), a_lo = a_hi + kSteps * 4096u;
+                        const uint32_t b_hi = smem_u32(stage_ptr(s, 2 + g)), b_lo = b_hi + kSteps * 4096u;
+                        const uint32_t d_tmem = tmem_base + (uint32_t)((h * 2 + g) * TN);
+                        uint32_t acc = (c > 0) ? 1u : 0u;
+                        for (int ks = 0; ks < kSteps; ks++) {      // hi . hi
+                            tc_mma_tf32(d_tmem, make_desc(a_hi + ks * 4096u), make_desc(b_hi + ks * 4096u), kInstrDesc, acc);
+                            acc = 1;
+                        }
+                        for (int ks = 0; ks < kSteps; ks++)        // lo . hi
+                            tc_mma_tf32(d_tmem, make_desc(a_lo + ks * 4096u), make_desc(b_hi + ks * 4096u), kInstrDesc, 1);
+                        for (int ks = 0; ks < kSteps; ks++)        // hi . lo
+                            tc_mma_tf32(d_tmem, make_desc(a_hi + ks * 4096u), make_desc(b_lo + ks * 4096u), kInstrDesc, 1);
+                    }
+                    tc_commit(&sh.empty[s]);
+                }
+                if (ok) tc_commit(&sh.acc_full);
+                n_unit++;
+            }
+        }
+    } else {
+        // ---------------- epilogue: one query per thread, one database tile of the unit per warp group ----------------
+        const int quarter = warp & 3, half = (warp >> 2) & 1, g = warp >> 3;
+        const int seg_cap = cap / 2;
+        const int row = quarter * 32 + lane;
+        const long long gq = (qt + half) * TM + row;
+        const bool serve = gq < nq;
+        float *bk = cand_key + (serve ? gq : 0) * cap + g * seg_cap;
+        int32_t *bi = cand_id + (serve ? gq : 0) * cap + g * seg_cap;
+        float thr = serve ? tau[gq] : -INFINITY;
+        int cnt = 0;
+        bool overflow = false;
+        if (serve) {
+            const int c0 = counts[gq * 2 + g];
+            cnt = c0 & 0x3fffffff;
+            overflow = (c0 & 0x40000000) != 0;
+            if (overflow) thr = -INFINITY;
+        }
+        const uint32_t tcol = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((half * 2 + g) * TN);
+        TileWalk walk(my_segs, my_nseg, unit_stride, win_lo, win_hi);
+        int unit;
+        for (long long n_unit = 0; walk.next(unit); n_unit++) {
+            if (!mbar_wait(&sh.acc_full, (uint32_t)(n_unit & 1), abort_flag, 32)) break;
+            tc_fence_after();
+            const long long p0 = (long long)unit * kWideUnit + (long long)g * TN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < TN; c0 += 32) {
+                uint32_t r[32];
+                tc_ld32_issue(tcol + (uint32_t)c0, r);
+                tc_ld32_wait(r);
+                if (c0 == TN - 32) {   // the last read has landed: hand the accumulators back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh.acc_empty);
+                }
+                float m4[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float a = min3(__uint_as_float(r[8 * q]), __uint_as_float(r[8 * q + 1]), __uint_as_float(r[8 * q + 2]));
+                    const float b = min3(__uint_as_float(r[8 * q + 3]), __uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
+                    const float c = fminf(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+                    m4[q] = min3(a, b, c);
+                }
+                const float mn = fminf(min3(m4[0], m4[1], m4[2]), m4[3]);
+                if (mn < thr) {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        if (m4[q] < thr) {
+#pragma unroll
+                            for (int e = 0; e < 8; e++) {
+                                const int c = q * 8 + e;
+                                const float key = __uint_as_float(r[c]);
+                                if (key < thr) {   // padding rows carry a huge norm and never pass a finite threshold
+                                    __stcg(bk + cnt, key);
+                                    __stcg(bi + cnt, (int32_t)(p0 + c0 + c));
+                                    cnt++;
+                                }
+                            }
+                        }
+                    }
+                }
+                if (cnt > seg_cap - 32) { overflow = true; thr = -INFINITY; }
+            }
+        }
+        if (serve) counts[gq * 2 + g] = cnt | (overflow ? 0x40000000 : 0);
+    }
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (threadIdx.x == 0 && sh.abort_flag) atomicExch(error_flag, 1);
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // final selection after a fixed-threshold scan: one warp per query
 // ------------------------------------------------------------------------------------------------
 // Buffer of query q: two halves of cap/2 entries with counts[2q], counts[2q+1] valid entries.  Leaves the L
@@ -992,6 +1197,71 @@ knn_sample_tau_kernel(const float *__restrict__ X, int D, const int *__restrict_
     }
 }
 
+// The same for points of any width: the inner dimension is walked in chunks of 64, the dot products with
+// the 32 staged sample points are kept in registers across the chunks.
+__global__ void __launch_bounds__(kTauThreads)
+knn_sample_tau_wide_kernel(const float *__restrict__ X, int D, const int *__restrict__ qlist, long long nq, long long s_lo,
+                           long long s_stride, int m, int rank, float *__restrict__ tau)
+{
+    __shared__ float s_pt[32][65];
+    __shared__ float s_nrm[32];
+    const long long q = (long long)blockIdx.x * kTauThreads + threadIdx.x;
+    const long long qrow = (q < nq) ? qlist[q] : 0;
+    float top[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) top[i] = INFINITY;
+    for (int k0 = 0; k0 < m; k0 += 32) {
+        float dot[32];
+#pragma unroll
+        for (int p = 0; p < 32; p++) dot[p] = 0.0f;
+        float n2 = 0.0f;
+        for (int d0 = 0; d0 < D; d0 += 64) {
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < 32 * 64; idx += kTauThreads) {
+                const int p = idx >> 6, d = idx & 63;
+                const long long k = k0 + p;
+                const long long j = s_lo + k * s_stride + (long long)(((unsigned long long)k * 2654435761ull) % (unsigned long long)s_stride);
+                s_pt[p][d] = (k < m && d0 + d < D) ? X[j * D + d0 + d] : 0.0f;
+            }
+            __syncthreads();
+            float qv[64];
+#pragma unroll
+            for (int d = 0; d < 64; d++) qv[d] = (q < nq && d0 + d < D) ? X[qrow * D + d0 + d] : 0.0f;
+#pragma unroll
+            for (int p = 0; p < 32; p++) {   // fully unrolled: dot[] stays in registers
+                float acc = 0.0f;
+#pragma unroll
+                for (int d = 0; d < 64; d++) acc = fmaf(qv[d], s_pt[p][d], acc);
+                dot[p] += acc;
+            }
+            if (threadIdx.x < 32)
+                for (int d = 0; d < 64; d++) n2 = fmaf(s_pt[threadIdx.x][d], s_pt[threadIdx.x][d], n2);
+        }
+        __syncthreads();
+        if (threadIdx.x < 32) s_nrm[threadIdx.x] = (k0 + threadIdx.x < m) ? n2 : INFINITY;
+        __syncthreads();
+#pragma unroll
+        for (int p = 0; p < 32; p++) {
+            const float key = fmaf(-2.0f, dot[p], s_nrm[p]);
+            if (key < top[15]) {
+                top[15] = key;
+#pragma unroll
+                for (int i = 15; i > 0; i--) {
+                    const float lo = fminf(top[i - 1], top[i]), hi = fmaxf(top[i - 1], top[i]);
+                    top[i - 1] = lo;
+                    top[i] = hi;
+                }
+            }
+        }
+    }
+    if (q < nq) {
+        float t = top[0];
+#pragma unroll
+        for (int i = 1; i < 16; i++) t = (i == rank) ? top[i] : t;
+        tau[q] = t;
+    }
+}
+
 // tau[q] = key of rank `rank` (0-based) in the sorted sample list of query q.  A list shorter than that,
 // or a sample pass that flagged the row, gives -inf: the next pass keeps nothing for the row, flags it,
 // and the row is recomputed by the SIMT search.  (When the whole database is smaller than the list the
@@ -1014,10 +1284,16 @@ __global__ void knn_tc_collect_failed_kernel(const int *__restrict__ failed, lon
 
 }  // namespace
 
-bool knn_tc_supported(int64_t N, int D, int K)
+// wide points: the inner dimension (D + 1) does not fit the narrow kernel's shared-memory images
+static bool tc_wide(int D) { return D + 1 > 64; }
+constexpr long long kWideMinRows = 16384;   // the wide kernel has fixed thresholds only: it needs a database to sample
+
+// nd: database rows the search will scan
+bool knn_tc_supported(int64_t nd, int D, int K)
 {
-    if (D > 64 || K + 32 > kMaxL) return false;   // three images of (D + 1 padded to 8) x 1 KB must fit in shared memory
-    return N >= 2048;   // below this the SIMT search is faster than the set-up of this one
+    if (K + 32 > kMaxL || D > 8192) return false;
+    if (tc_wide(D)) return nd >= kWideMinRows;
+    return nd >= 2048;   // below this the SIMT search is faster than the set-up of this one
 }
 
 // candidate buffer entries per query in a fixed-threshold pass: 8 L (two halves of 4 L for ~1.5 L expected each)
@@ -1027,6 +1303,7 @@ constexpr long long kTwoPassMinTiles = 512;   // below this many database tiles 
 
 // Device workspace of launch_knn_tc, carved in this order.
 struct TcWorkspace {
+    bool wide;
     int Dp, cells;
     long long tq, td;          // tiles allocated for the query list / the database list
     float *img_q, *img_db;
@@ -1045,12 +1322,16 @@ struct TcWorkspace {
 static TcWorkspace tc_carve(void *base, int D, int K, long long nq, long long nd)
 {
     TcWorkspace w;
-    w.Dp = (D + 1 + 7) / 8 * 8;   // one extra inner column carries the norm
-    const bool two_pass = nd >= kTwoPassMinTiles * TN;
+    w.wide = tc_wide(D);
+    // one extra inner column carries the norm; wide points are chunked along the inner dimension
+    w.Dp = w.wide ? (D + 1 + kWideKC - 1) / kWideKC * kWideKC : (D + 1 + 7) / 8 * 8;
+    const bool two_pass = nd >= (w.wide ? kWideMinRows : kTwoPassMinTiles * TN);
     // cells of at least 16384 points: the padding between them stays below 1 % of the database
-    w.cells = two_pass ? (int)std::min<long long>(kMaxCells, std::max<long long>(1, nd / 16384)) : 1;
+    // (wide points are not visited by cells: the cell kernels keep a point in registers)
+    w.cells = (two_pass && !w.wide) ? (int)std::min<long long>(kMaxCells, std::max<long long>(1, nd / 16384)) : 1;
     w.tq = (nq + TM - 1) / TM + 1;                 // one padding tile: a block may hold two query tiles
     w.td = (nd + TN - 1) / TN + w.cells;           // every cell may end in a partly filled tile
+    if (w.wide) w.td = (w.td + 1) / 2 * 2;         // the wide kernel takes the database two tiles at a time
     const int C = (K + 32 <= 128) ? 256 : 512;
     char *p = static_cast<char *>(base);
     auto take = [&](size_t bytes) { char *r = p; p += (bytes + 255) / 256 * 256; return r; };
@@ -1098,6 +1379,8 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     if (nq <= 0) return 0;
     TcWorkspace w = tc_carve(workspace, D, K, nq, nd);
     const int Dp = w.Dp, cells = w.cells;
+    const bool wide = w.wide;
+    const int KC = wide ? kWideKC : Dp;   // inner dimensions per image chunk
     const int EPL = (K + 32 <= 128) ? 8 : 16, C = 32 * EPL, L = 16 * EPL;
     const int kFixedCap = fixed_cap(K);
     const bool two_pass = w.fix_key != nullptr;
@@ -1124,8 +1407,8 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         knn_iota_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(w.qlist, q_lo, nq);
     }
     B200_CUDA(cudaGetLastError());
-    knn_tc_prepare_kernel<<<(unsigned)w.tq, 128, 0, st>>>(X, w.qlist, D, Dp, 0, w.img_q, w.norms_q);
-    knn_tc_prepare_kernel<<<(unsigned)w.td, 128, 0, st>>>(X, w.dblist, D, Dp, 1, w.img_db, nullptr);
+    knn_tc_prepare_kernel<<<(unsigned)w.tq, 128, 0, st>>>(X, w.qlist, D, Dp, KC, 0, w.img_q, w.norms_q);
+    knn_tc_prepare_kernel<<<(unsigned)w.td, 128, 0, st>>>(X, w.dblist, D, Dp, KC, 1, w.img_db, nullptr);
     B200_CUDA(cudaGetLastError());
 
     // two query tiles per block when their images and the database stages fit in shared memory
@@ -1133,7 +1416,7 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     const long long q_tiles = (nq + TM - 1) / TM;
     // Segments of the blocks: all database tiles (one shared list) unless the cells prune (per block).
     // The blocks of an online pass hold one query tile, those of a fixed-threshold pass QH.
-    knn_single_segment_kernel<<<1, 1, 0, st>>>(w.segs, w.nseg, (int)((nd + TN - 1) / TN));
+    knn_single_segment_kernel<<<1, 1, 0, st>>>(w.segs, w.nseg, wide ? (int)(w.td / 2) : (int)((nd + TN - 1) / TN));
     B200_CUDA(cudaGetLastError());
     int seg_stride = 0;
     auto prune = [&]() -> int {   // segments from the current thresholds
@@ -1166,10 +1449,27 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
             B200_CUDA(cudaGetLastError());                                                                                      \
         }                                                                                                                       \
     } while (0)
+    // wide points: the same scan by the chunked kernel, in units of two database tiles
+#define B200_KNN_FILTER_WIDE(EPL_, stride_, tau_, cap_, key_, id_, counts_)                                                      \
+    do {                                                                                                                        \
+        const size_t smem_ = (size_t)kWideStages * 4 * kWideChunkBytes;                                                         \
+        B200_CUDA(cudaFuncSetAttribute(knn_tc_wide_kernel<EPL_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_));      \
+        B200_CUDA(cudaMemsetAsync(counts_, 0, sizeof(int) * (size_t)nq * 2, st));                                               \
+        const long long units_ = w.td / 2;                                                                                      \
+        const long long win_ = (long long)std::max(1, window_tiles / 2) * (stride_);                                            \
+        for (long long lo_ = 0; lo_ < units_; lo_ += win_) {                                                                    \
+            const int hi_ = (int)std::min<long long>(units_, lo_ + win_);                                                       \
+            knn_tc_wide_kernel<EPL_><<<(unsigned)((q_tiles + 1) / 2), tc_threads(2), smem_, st>>>(                               \
+                w.img_q, w.img_db, Dp / kWideKC, nq, w.segs, w.nseg, seg_stride, stride_, (int)lo_, hi_, tau_, cap_, key_, id_,  \
+                counts_, counters + 0);                                                                                         \
+            B200_CUDA(cudaGetLastError());                                                                                      \
+        }                                                                                                                       \
+    } while (0)
     // the online threshold keeps one group per query busy: one query tile per block is enough there
 #define B200_KNN_FILTER(EPL_, FIXED_, stride_, tau_, cap_, key_, id_, counts_)                                                   \
     do {                                                                                                                        \
-        if (!FIXED_ || QH == 1) B200_KNN_FILTER_V(EPL_, FIXED_, 1, stride_, tau_, cap_, key_, id_, counts_);                     \
+        if (FIXED_ && wide) B200_KNN_FILTER_WIDE(EPL_, stride_, tau_, cap_, key_, id_, counts_);                                 \
+        else if (!FIXED_ || QH == 1) B200_KNN_FILTER_V(EPL_, FIXED_, 1, stride_, tau_, cap_, key_, id_, counts_);                \
         else B200_KNN_FILTER_V(EPL_, FIXED_, (FIXED_ ? 2 : 1), stride_, tau_, cap_, key_, id_, counts_);                         \
     } while (0)
     const float *final_key = cand_key;
@@ -1186,20 +1486,26 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         //  C  everything against tau_B = the key of rank ~3L/kSampleStride in sample B: ~3L points beat it.
         // Before each scan the cells are tested against the thresholds it will use; a skipped cell holds no
         // point below them, so the candidate sets (and the sample statistics) are those of a full scan.
+        // (the wide kernel strides over units of two tiles: the same 1/kSampleStride of the database)
         const long long n_db_tiles = (nd + TN - 1) / TN;
-        const double b_points = (double)((n_db_tiles + kSampleStride - 1) / kSampleStride) * TN;
+        const double b_points = wide ? (double)((n_db_tiles / 2 + kSampleStride - 1) / kSampleStride) * kWideUnit
+                                     : (double)((n_db_tiles + kSampleStride - 1) / kSampleStride) * TN;
         const long long db_n = nd;
         // Up to ~400k points the sample of level A is large enough (16 N / 3L points, rank ~16) to fix the
         // threshold of level C directly; beyond that level B refines it.
         const bool direct = db_n <= 393216;
-        const int m_a = direct ? (int)std::min<long long>(16384, std::max<long long>(1024, 16 * db_n / (3 * L)))
+        const int m_a = direct ? (int)std::min<long long>(16384, std::max<long long>(256, 16 * db_n / (3 * L)))
                                : (int)std::min<long long>(16384, std::max<long long>(2048, (long long)(b_points / 32)));
         const long long a_stride = std::max<long long>(1, db_n / m_a);
         const double a_target = direct ? 3.0 * L * m_a / (double)db_n : 300.0 * m_a / b_points;
         const int rank_a = std::min(16, std::max(4, (int)(a_target + 0.5))) - 1;
         const int rank_b = std::max(4, (3 * L + kSampleStride - 1) / kSampleStride) - 1;
-        knn_sample_tau_kernel<<<(unsigned)((nq + kTauThreads - 1) / kTauThreads), kTauThreads, 0, st>>>(X, D, w.qlist, nq, db_lo, a_stride,
-                                                                                                m_a, rank_a, tau);
+        if (wide)
+            knn_sample_tau_wide_kernel<<<(unsigned)((nq + kTauThreads - 1) / kTauThreads), kTauThreads, 0, st>>>(X, D, w.qlist, nq, db_lo,
+                                                                                                         a_stride, m_a, rank_a, tau);
+        else
+            knn_sample_tau_kernel<<<(unsigned)((nq + kTauThreads - 1) / kTauThreads), kTauThreads, 0, st>>>(X, D, w.qlist, nq, db_lo, a_stride,
+                                                                                                    m_a, rank_a, tau);
         B200_CUDA(cudaGetLastError());
         B200_TRY(prune());
         const unsigned sel_grid = (unsigned)((nq + 3) / 4);
@@ -1230,6 +1536,7 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     }
 #undef B200_KNN_FILTER
 #undef B200_KNN_FILTER_V
+#undef B200_KNN_FILTER_WIDE
     // Error bound of the filter relative to (|x_i|^2 + d^2 + 1): 3xTF32 drops terms of order 2^-22 |x_i||x_j|
     // and the tensor-core accumulation is not IEEE; 2^-14 covers both with a wide margin, and the re-rank
     // checks the observed error of every candidate against half of it.
