@@ -1537,10 +1537,12 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
 #undef B200_KNN_FILTER
 #undef B200_KNN_FILTER_V
 #undef B200_KNN_FILTER_WIDE
-    // Error bound of the filter relative to (|x_i|^2 + d^2 + 1): 3xTF32 drops terms of order 2^-22 |x_i||x_j|
-    // and the tensor-core accumulation is not IEEE; 2^-14 covers both with a wide margin, and the re-rank
-    // checks the observed error of every candidate against half of it.
-    const float err_scale = 6.103515625e-05f;   // 2^-14
+    // Error bound of the filter relative to (|x_i|^2 + d^2 + 1): 3xTF32 drops terms of order 2^-22 |x_i||x_j|,
+    // and the fp32 accumulation of D products (not IEEE in the tensor core: take two units in the last place
+    // per addition) adds up to 2 D 2^-24 |x_i||x_j| in the worst case.  2^-14 covers both with a wide margin
+    // up to D = 256; beyond, the bound grows with D.  The re-rank checks the observed error of every
+    // candidate against half of it.
+    const float err_scale = std::max(6.103515625e-05f, (float)(D + 8) * 2.384185791015625e-07f);   // max(2^-14, (D + 8) 2^-22)
     knn_tc_rerank_kernel<<<(unsigned)((nq + kRerankWarps - 1) / kRerankWarps), kRerankWarps * 32, 0, st>>>(
         X, D, w.qlist, w.dblist, q_lo, nq, final_key, final_id, L, final_stride, K, w.norms_q, err_scale, two_pass ? row_flags : nullptr, ids, d2,
         failed, counters + 1, reinterpret_cast<float *>(counters + 3));
