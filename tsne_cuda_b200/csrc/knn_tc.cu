@@ -1,4 +1,5 @@
-// Exact k-nearest-neighbour search on the tensor cores (tcgen05 + TMEM), for D <= 64.
+// Exact k-nearest-neighbour search on the tensor cores (tcgen05 + TMEM): a kernel that keeps the whole inner
+// dimension in shared memory (D <= 63) and a chunked one for wider points (knn_tc_wide_kernel).
 //
 // Replaces the reference's FAISS IVF-Flat call (src/util/distance_utils.cu:79-121, approximate).
 // The result is the same as the SIMT search of knn.cu: ids ordered by the canonical fp32 distance
@@ -8,7 +9,7 @@
 //     query operand is [x_i, 1], the database operand [-2 x_j, |x_j|^2] (one of the padding columns of
 //     the 8-aligned inner dimension carries the norm), multiplied as a 3xTF32 product (v = hi + lo with
 //     hi, lo representable in TF32;  hi.hi + lo.hi + hi.lo, accumulated in fp32 in TMEM), accurate to
-//     about 2^-20 of |x_i||x_j|.  A block owns 128 queries (one TMEM lane each) and
+//     about 2^-20 of |x_i||x_j|.  A block owns 256 queries (one TMEM lane each per query tile) and
 //     walks the database in tiles of 128 points; each epilogue thread compares its row of the
 //     accumulator tile with a per-query threshold and appends the rare survivors to the query's
 //     candidate buffer with plain stores; the L = K + slack best are kept.  No N x N matrix is written.
@@ -39,6 +40,11 @@
 // Epilogue: a thread first reduces its 32 keys of a chunk to their minimum (a tree of independent
 // min operations); only if that minimum beats the threshold, which becomes rare as the scan
 // proceeds, does it locate and append the survivors.
+//
+// Order of the scan.  Queries and database rows are visited by Voronoi cells around sample points; a block
+// skips the database cells none of its queries can reach under their thresholds (triangle inequality, see
+// the knn_cells_* kernels), which leaves the result untouched and removes most tile pairs on clustered
+// data.  A database image much larger than L2 is scanned in windows, one launch per window.
 //
 // Warp roles: a block serves QH = 2 query tiles (256 queries; 1 when the operand images are too wide for
 // that) against every database tile, so a database image is fetched from L2 once per 256 queries.

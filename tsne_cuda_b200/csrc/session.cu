@@ -2,11 +2,13 @@
 // points to affinities, and the gradient loop (reference: the body of tsnecuda::RunTsne,
 // src/fit_tsne.cu:84-166 for the set-up and :402-580 for the loop).
 //
-// One iteration is seven kernels and no host synchronisation:
-//   stream  : spread -> FFT rows -> FFT columns -> FFT rows^-1 -> gather ------------> update
-//   stream2 : attractive (HBM-bound, overlaps the latency-bound grid pipeline) ------^
+// One iteration is seven kernels (ten when the spread order is refreshed) and no host synchronisation:
+//   stream  : [order x3] -> spread -> FFT rows -> FFT columns -> FFT rows^-1 -> gather --> update
+//   stream2 : attractive (gather-bound; overlaps the latency-bound grid pipeline) ------^
 // The embedding's min/max and the normalisation sum travel between kernels in device memory
 // (IterState), so the two per-iteration host round trips of the reference do not exist.
+// A sharded run adds two meetings of the ranks per iteration and exchanges over peer memory
+// (peer.h): spread -> meet -> sum of the partial grids -> FFT ... update into every rank -> meet.
 #include "session.h"
 
 #include <math.h>
