@@ -77,6 +77,7 @@ int Session::init(int64_t N_, int K_, int64_t lo, int64_t hi, int device_)
     B200_TRY(launch_order_identity(order, rows(), stream));
     if (const char *e = getenv("B200TSNE_ORDER_REFRESH")) order_refresh = atoi(e);
     if (const char *e = getenv("B200TSNE_ORDER_REFRESH_EARLY")) order_refresh_early = std::max(1, atoi(e));
+    if (const char *e = getenv("B200TSNE_GRAPHS")) use_graphs = atoi(e) != 0;
     B200_TRY(arena.alloc((void **)&Y2, sizeof(float2) * npad));
     B200_TRY(arena.alloc((void **)&Fattr, sizeof(float2) * npad));
     B200_TRY(arena.alloc((void **)&Frep, sizeof(float2) * npad));
@@ -108,6 +109,7 @@ void Session::destroy()
     cudaSetDevice(device);
     if (stream) cudaStreamSynchronize(stream);
     if (stream2) cudaStreamSynchronize(stream2);
+    drop_graphs();
     if (px) { peer_exchange_release(px, comm); px = nullptr; }
     comm = nullptr;  // owned by the communicator cache (comm.h)
     arena.release();
@@ -280,6 +282,76 @@ int Session::one_iteration(bool want_norm)
     return 0;
 }
 
+void Session::drop_graphs()
+{
+    for (IterGraph &g : graphs) {
+        if (g.exec) cudaGraphExecDestroy(g.exec);
+        g = IterGraph();
+    }
+}
+
+// Which graph covers the iterations from `step` on, and how many of them; 0 when the next iteration has to be
+// launched directly (misaligned with the block, a phase boundary inside it, or a feature graphs do not carry).
+int Session::graph_block(int remaining, bool want_norm, int *kind) const
+{
+    if (!use_graphs || stage_timers || want_norm || (comm && comm->world > 1) || order_refresh_early != 1) return 0;
+    const int settle_end = force_magnify_iters + 50;
+    int k, block, limit;
+    if (step < force_magnify_iters) { k = 0; block = 2; limit = force_magnify_iters; }
+    else if (step < settle_end) { k = 1; block = 2; limit = settle_end; }
+    else { k = 2; block = order_refresh > 0 ? 2 * order_refresh : 2; limit = INT_MAX; }
+    if (step % block != 0 || remaining < block || (long long)step + block > limit) return 0;
+    *kind = k;
+    return block;
+}
+
+int Session::run_graph_block(int kind, int iters)
+{
+    IterGraph &g = graphs[kind];
+    const bool late = kind > 0;
+    const float momentum = late ? post_momentum : pre_momentum, exag = late ? 1.0f : exaggeration;
+    if (g.exec && (g.iters != iters || g.eta != eta || g.exaggeration != exag || g.momentum != momentum || g.refresh != order_refresh)) {
+        cudaGraphExecDestroy(g.exec);
+        g = IterGraph();
+    }
+    if (!g.exec) {
+        // capture: the launches are recorded, not run, so the host-side counters are put back afterwards
+        const int step0 = step;
+        const int64_t launches0 = launches;
+        int32_t *const order0 = order;
+        cudaGraph_t graph = nullptr;
+        B200_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+        int rc = 0;
+        for (int b = 0; b < iters && rc == 0; b++) rc = one_iteration(false);
+        const cudaError_t end = cudaStreamEndCapture(stream, &graph);
+        g.launches = launches - launches0;
+        step = step0;
+        launches = launches0;
+        const bool same_order = order == order0;
+        if (!same_order) std::swap(order, order_alt);
+        if (rc != 0 || end != cudaSuccess || !graph || !same_order) {
+            if (graph) cudaGraphDestroy(graph);
+            (void)cudaGetLastError();
+            use_graphs = false;   // the caller falls back to direct launches
+            return 1;
+        }
+        const cudaError_t inst = cudaGraphInstantiate(&g.exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (inst != cudaSuccess) {
+            (void)cudaGetLastError();
+            g = IterGraph();
+            use_graphs = false;
+            return 1;
+        }
+        g.iters = iters;
+        g.eta = eta; g.exaggeration = exag; g.momentum = momentum; g.refresh = order_refresh;
+    }
+    B200_CUDA(cudaGraphLaunch(g.exec, stream));
+    step += iters;
+    launches += g.launches;
+    return 0;
+}
+
 int Session::iterate(int n_iters, float min_gradient_norm, float *elapsed_ms, int *iters_done)
 {
     B200_CUDA(cudaSetDevice(device));
@@ -288,6 +360,13 @@ int Session::iterate(int n_iters, float min_gradient_norm, float *elapsed_ms, in
     int done = 0;
     B200_CUDA(cudaEventRecord(ev_t0, stream));
     for (int it = 0; it < n_iters; it++) {
+        int kind = 0;
+        const int block = graph_block(n_iters - it, want_norm, &kind);
+        if (block > 0) {
+            const int rc = run_graph_block(kind, block);
+            if (rc < 0) return rc;
+            if (rc == 0) { done += block; it += block - 1; continue; }
+        }
         if (want_norm) B200_CUDA(cudaMemsetAsync(&state->unorm2, 0, sizeof(double), stream));
         B200_TRY(one_iteration(want_norm));
         done++;

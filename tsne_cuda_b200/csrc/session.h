@@ -76,6 +76,24 @@ struct Session {
     float4 *w_sum = nullptr;
     int attach_peer_exchange();   // collective, after comm is set
 
+    // Captured iterations (single GPU, no stage timers, no update norm): at small N the loop is bound by the
+    // launch and dependency latency of its ten kernels, so whole blocks of iterations are replayed as CUDA
+    // graphs.  One graph per phase of the schedule: [0] exaggerated, [1] the 50 iterations after, [2]
+    // settled.  A block holds an even number of iterations (the state slots alternate) and an even number
+    // of order refreshes (the two order buffers swap at each).
+    struct IterGraph {
+        cudaGraphExec_t exec = nullptr;
+        int iters = 0;
+        int64_t launches = 0;
+        float eta = 0, exaggeration = 0, momentum = 0;
+        int refresh = 0;
+    };
+    IterGraph graphs[3];
+    bool use_graphs = true;   // B200TSNE_GRAPHS=0 turns them off
+    int graph_block(int remaining, bool want_norm, int *kind) const;   // iterations the next graph would cover, 0 = none
+    int run_graph_block(int kind, int iters);
+    void drop_graphs();
+
     int64_t rows() const { return row_hi - row_lo; }
     int init(int64_t N, int K, int64_t row_lo, int64_t row_hi, int device);
     void destroy();
