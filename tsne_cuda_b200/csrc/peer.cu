@@ -43,9 +43,14 @@ constexpr int kMinMaxOffset = 2 * kMaxPeers;
 // waits until rank r's slot of the local array has reached it; gives up after 2 s.  With `state` the ranks also
 // exchange the min/max of the rows they have just updated (IterState slot mm_slot) and leave the global
 // min/max there, which replaces a pass over the whole embedding.
-__global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int value, IterState *state, int mm_slot, int *err)
+__global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int *epochs, IterState *state, int mm_slot, int *err)
 {
     const int lane = threadIdx.x;
+    // the meeting's number: a device counter per kind that every rank advances alike (a launch parameter
+    // would be frozen into a captured graph)
+    unsigned int value = 0;
+    if (lane == 0) value = ++epochs[kind];
+    value = __shfl_sync(0xffffffffu, value, 0);
     unsigned int my_min = 0, my_max = 0;
     if (state) { my_min = state->min_enc[mm_slot]; my_max = state->max_enc[mm_slot]; }
     __threadfence_system();   // everything this stream wrote before (kernel boundary) is ordered before the flag
@@ -251,9 +256,9 @@ void peer_exchange_destroy(PeerExchange *px, Comm *comm, cudaStream_t st)
     delete px;
 }
 
-int launch_peer_barrier(PeerExchange *px, int kind, unsigned int value, IterState *state, int mm_slot, cudaStream_t st)
+int launch_peer_barrier(PeerExchange *px, int kind, IterState *state, int mm_slot, cudaStream_t st)
 {
-    peer_barrier_kernel<<<1, 32, 0, st>>>(px->tab, kind, value, state, mm_slot, px->err);
+    peer_barrier_kernel<<<1, 32, 0, st>>>(px->tab, kind, reinterpret_cast<unsigned int *>(px->err) + 2, state, mm_slot, px->err);
     B200_CUDA(cudaGetLastError());
     return 0;
 }

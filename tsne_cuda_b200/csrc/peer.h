@@ -44,8 +44,7 @@ struct PeerExchange {
     PeerTable tab;
     void *local = nullptr;       // this rank's block
     void *mapped[kMaxPeers];     // peers' blocks as mapped here (null for this rank)
-    int *err = nullptr;          // device word: a bounded wait expired
-    unsigned int epoch = 0;      // last epoch signalled (one per iteration, never reset)
+    int *err = nullptr;          // device words: [0] a bounded wait expired, [1] scratch of the closing meeting, [2], [3] epoch counters per kind
     int parity = 0;              // which of the two buffers holds the current embedding / grid (alike on all ranks)
     int64_t npad = 0;
 
@@ -62,9 +61,9 @@ void peer_exchange_release(PeerExchange *px, Comm *comm);
 // Collective: unmaps the peers, meets the other ranks, then frees the local block.
 void peer_exchange_destroy(PeerExchange *px, Comm *comm, cudaStream_t st);
 
-// All ranks meet: publish `value` for `kind` everywhere, wait (bounded) until every rank has.  With `state`, the
+// All ranks meet: publish the next epoch of `kind` everywhere, wait (bounded) until every rank has.  With `state`, the
 // ranks' min/max encodings in IterState slot mm_slot are combined across the ranks on the way.
-int launch_peer_barrier(PeerExchange *px, int kind, unsigned int value, IterState *state, int mm_slot, cudaStream_t st);
+int launch_peer_barrier(PeerExchange *px, int kind, IterState *state, int mm_slot, cudaStream_t st);
 // w_sum[node] = sum over ranks (in rank order) of their partial grid `buf`
 int launch_peer_grid_reduce(PeerExchange *px, int buf, float4 *w_sum, cudaStream_t st);
 // state->zsum[slot] += sum over nodes of the bilinear form of charges w_sum and potentials ytilde

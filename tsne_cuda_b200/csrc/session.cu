@@ -191,9 +191,7 @@ int Session::one_iteration(bool want_norm)
     const bool p2p = multi && px != nullptr;   // exchanges over peer memory instead of collectives
     StageClock clk(this);
     cudaStream_t sa = stage_timers ? stream : stream2;  // attractive stream
-    unsigned int epoch = 0;
     if (p2p) {
-        epoch = ++px->epoch;
         // the grid buffer of the next iteration: the peers finished reading it before they signalled the
         // update this rank waited for at the end of the previous iteration
         B200_CUDA(cudaMemsetAsync(px->w_local(px->parity ^ 1), 0, sizeof(float4) * kG * kG, stream));
@@ -221,7 +219,7 @@ int Session::one_iteration(bool want_norm)
     clk.end(stream, kStSpread, 1);
     if (p2p) {
         clk.begin(stream);
-        B200_TRY(launch_peer_barrier(px, kFlagSpread, epoch, nullptr, 0, stream));
+        B200_TRY(launch_peer_barrier(px, kFlagSpread, nullptr, 0, stream));
         B200_TRY(launch_peer_grid_reduce(px, px->parity, w_sum, stream));
         clk.end(stream, kStExchange, 2);
     } else if (multi) {
@@ -266,7 +264,7 @@ int Session::one_iteration(bool want_norm)
     if (p2p) {
         clk.begin(stream);
         // the update kernel left this rank's min/max in slot^1; the meeting makes them global
-        B200_TRY(launch_peer_barrier(px, kFlagUpdate, epoch, state, slot ^ 1, stream));
+        B200_TRY(launch_peer_barrier(px, kFlagUpdate, state, slot ^ 1, stream));
         px->parity ^= 1;
         Y2 = px->y_local(px->parity);
         w = px->w_local(px->parity);
@@ -294,7 +292,8 @@ void Session::drop_graphs()
 // launched directly (misaligned with the block, a phase boundary inside it, or a feature graphs do not carry).
 int Session::graph_block(int remaining, bool want_norm, int *kind) const
 {
-    if (!use_graphs || stage_timers || want_norm || (comm && comm->world > 1) || order_refresh_early != 1) return 0;
+    // (a sharded run qualifies when it exchanges over peer memory: its meetings are kernels of this library)
+    if (!use_graphs || stage_timers || want_norm || (comm && comm->world > 1 && !px) || order_refresh_early != 1) return 0;
     const int settle_end = force_magnify_iters + 50;
     int k, block, limit;
     if (step < force_magnify_iters) { k = 0; block = 2; limit = force_magnify_iters; }
@@ -310,7 +309,9 @@ int Session::run_graph_block(int kind, int iters)
     IterGraph &g = graphs[kind];
     const bool late = kind > 0;
     const float momentum = late ? post_momentum : pre_momentum, exag = late ? 1.0f : exaggeration;
-    if (g.exec && (g.iters != iters || g.eta != eta || g.exaggeration != exag || g.momentum != momentum || g.refresh != order_refresh)) {
+    const int parity = px ? px->parity : 0;   // which exchange buffers the block starts from
+    if (g.exec && (g.iters != iters || g.eta != eta || g.exaggeration != exag || g.momentum != momentum || g.refresh != order_refresh ||
+                   g.parity != parity)) {
         cudaGraphExecDestroy(g.exec);
         g = IterGraph();
     }
@@ -327,8 +328,9 @@ int Session::run_graph_block(int kind, int iters)
         g.launches = launches - launches0;
         step = step0;
         launches = launches0;
-        const bool same_order = order == order0;
-        if (!same_order) std::swap(order, order_alt);
+        const bool same_order = order == order0 && (!px || px->parity == parity);
+        if (order != order0) std::swap(order, order_alt);
+        if (px && px->parity != parity) { px->parity = parity; Y2 = px->y_local(parity); w = px->w_local(parity); }
         if (rc != 0 || end != cudaSuccess || !graph || !same_order) {
             if (graph) cudaGraphDestroy(graph);
             (void)cudaGetLastError();
@@ -344,7 +346,7 @@ int Session::run_graph_block(int kind, int iters)
             return 1;
         }
         g.iters = iters;
-        g.eta = eta; g.exaggeration = exag; g.momentum = momentum; g.refresh = order_refresh;
+        g.eta = eta; g.exaggeration = exag; g.momentum = momentum; g.refresh = order_refresh; g.parity = parity;
     }
     B200_CUDA(cudaGraphLaunch(g.exec, stream));
     step += iters;

@@ -76,7 +76,7 @@ struct Session {
     float4 *w_sum = nullptr;
     int attach_peer_exchange();   // collective, after comm is set
 
-    // Captured iterations (single GPU, no stage timers, no update norm): at small N the loop is bound by the
+    // Captured iterations (single GPU or peer-memory exchange, no stage timers, no update norm): at small N the loop is bound by the
     // launch and dependency latency of its ten kernels, so whole blocks of iterations are replayed as CUDA
     // graphs.  One graph per phase of the schedule: [0] exaggerated, [1] the 50 iterations after, [2]
     // settled.  A block holds an even number of iterations (the state slots alternate) and an even number
@@ -86,7 +86,7 @@ struct Session {
         int iters = 0;
         int64_t launches = 0;
         float eta = 0, exaggeration = 0, momentum = 0;
-        int refresh = 0;
+        int refresh = 0, parity = 0;
     };
     IterGraph graphs[3];
     bool use_graphs = true;   // B200TSNE_GRAPHS=0 turns them off
