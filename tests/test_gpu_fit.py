@@ -42,6 +42,31 @@ def test_session_matches_reference_quality(engine, oracle_cpu, golden):
     assert abs(nnp - float(golden["nnp_fit"])) < 0.005 + 0.01
 
 
+def test_graph_replay_equals_direct_launches(engine, oracle_cpu, golden, monkeypatch):
+    """Blocks of iterations replayed as CUDA graphs run the same kernels with the same arguments as direct
+    launches: same launch count and step; embeddings equal up to the order of the spread's floating-point
+    reductions, which the iterations amplify (so the long run is compared by its KL, as for chunked runs)."""
+    P, ids, Y0 = golden["P"], golden["ids"], golden["Y_a"]
+    N, K = P.shape
+    out = []
+    for graphs in ("1", "0"):
+        monkeypatch.setenv("B200TSNE_GRAPHS", graphs)      # read when the session is created
+        with engine.Session(N, K) as s:
+            s.set_affinities(P, ids)
+            s.set_schedule(200.0, 12.0, 6, 0.5, 0.8)       # phase change after 6 iterations
+            s.set_embedding(Y0)
+            l0 = s.launch_count()
+            s.run(3)                                        # leaves the step odd: the next iteration is launched directly
+            s.run(17)
+            Y20 = s.get_embedding()
+            s.run(62)                                       # crosses the second phase boundary and reaches the 16-iteration blocks
+            out.append((Y20, s.get_embedding(), s.launch_count() - l0, s.stats()["step"]))
+    assert out[0][2] == out[1][2] and out[0][3] == out[1][3] == 82
+    assert rel_l2(out[0][0], out[1][0]) < 2e-3
+    kl = [oracle_cpu.kl_divergence(P, ids, o[1]) for o in out]
+    assert abs(kl[0] - kl[1]) / kl[1] < 0.02
+
+
 def test_chunked_run_equals_single_run_in_quality(engine, oracle_cpu, golden):
     """Running the loop in pieces follows the same schedule; only the order of the spread's floating-point
     reductions differs, which exaggerated iterations amplify, so the runs are compared by their KL."""
