@@ -215,6 +215,11 @@ void b200tsne_comm_release_all(void);
  * ranks).  With mode 2, destroying the session is collective: all ranks must call it. */
 int b200tsne_session_exchange_mode(b200tsne_session *s);
 
+/* Device memory the library has freed stays in the device's default memory pool so that the next call
+ * gets it back without going to the driver (no reference counterpart: the reference allocates with
+ * thrust per call).  This returns the pool of `device` to the driver. */
+int b200tsne_release_cached_memory(int device);
+
 #ifdef __cplusplus
 }
 #endif

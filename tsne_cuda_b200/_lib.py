@@ -71,6 +71,7 @@ SIGNATURES = {
     "b200tsne_session_attach_comm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "b200tsne_comm_release_all": (None, []),
     "b200tsne_session_exchange_mode": (C.c_int, [C.c_void_p]),
+    "b200tsne_release_cached_memory": (C.c_int, [C.c_int]),
 }
 for _name, (_res, _args) in SIGNATURES.items():
     _fn = getattr(lib, _name)
@@ -286,6 +287,11 @@ def comm_unique_id():
     buf = C.create_string_buffer(128)
     check(lib.b200tsne_comm_unique_id(buf))
     return buf.raw
+
+
+def release_cached_memory(device=0):
+    """Return the device memory the library keeps for reuse to the driver."""
+    check(lib.b200tsne_release_cached_memory(device))
 
 
 def comm_release_all():

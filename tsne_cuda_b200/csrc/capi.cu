@@ -383,6 +383,12 @@ int b200tsne_session_attach_comm(b200tsne_session *h, const void *id128, int ran
 
 void b200tsne_comm_release_all(void) { comm_release_all(); }
 
+int b200tsne_release_cached_memory(int device)
+{
+    B200_CUDA(cudaSetDevice(device));
+    return release_cached_memory();
+}
+
 int b200tsne_session_exchange_mode(b200tsne_session *h)
 {
     if (!h || !h->s.comm || h->s.comm->world < 2) return 0;

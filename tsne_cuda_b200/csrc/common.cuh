@@ -18,6 +18,7 @@ constexpr int kStages = 9;             // instrumented stages (== B200TSNE_N_STA
 // ---- error plumbing ----
 void set_error(const std::string &msg);
 const std::string &last_error();
+int release_cached_memory();   // session.cu: hand the device memory pool of the current device back to the driver
 int cuda_fail(cudaError_t e, const char *what, const char *file, int line);
 
 #define B200_CUDA(expr)                                                        \

@@ -35,18 +35,50 @@ int cuda_fail(cudaError_t e, const char *what, const char *file, int line)
 }
 
 // ---- arena ------------------------------------------------------------------------------------
+// Device memory comes from the device's default stream-ordered pool with the release threshold lifted, so
+// what one call frees the next call gets back without a trip to the driver (a fit allocates and frees
+// about 5 GB at N = 10^6; cudaMalloc/cudaFree of that cost tens of milliseconds per call).  Every arena
+// is released only after the streams that used its memory have been synchronised, so the memory may be
+// handed to any stream afterwards.  b200tsne_release_cached_memory() returns the pool to the driver.
+static int configure_pool()
+{
+    static bool done[64] = {false};
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || done[dev]) return 0;
+    cudaMemPool_t pool;
+    B200_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+    unsigned long long keep = ~0ull;
+    B200_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+    done[dev] = true;
+    return 0;
+}
+
+int release_cached_memory()
+{
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    cudaMemPool_t pool;
+    B200_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+    B200_CUDA(cudaDeviceSynchronize());
+    B200_CUDA(cudaMemPoolTrimTo(pool, 0));
+    return 0;
+}
+
 DeviceArena::~DeviceArena() { release(); }
 int DeviceArena::alloc(void **p, size_t bytes)
 {
     *p = nullptr;
     if (bytes == 0) bytes = 16;
-    B200_CUDA(cudaMalloc(p, bytes));
+    B200_TRY(configure_pool());
+    B200_CUDA(cudaMallocAsync(p, bytes, cudaStreamPerThread));
     ptrs.push_back(*p);
     return 0;
 }
 void DeviceArena::release()
 {
-    for (void *p : ptrs) cudaFree(p);
+    for (void *p : ptrs) cudaFreeAsync(p, cudaStreamPerThread);
+    if (!ptrs.empty()) cudaStreamSynchronize(cudaStreamPerThread);
     ptrs.clear();
 }
 
