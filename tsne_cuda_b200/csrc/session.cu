@@ -73,6 +73,14 @@ int DeviceArena::alloc(void **p, size_t bytes)
     B200_TRY(configure_pool());
     B200_CUDA(cudaMallocAsync(p, bytes, cudaStreamPerThread));
     ptrs.push_back(*p);
+    // B200TSNE_POISON=1 fills every new allocation with 0xFF bytes (NaN floats, -1 ints): pooled memory is not
+    // zero like fresh device memory often is, and this makes any read of memory the library has not written
+    // show up at once (the GPU suite passes with it)
+    static const bool poison = getenv("B200TSNE_POISON") && atoi(getenv("B200TSNE_POISON")) != 0;
+    if (poison) {
+        B200_CUDA(cudaMemsetAsync(*p, 0xff, bytes, cudaStreamPerThread));
+        B200_CUDA(cudaStreamSynchronize(cudaStreamPerThread));
+    }
     return 0;
 }
 void DeviceArena::release()
