@@ -80,6 +80,16 @@ def test_knn_tensor_core_wide_points(engine, monkeypatch, n, d, k):
     assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
 
 
+def test_cached_device_memory_can_be_released(engine):
+    """Freed device memory stays in the device's pool for the next call; releasing it to the driver must leave the
+    library usable (and the result unchanged)."""
+    X = mixture(3000, 20, 9)
+    a = engine.knn(X, 30)
+    engine.release_cached_memory()
+    b = engine.knn(X, 30)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
 def test_knn_ties_and_duplicates(engine, oracle_cpu):
     X = np.zeros((300, 4), np.float32)
     X[100:200] = 1.0
