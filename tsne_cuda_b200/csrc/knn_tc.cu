@@ -34,7 +34,8 @@
 // levels, each sizing the candidate set of the next: (A) on the CUDA cores, the key of rank ~10 among a
 // few thousand jittered sample points; (B) every 16th tile against tau_A (~300 candidates); (C) all
 // tiles against tau_B = the key of rank ~3L/16 of sample B, which about 3L points beat.  Nothing is
-// compacted during a fixed-threshold scan; the L best are selected once at the end.  A row whose buffer
+// compacted during a fixed-threshold scan; the L best are selected once at the end (by bisection on the
+// key bits, not by sorting).  A row whose buffer
 // overflows or ends with fewer than L candidates is flagged and recomputed by the SIMT search.
 //
 // Epilogue: a thread first reduces its 32 keys of a chunk to their minimum (a tree of independent
@@ -554,7 +555,7 @@ struct TcShared {
 // on return the first L = 16*EPL entries of each are the L best keys in ascending order ((+inf, INT_MAX)
 // where the database had fewer points).  FIXED = true: threshold tau[query] fixed, two segments of cap/2
 // entries per query; counts[2*query + buffer] receives the number of entries appended to each (bit 30 set
-// if it overflowed); knn_tc_select_kernel finishes.
+// if it overflowed); knn_tc_pick_kernel finishes.
 template <int EPL, bool FIXED, int QH>
 __global__ void __launch_bounds__(tc_threads(QH), 1)
 knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int Dp, long long nq, long long nd_pos,
@@ -988,46 +989,91 @@ knn_tc_wide_kernel(const float *__restrict__ img_q, const float *__restrict__ im
 // ------------------------------------------------------------------------------------------------
 // final selection after a fixed-threshold scan: one warp per query
 // ------------------------------------------------------------------------------------------------
-// Buffer of query q: two halves of cap/2 entries with counts[2q], counts[2q+1] valid entries.  Leaves the L
-// best (ascending) in front and sets row_flags[q]: bit 0 = a half overflowed (keys below tau were lost),
-// bit 1 = fewer than L candidates.
-template <int EPL>
+// Buffer of query q: two segments of cap/2 entries with counts[2q], counts[2q+1] valid entries (bit 30 of a
+// count: the segment overflowed, i.e. keys below tau were lost).
+// The k smallest keys of the buffer by selection rather than sorting (a warp-wide bitonic sort of the buffer
+// was measured at ~17 000 issue slots per query, this takes ~1 500).  The warp holds the keys in
+// registers as order-preserving integers, finds the k-th smallest value v by bisection on the 32 bits (each
+// step counts the keys <= mid), keeps every key below v and as many of the keys equal to v as are needed.
+// kth[q] (optional) = v, or -inf when the buffer lost keys or holds fewer than k; out_* (optional) receive
+// the k kept pairs in buffer order, padded with (+inf, INT_MAX); row_flags[q]: bit 0 = a segment overflowed,
+// bit 1 = fewer than k candidates.
+template <int SLOTS>
 __global__ void __launch_bounds__(128)
-knn_tc_select_kernel(float *cand_key, int32_t *cand_id, int cap, const int *__restrict__ counts, long long nq,
-                     int *__restrict__ row_flags)
+knn_tc_pick_kernel(const float *__restrict__ cand_key, const int32_t *__restrict__ cand_id, int cap, const int *__restrict__ counts,
+                   long long nq, int k, float *__restrict__ out_key, int32_t *__restrict__ out_id, int out_stride,
+                   float *__restrict__ kth, int *__restrict__ row_flags)
 {
-    constexpr int C = 32 * EPL, L = 16 * EPL;
     const int lane = threadIdx.x & 31;
     const long long q = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (q >= nq) return;
-    float *ok = cand_key + q * cap;
-    int32_t *oi = cand_id + q * cap;
     const int c0 = counts[2 * q], c1 = counts[2 * q + 1];
     const bool ovf = ((c0 | c1) & 0x40000000) != 0;
-    int n = c0 & 0x3fffffff;
-    const int n1 = c1 & 0x3fffffff;
-    for (int e0 = 0; e0 < n1; e0 += 32) {   // bring the second half next to the first (moving down, 32 at a time)
-        const int e = e0 + lane;
-        float kk = 0.0f;
-        int ii = 0;
-        if (e < n1) { kk = __ldcg(ok + cap / 2 + e); ii = __ldcg(oi + cap / 2 + e); }
-        __syncwarp();
-        if (e < n1) { __stcg(ok + n + e, kk); __stcg(oi + n + e, ii); }
-        __syncwarp();
+    const int n0 = c0 & 0x3fffffff, n1 = c1 & 0x3fffffff, n = n0 + n1;
+    const int jmax = (n + 31) / 32;
+    const float *bk = cand_key + q * cap;
+    const int32_t *bi = cand_id + q * cap;
+    unsigned int enc[SLOTS];
+#pragma unroll
+    for (int j = 0; j < SLOTS; j++) {
+        const int e = lane + 32 * j;
+        enc[j] = 0xffffffffu;
+        if (e < n) enc[j] = enc_float(__ldcg(bk + (e < n0 ? e : cap / 2 + (e - n0))));
     }
-    n += n1;
-    const int first = min(n, C);
-    (void)warp_compact<EPL>(ok, oi, first, lane);
-    for (int pos = first; pos < n; pos += C - L) {     // fold the rest in, C - L at a time
-        const int chunk = min(C - L, n - pos);
-        for (int e = lane; e < chunk; e += 32) {
-            __stcg(ok + L + e, __ldcg(ok + pos + e));
-            __stcg(oi + L + e, __ldcg(oi + pos + e));
+    unsigned int v = 0xffffffffu;   // with fewer than k keys everything is kept
+    if (n > k) {
+        unsigned int lo = 0u, hi = 0xfffffffeu;
+#pragma unroll 1
+        for (int it = 0; it < 32; it++) {
+            const unsigned int mid = lo + ((hi - lo) >> 1);
+            int cnt = 0;
+#pragma unroll
+            for (int j = 0; j < SLOTS; j++) {
+                if (j >= jmax) break;
+                cnt += (enc[j] <= mid) ? 1 : 0;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+            if (cnt >= k) hi = mid;
+            else lo = mid + 1;
         }
-        __syncwarp();
-        (void)warp_compact<EPL>(ok, oi, L + chunk, lane);
+        v = lo;
     }
-    if (lane == 0) row_flags[q] = (ovf ? 1 : 0) | (n < L ? 2 : 0);
+    const bool short_list = n < k;
+    if (kth && lane == 0) kth[q] = (ovf || short_list) ? -INFINITY : dec_float(v);
+    if (lane == 0) row_flags[q] = (ovf ? 1 : 0) | (short_list ? 2 : 0);
+    if (!out_key) return;
+    // keys below v, then as many keys equal to v as fit
+    int below = 0;
+#pragma unroll
+    for (int j = 0; j < SLOTS; j++) {
+        if (j >= jmax) break;
+        below += (enc[j] < v) ? 1 : 0;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) below += __shfl_xor_sync(0xffffffffu, below, o);
+    int room_eq = min(k, n) - below;     // keys equal to v still to take (n <= k: v is above every key, all are "below")
+    int out_pos = 0;
+    float *ok = out_key + q * out_stride;
+    int32_t *oi = out_id + q * out_stride;
+    const unsigned int lt = (1u << lane) - 1u;
+#pragma unroll
+    for (int j = 0; j < SLOTS; j++) {
+        if (j >= jmax) break;
+        const int e = lane + 32 * j;
+        const bool is_eq = enc[j] == v && e < n;
+        const unsigned int eqmask = __ballot_sync(0xffffffffu, is_eq);
+        const bool keep = (e < n) && (enc[j] < v || (is_eq && __popc(eqmask & lt) < room_eq));
+        const unsigned int keepmask = __ballot_sync(0xffffffffu, keep);
+        if (keep) {
+            const int slot = e < n0 ? e : cap / 2 + (e - n0);
+            ok[out_pos + __popc(keepmask & lt)] = dec_float(enc[j]);
+            oi[out_pos + __popc(keepmask & lt)] = __ldcg(bi + slot);
+        }
+        out_pos += __popc(keepmask);
+        room_eq -= min(room_eq, __popc(eqmask));
+    }
+    for (int e = out_pos + lane; e < k; e += 32) { ok[e] = INFINITY; oi[e] = INT_MAX; }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1268,19 +1314,6 @@ knn_sample_tau_wide_kernel(const float *__restrict__ X, int D, const int *__rest
     }
 }
 
-// tau[q] = key of rank `rank` (0-based) in the sorted sample list of query q.  A list shorter than that,
-// or a sample pass that flagged the row, gives -inf: the next pass keeps nothing for the row, flags it,
-// and the row is recomputed by the SIMT search.  (When the whole database is smaller than the list the
-// caller does not use a sample pass.)
-__global__ void knn_tc_tau_kernel(const float *__restrict__ sample_key, const int32_t *__restrict__ sample_id, int stride,
-                                  int rank, const int *__restrict__ flags, long long nq, float *__restrict__ tau)
-{
-    const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (q >= nq) return;
-    const bool bad = sample_id[q * stride + rank] == INT_MAX || (flags && (flags[q] & 1));   // overflow loses keys below tau; a short list does not
-    tau[q] = bad ? -INFINITY : sample_key[q * stride + rank];
-}
-
 __global__ void knn_tc_collect_failed_kernel(const int *__restrict__ failed, long long nq, const int *__restrict__ qlist, int *__restrict__ list,
                                              int *__restrict__ count)
 {
@@ -1516,29 +1549,31 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         B200_TRY(prune());
         const unsigned sel_grid = (unsigned)((nq + 3) / 4);
         if (!direct) {
+            // level B: only the key of rank rank_b among the sample's candidates is needed
             if (EPL == 8) {
                 B200_KNN_FILTER(8, true, kSampleStride, tau, kFixedCap, fix_key, fix_id, counts);
-                knn_tc_select_kernel<8><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, row_flags);
+                knn_tc_pick_kernel<32><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, rank_b + 1, nullptr, nullptr, 0, tau,
+                                                                 row_flags);
             } else {
                 B200_KNN_FILTER(16, true, kSampleStride, tau, kFixedCap, fix_key, fix_id, counts);
-                knn_tc_select_kernel<16><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, row_flags);
+                knn_tc_pick_kernel<64><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, rank_b + 1, nullptr, nullptr, 0, tau,
+                                                                 row_flags);
             }
-            B200_CUDA(cudaGetLastError());
-            knn_tc_tau_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(fix_key, fix_id, kFixedCap, rank_b, row_flags, nq, tau);
             B200_CUDA(cudaGetLastError());
             B200_TRY(prune());
         }
+        // level C: the L best go to the (otherwise unused) online buffers, in no particular order
         if (EPL == 8) {
             B200_KNN_FILTER(8, true, 1, tau, kFixedCap, fix_key, fix_id, counts);
-            knn_tc_select_kernel<8><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, row_flags);
+            knn_tc_pick_kernel<32><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, L, cand_key, cand_id, C, nullptr, row_flags);
         } else {
             B200_KNN_FILTER(16, true, 1, tau, kFixedCap, fix_key, fix_id, counts);
-            knn_tc_select_kernel<16><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, row_flags);
+            knn_tc_pick_kernel<64><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, L, cand_key, cand_id, C, nullptr, row_flags);
         }
         B200_CUDA(cudaGetLastError());
-        final_key = fix_key;
-        final_id = fix_id;
-        final_stride = kFixedCap;
+        final_key = cand_key;
+        final_id = cand_id;
+        final_stride = C;
     }
 #undef B200_KNN_FILTER
 #undef B200_KNN_FILTER_V
