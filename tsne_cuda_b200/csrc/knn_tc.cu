@@ -1076,6 +1076,19 @@ knn_tc_pick_kernel(const float *__restrict__ cand_key, const int32_t *__restrict
     for (int e = out_pos + lane; e < k; e += 32) { ok[e] = INFINITY; oi[e] = INT_MAX; }
 }
 
+// Xp[pos] = X[list[pos]] (zeros for padding): the database rows in visiting order.  The re-rank reads ~130 candidate
+// rows per query; in cell order the candidates of neighbouring queries share a few megabytes that stay in L2,
+// in the original order they are 200-byte reads scattered over the whole array.
+__global__ void knn_gather_rows_kernel(const float *__restrict__ X, const int *__restrict__ list, int D, long long n_pos,
+                                       float *__restrict__ Xp)
+{
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_pos * D) return;
+    const long long pos = t / D;
+    const int i = list[pos];
+    Xp[t] = (i >= 0) ? X[(long long)i * D + (t - pos * D)] : 0.0f;
+}
+
 // ------------------------------------------------------------------------------------------------
 // exact re-rank + proof
 // ------------------------------------------------------------------------------------------------
@@ -1101,8 +1114,9 @@ knn_tc_rerank_kernel(const float *__restrict__ X, int D, const int *__restrict__
                      const int32_t *__restrict__ cand_id, int L, int C, int K, const double *__restrict__ norms_exact,
                      float err_scale, const int *__restrict__ row_flags, int32_t *__restrict__ ids, float *__restrict__ d2,
                      int *__restrict__ failed,
-                     int *__restrict__ n_failed, float *__restrict__ max_err_ratio)
+                     int *__restrict__ n_failed, float *__restrict__ max_err_ratio, const float *__restrict__ Xp)
 {
+    // Xp (optional): the database rows in list order, Xp[pos] = X[dblist[pos]]
     __shared__ float s_d[kRerankWarps][kMaxL];
     __shared__ int s_i[kRerankWarps][kMaxL];
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1122,7 +1136,7 @@ knn_tc_rerank_kernel(const float *__restrict__ X, int D, const int *__restrict__
         const float key = cand_key[q * C + e];
         float dist = INFINITY;
         if (id != INT_MAX) {
-            dist = canon_dist(xq, X + (long long)id * D, D);
+            dist = canon_dist(xq, Xp ? Xp + (long long)pos * D : X + (long long)id * D, D);
             n_valid++;
             T = fmaxf(T, key);
             const double approx = ni + (double)key;
@@ -1348,6 +1362,7 @@ struct TcWorkspace {
     float *img_q, *img_db;
     double *norms_q;
     int *qlist, *dblist;
+    float *xp;   // database rows in list order (cells only)
     unsigned char *cell_q, *cell_db;
     CellTable *tab;
     int2 *segs;
@@ -1379,6 +1394,7 @@ static TcWorkspace tc_carve(void *base, int D, int K, long long nq, long long nd
     w.norms_q = reinterpret_cast<double *>(take(sizeof(double) * (size_t)w.tq * TM));
     w.qlist = reinterpret_cast<int *>(take(sizeof(int) * (size_t)w.tq * TM));
     w.dblist = reinterpret_cast<int *>(take(sizeof(int) * (size_t)w.td * TN));
+    w.xp = (w.cells > 1) ? reinterpret_cast<float *>(take(sizeof(float) * (size_t)w.td * TN * D)) : nullptr;
     w.cell_q = reinterpret_cast<unsigned char *>(take((size_t)nq));
     w.cell_db = reinterpret_cast<unsigned char *>(take((size_t)nd));
     w.tab = reinterpret_cast<CellTable *>(take(sizeof(CellTable)));
@@ -1441,6 +1457,7 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         knn_cells_scatter_kernel<<<gd, kCellThreads, 0, st>>>(w.cell_db, db_lo, nd, cells, w.tab, 1, w.dblist);
         knn_cells_scatter_kernel<<<gq, kCellThreads, 0, st>>>(w.cell_q, q_lo, nq, cells, w.tab, 0, w.qlist);
         nd_pos = w.td * TN;
+        knn_gather_rows_kernel<<<(unsigned)((nd_pos * D + 255) / 256), 256, 0, st>>>(X, w.dblist, D, nd_pos, w.xp);
     } else {
         knn_iota_kernel<<<(unsigned)((nd + 255) / 256), 256, 0, st>>>(w.dblist, db_lo, nd);
         knn_iota_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(w.qlist, q_lo, nq);
@@ -1586,7 +1603,7 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     const float err_scale = std::max(6.103515625e-05f, (float)(D + 8) * 2.384185791015625e-07f);   // max(2^-14, (D + 8) 2^-22)
     knn_tc_rerank_kernel<<<(unsigned)((nq + kRerankWarps - 1) / kRerankWarps), kRerankWarps * 32, 0, st>>>(
         X, D, w.qlist, w.dblist, q_lo, nq, final_key, final_id, L, final_stride, K, w.norms_q, err_scale, two_pass ? row_flags : nullptr, ids, d2,
-        failed, counters + 1, reinterpret_cast<float *>(counters + 3));
+        failed, counters + 1, reinterpret_cast<float *>(counters + 3), w.xp);
     B200_CUDA(cudaGetLastError());
     knn_tc_collect_failed_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(failed, nq, w.qlist, flist, counters + 2);
     B200_CUDA(cudaGetLastError());
