@@ -118,6 +118,8 @@ def run_ours(args):
     s.set_schedule(hp["learning_rate"], hp["early_exaggeration"], 250, 0.5, 0.8)
     s.set_embedding(Y0)
     s.run(args.warmup)
+    attr_mode, entries_per_group = s.attractive_mode()
+    sharded_check = sharded_parity(s, X, K, lo, hi, rank, world) if multi else None
 
     def barrier():
         if multi:
@@ -143,16 +145,22 @@ def run_ours(args):
     stages = s.stage_times()
     s.enable_stage_timers(False)
     stage_us = {k: v[0] / n_prof * 1e3 for k, v in stages.items() if v[1] > 0}
-    attr_s = stages["attractive"][0] / max(stages["attractive"][1], 1) * 1e-3
+    # the attractive stage of one iteration: the row-major kernel alone, or the blocked kernel with its two small
+    # companions (gather of the embedding into the cell order, scatter of the forces back), timed together
+    attr_s = stages["attractive"][0] / n_prof * 1e-3
     rows = hi - lo
     attr_bytes = 8.0 * rows * K + 16.0 * rows
     peak, peak_kind = load_peaks()
-    roof = {"bound": "hbm", "kernel": "attractive_kernel", "achieved": attr_bytes / attr_s / 1e9 if attr_s > 0 else None,
+    # dram__bytes_read + dram__bytes_write of one launch from the committed ncu captures, scaled by the units
+    # processed: row-major kernel 296.3 MB for 294.4 MB algorithmic (profiles/attractive_kernel_n400k.md);
+    # blocked kernel: its stream of 6-byte entries padded to whole lanes (profiles/attractive_blocked_kernel_n400k.md)
+    traffic_ratio = TRAFFIC_RATIO_BLOCKED if attr_mode else 296.3 / 294.4
+    roof = {"bound": "hbm", "kernel": "attractive_blocked_kernel" if attr_mode else "attractive_kernel",
+            "achieved": attr_bytes / attr_s / 1e9 if attr_s > 0 else None,
             "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-            # dram__bytes_read + dram__bytes_write of one launch, from the ncu capture at N = 400,000 summarised in
-            # profiles/attractive_kernel_n400k.md (296.3 MB for 294.4 MB algorithmic), scaled by the units processed
-            "traffic": attr_bytes * (296.3 / 294.4),
-            "algorithmic_bytes_per_launch": attr_bytes, "avg_launch_us": attr_s * 1e6}
+            "traffic": attr_bytes * traffic_ratio, "entries_per_row_and_tile": entries_per_group,
+            "algorithmic_bytes_per_launch": attr_bytes, "avg_launch_us": attr_s * 1e6,
+            "launches_timed_together": 3 if attr_mode else 1}
     roof["frac"] = roof["achieved"] / peak if roof["achieved"] else None
     it_bytes = iter_bytes(N, K) / world
     roof["iteration"] = {"achieved": it_bytes / (ms * 1e-3 / args.steps) / 1e9, "frac": it_bytes / (ms * 1e-3 / args.steps) / 1e9 / peak,
@@ -168,6 +176,8 @@ def run_ours(args):
                       "parallelism": "points sharded over %d GPU(s)" % world},
            "gpu_launches": int(launches), "setup_s": setup_s, "open_session_s": open_s, "stage_us_per_iteration": stage_us,
            "roofline": roof, "clocks": clk.summary()}
+    if sharded_check is not None:
+        out["sharded_check"] = sharded_check
 
     if rank == 0 and not multi and not args.no_e2e:
         out["e2e"] = e2e_ours(X, hp, Y0, args)
@@ -179,6 +189,32 @@ def run_ours(args):
         distributed.release_communicators()
         dist.destroy_process_group()
     return out if rank == 0 else None
+
+
+TRAFFIC_RATIO_BLOCKED = 0.90   # DRAM bytes / algorithmic bytes of the blocked kernel, from the committed capture
+
+
+def sharded_parity(s, X, K, lo, hi, rank, world):
+    """Evidence that N ranks compute what one does, printed with the bench line: 64 of this rank's neighbour
+    rows against the CPU oracle's exact search, and the largest difference between this rank's embedding and
+    rank 0's after the warm-up iterations (every rank must hold the same embedding)."""
+    import torch
+    import torch.distributed as dist
+    from oracle import cpu
+    _, ids = s.get_affinities()
+    q0 = lo + (hi - lo) // 2
+    q1 = min(hi, q0 + 64)
+    ids_o, _ = cpu.knn(X, K, q_lo=q0, q_hi=q1)
+    knn_ok = bool(np.array_equal(ids[q0 - lo:q1 - lo], ids_o))
+    Y = torch.from_numpy(s.get_embedding()).cuda()
+    Y0 = Y.clone()
+    dist.broadcast(Y0, 0)
+    diff = (Y - Y0).abs().max().reshape(1)
+    dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+    ok = torch.tensor([1 if knn_ok else 0], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return {"knn_rows_checked_per_rank": int(q1 - q0), "knn_rows_equal_cpu_oracle_on_all_ranks": bool(ok.item()),
+            "max_abs_embedding_difference_to_rank0": float(diff.item()), "exchange_mode": s.exchange_mode()}
 
 
 def e2e_ours(X, hp, Y0, args):
@@ -200,8 +236,26 @@ def e2e_ours(X, hp, Y0, args):
         times.append(time.time() - t0)
         assert np.isfinite(Y).all()
     T = sorted(times)[1]
+    # where the time goes: the same fit through the session entry points, phases timed on the host
+    from tsne_cuda_b200 import _lib
+    ph = [time.time()]
+    with _lib.Session(X.shape[0], hp["num_neighbors"]) as s:
+        ph.append(time.time())
+        s.affinities_from_points(X, hp["perplexity"], 1e-3)
+        ph.append(time.time())
+        s.set_schedule(hp["learning_rate"], hp["early_exaggeration"], 250, 0.5, 0.8)
+        s.set_embedding(Y0)
+        ph.append(time.time())
+        loop_ms, _ = s.run(n_iter)
+        ph.append(time.time())
+        s.get_embedding()
+        ph.append(time.time())
+    ph.append(time.time())
+    phases = {"open_session_s": ph[1] - ph[0], "h2d_points_knn_affinities_s": ph[2] - ph[1], "h2d_embedding_s": ph[3] - ph[2],
+              "iterations_s": ph[4] - ph[3], "iterations_device_s": loop_ms * 1e-3, "d2h_embedding_s": ph[5] - ph[4],
+              "close_s": ph[6] - ph[5]}
     return {"value": n_iter / T, "unit": "iterations/s", "fit_transform_s": T, "fit_transform_s_calls": times,
-            "iterations": n_iter, "warmup_calls": 1,
+            "iterations": n_iter, "warmup_calls": 1, "phases_session_api": phases,
             "h2d_bytes_per_step": (X.nbytes + Y0.nbytes) / n_iter, "d2h_bytes_per_step": Y0.nbytes / n_iter,
             "api": "tsne_cuda_b200.TSNE.fit_transform -> pymodule_tsne"}
 
@@ -271,11 +325,32 @@ def cpu_baseline(X, hp, Y0, args, budget_s=20.0):
             "sample": "%d full gradient iterations at N=%d K=%d on random affinities of the workload's shape" % (n, N, K)}
 
 
+def knn_in_child_process(X, K, config, n):
+    """The exact neighbour list the reference arm injects, computed by a CHILD python process so that the
+    process that times the reference never maps this repository's CUDA library.  The child regenerates the
+    seeded workload itself and leaves two .npy files in a temporary directory."""
+    import tempfile
+    tmp = tempfile.mkdtemp(prefix="b200tsne_knn_")
+    code = ("import sys, numpy as np; sys.path.insert(0, %r); from tsne_cuda_b200 import _lib, datasets; "
+            "X, hp = datasets.make(%r, n=%r); ids, d2 = _lib.knn(X, %d); "
+            "np.save(%r, ids); np.save(%r, d2)" %
+            (ROOT, config, n, K, os.path.join(tmp, "ids.npy"), os.path.join(tmp, "d2.npy")))
+    subprocess.check_call([sys.executable, "-c", code], stdout=sys.stderr)
+    ids, d2 = np.load(os.path.join(tmp, "ids.npy")), np.load(os.path.join(tmp, "d2.npy"))
+    for f in ("ids.npy", "d2.npy"):
+        os.remove(os.path.join(tmp, f))
+    os.rmdir(tmp)
+    assert ids.shape == (X.shape[0], K)
+    return ids, d2
+
+
 def run_reference(args):
     """The reference's own CUDA kernels (oracle/_ref, compiled from the reference tree for sm_100) through
     its own pymodule_tsne.  The reference's neighbour search is FAISS, which is not installed; the exact
-    neighbour list is computed beforehand (outside the timed region) and injected.  When the reference
-    build is absent the OpenMP port is timed instead."""
+    neighbour list is computed beforehand, outside the timed region and in another process, and injected.
+    `value` comes from the reference's own loop timers: median over five pairs of runs of
+    (loop time of warmup + steps iterations) - (loop time of warmup iterations).  When the reference build
+    is absent the OpenMP port is timed instead."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return None
@@ -293,32 +368,43 @@ def run_reference(args):
         base.update({"value": cb["value"], "ms_per_step": 1e3 / cb["value"], "cpu_baseline": cb,
                      "e2e": {"value": cb["value"], "unit": "iterations/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
         return base
-    from tsne_cuda_b200 import _lib
-    ids, d2 = _lib.knn(X, K)          # outside the timed region; stands in for the missing FAISS search
+    ids, d2 = knn_in_child_process(X, K, args.config, args.n)
     ref.set_knn(ids, d2)
     kw = dict(perplexity=hp["perplexity"], learning_rate=hp["learning_rate"], num_neighbors=K,
               early_exaggeration=hp["early_exaggeration"], perplexity_search_epsilon=1e-3)
 
-    def timed(n_iter):
-        t0 = time.time()
-        Y = ref.fit_transform(X, Y0, iterations=n_iter, **kw)
-        return time.time() - t0, Y
+    def loop_seconds(n_iter):
+        Y, tm = ref.fit_transform_timed(X, Y0, iterations=n_iter, **kw)
+        return tm["loop_s"], tm, Y
 
-    timed(max(args.warmup, 3))                      # context, plans, first-use costs
+    loop_seconds(max(args.warmup, 3))                      # context, plans, first-use costs
+    pairs = []
     with ClockSampler(0) as clk:
-        t_a, _ = timed(args.warmup)
-        t_b, Y = timed(args.warmup + args.steps)
-    loop = max(t_b - t_a, 1e-9)
+        for _ in range(5):
+            t_a, _, _ = loop_seconds(args.warmup)
+            t_b, tm, Y = loop_seconds(args.warmup + args.steps)
+            pairs.append(max(t_b - t_a, 1e-9))
+    loop = float(np.median(pairs))
     value = args.steps / loop
+    e2e = {"value": value, "unit": "iterations/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+           "note": "same as value: the full-length fit was skipped (--no-e2e)"}
+    if not args.no_e2e:
+        t0 = time.time()
+        Yf = ref.fit_transform(X, Y0, iterations=args.e2e_iters, **kw)
+        T = time.time() - t0
+        e2e = {"value": args.e2e_iters / T, "unit": "iterations/s", "fit_transform_s": T, "iterations": args.e2e_iters,
+               "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+               "note": "one fit of the same length as this engine's e2e, host X -> host Y, wall clock; EXCLUDES the "
+                       "neighbour search (injected), which this engine's e2e includes",
+               "finite": bool(np.isfinite(Yf).all())}
     base.update({"value": value, "ms_per_step": loop / args.steps * 1e3, "clocks": clk.summary(),
+                 "iterations_per_s_pairs": [args.steps / p for p in pairs],
+                 "reference_timers_last_run": {k: v for k, v in tm.items()},
                  "cpu_baseline": {"value": value, "unit": "iterations/s", "cores": 1, "kind": "reference",
-                                  "sample": "reference CUDA kernels on the GPU driven by one host thread; "
-                                            "difference of two pymodule_tsne calls (%d and %d iterations), "
-                                            "neighbour list injected" % (args.warmup, args.warmup + args.steps)},
-                 "e2e": {"value": (args.warmup + args.steps) / t_b, "unit": "iterations/s", "fit_transform_s": t_b,
-                         "iterations": args.warmup + args.steps, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-                         "note": "excludes the neighbour search (injected)"},
-                 "finite": bool(np.isfinite(Y).all())})
+                                  "sample": "reference CUDA kernels on the GPU driven by one host thread; median of 5 "
+                                            "differences of the reference's own loop timers between runs of %d and %d "
+                                            "iterations, neighbour list injected" % (args.warmup, args.warmup + args.steps)},
+                 "e2e": e2e, "finite": bool(np.isfinite(Y).all())})
     return base
 
 

@@ -117,9 +117,10 @@ int b200tsne_knn_last_stats(int *tensor_core, int *rows_recomputed, float *filte
  * library, so N * D must not exceed b200tsne_knn_noalloc_max_elements() (4 Mi floats = 16 MiB, resident
  * on every GPU that loads the library); larger inputs are rejected with B200TSNE_ERR_UNSUPPORTED.
  * The work is queued on cuda_stream (a cudaStream_t, NULL = default stream) and the call returns without
- * waiting.  The first call on a device looks up the array's device address; make that call before any
- * stream capture.  All calls share the one array, which keeps the previous call's contents (every element
- * the search reads is rewritten first): two calls whose GPU work overlaps, on different streams or from
+ * waiting, on the device that is current (cuda_stream must belong to it).  The first call on a device looks up
+ * the array's device address and sets kernel attributes, which may load the library's device code: make that
+ * call once at start-up, before any stream capture.  All calls share the one array, which keeps the previous
+ * call's contents (every element the search reads is rewritten first): two calls whose GPU work overlaps, on different streams or from
  * different threads, race on it.  Results equal b200tsne_knn's (SIMT search; whole database, all queries). */
 int b200tsne_knn_noalloc(const float *X_device, int64_t N, int D, int K, int32_t *ids_device, float *d2_device,
                          void *cuda_stream);
@@ -142,6 +143,16 @@ int b200tsne_symmetrize(const float *p, const int32_t *ids, int64_t N, int K, fl
  * Replaces: tsnecuda::ComputeAttractiveForcesV3 (src/kernels/attr_forces.cu:186-240). */
 int b200tsne_attractive(const float *P, const int32_t *ids, const float *Y, int64_t N, int K,
                         int64_t row_lo, int64_t row_hi, float *F, int device);
+
+/* The same force from the column-blocked copy of P that the gradient loop uses when the graph suits it: the
+ * points are ordered by Voronoi cell (from X [N][D] when given, else the natural order), every stored entry
+ * moves into the stream of the tile (<= 28,672 points) that holds its column, and the kernel gathers the
+ * neighbour coordinates from shared memory.  entries_per_group (may be NULL) receives the sampled average
+ * number of entries a row has per tile; the copy is not built (B200TSNE_ERR_UNSUPPORTED) when that is below 2.5
+ * unless the environment says B200TSNE_ATTRACTIVE=blocked.  Same arithmetic per entry as b200tsne_attractive,
+ * other summation order.  Replaces: tsnecuda::ComputeAttractiveForcesV3 (src/kernels/attr_forces.cu:186-240). */
+int b200tsne_attractive_blocked(const float *P, const int32_t *ids, const float *Y, int64_t N, int K, int64_t row_lo,
+                                int64_t row_hi, const float *X, int D, float *F, float *entries_per_group, int device);
 
 /* One FIt-SNE repulsive evaluation on a fixed Y: min/max, charges, spread, FFT convolution with
  * the squared-Cauchy kernel, gather, Z.  Frep: 2N floats SoA; Z = sum_i Z_i - N.
@@ -179,6 +190,9 @@ int b200tsne_session_set_embedding(b200tsne_session *s, const float *Y, int rese
 int b200tsne_session_get_embedding(b200tsne_session *s, float *Y);
 /* Download the owned rows of P / ids. */
 int b200tsne_session_get_affinities(b200tsne_session *s, float *P_rows, int32_t *ids_rows);
+/* Which attractive kernel the session's loop runs: 1 = column-blocked copy of P (built with the affinities),
+ * 0 = row-major P / ids.  entries_per_group (may be NULL): see b200tsne_attractive_blocked. */
+int b200tsne_session_attractive_mode(b200tsne_session *s, float *entries_per_group);
 /* Hyper-parameters of the loop (Options::learning_rate, early_exaggeration, force_magnify_iters,
  * pre/post momentum; src/include/options.h:67-77). */
 int b200tsne_session_set_schedule(b200tsne_session *s, float learning_rate, float early_exaggeration,
@@ -214,6 +228,22 @@ void b200tsne_comm_release_all(void);
  * could map all others and the environment does not say B200TSNE_EXCHANGE=nccl (set alike on all
  * ranks).  With mode 2, destroying the session is collective: all ranks must call it. */
 int b200tsne_session_exchange_mode(b200tsne_session *s);
+/* Limit of one meeting of the ranks in exchange mode 2 (default 2000 ms, or B200TSNE_PEER_TIMEOUT_MS when the
+ * exchange was created).  A rank that waits longer gives up: it tells every rank (an abort word in each
+ * rank's exchange block), all later meetings of that exchange return at once, and b200tsne_session_run
+ * returns B200TSNE_ERR_COMM on every rank that met it.  After that status the embedding is not meaningful;
+ * destroy the sessions and call b200tsne_comm_release_all on all ranks before starting over.  No counterpart
+ * in the reference (single GPU). */
+int b200tsne_session_set_peer_timeout_ms(b200tsne_session *s, int timeout_ms);
+
+/* Self-test of the two bounded device-side waits of this library, without a peer and without faulting or
+ * hanging anything: (1) a meeting of two ranks whose second rank is local memory that nothing writes, (2) a
+ * shared-memory barrier of the kNN pipeline that expects an arrival that never comes.  Each must give up after
+ * timeout_ms (1..2000) and leave the device usable.  *_status receive the status the wait produced
+ * (B200TSNE_ERR_COMM = gave up as designed, 0 = wrongly got through), *_ms the device time spent waiting.
+ * Returns 0 when both ran.  No counterpart in the reference. */
+int b200tsne_selftest_bounded_waits(int device, int timeout_ms, int *peer_status, float *peer_ms, int *barrier_status,
+                                    float *barrier_ms);
 
 /* Device memory the library has freed stays in the device's default memory pool so that the next call
  * gets it back without going to the driver (no reference counterpart: the reference allocates with

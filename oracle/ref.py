@@ -28,6 +28,7 @@ def lib():
         L.ref_repulsive.argtypes = [_fp, C.c_int, _fp, _fp, _fp, _fp, _fp]
         L.ref_apply_forces.argtypes = [_fp, _fp, _fp, _fp, _fp, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int]
         L.ref_set_knn.argtypes = [C.POINTER(C.c_int64), _fp, C.c_longlong, C.c_int]
+        L.ref_run_seeded.argtypes = [_fp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, _fp]
         _lib = L
     return _lib
 
@@ -102,6 +103,44 @@ def clear_knn():
     lib().ref_set_knn(None, None, 0, 0)
 
 
+def run_seeded(X, init_type, seed, iterations=0, num_neighbors=30, perplexity=10.0):
+    """tsnecuda::RunTsne of the reference with Options::random_seed = seed; init_type 0 UNIFORM, 1 GAUSSIAN.
+    Returns Y (2,N) SoA; with iterations = 0 that is the initial embedding the reference draws."""
+    X = np.ascontiguousarray(X, np.float32)
+    N, D = X.shape
+    Y = np.zeros((2, N), np.float32)
+    lib().ref_run_seeded(_f(X), N, D, init_type, seed, iterations, num_neighbors, perplexity, _f(Y))
+    return Y
+
+
+LOOP_TIMERS = ("_time_other", "_time_compute_charges", "_time_precompute_2d", "_time_nbodyfft", "_time_norm",
+               "_time_attr", "_time_apply_forces")
+
+
+def fit_transform_timed(X, y0=None, **kw):
+    """fit_transform with verbosity 1, returning (Y, timers): the reference's own `_time_*: <s>s` lines
+    (src/fit_tsne.cu:586-601) parsed into a dict.  timers["loop_s"] is the sum of the seven timers the
+    reference accumulates inside its gradient loop (src/fit_tsne.cu:402-544); they are host clocks around
+    phases that each end in a host synchronisation or follow one, so their sum is the loop's wall time.
+    print_interval is pushed out of reach so that verbosity adds one norm computation, at step 0."""
+    import re
+    import tempfile
+    kw = dict(kw, verbosity=1, print_interval=1 << 30)
+    with tempfile.TemporaryFile(mode="w+b") as tmp:
+        saved = os.dup(1)
+        os.dup2(tmp.fileno(), 1)
+        try:
+            Y = fit_transform(X, y0, **kw)
+        finally:
+            os.dup2(saved, 1)
+            os.close(saved)
+        tmp.seek(0)
+        text = tmp.read().decode(errors="replace")
+    timers = {m.group(1): float(m.group(2)) for m in re.finditer(r"^(_time_\w+|total_time): ([0-9.eE+-]+)s\s*$", text, re.M)}
+    timers["loop_s"] = sum(timers.get(k, 0.0) for k in LOOP_TIMERS)
+    return Y, timers
+
+
 def fit_transform(X, y0=None, **kw):
     """The reference's pymodule_tsne through the reference's argument order (src/ext/pymodule_ext.cu:6-40).
     Returns Y as (2,N) SoA."""
@@ -120,5 +159,5 @@ def fit_transform(X, y0=None, **kw):
                     g("early_exaggeration", 12.0), 5.0, g("num_neighbors", 32), g("iterations", 1000), 1000,
                     g("force_magnify_iters", 250), g("perplexity_search_epsilon", 1e-3), g("pre_momentum", 0.5),
                     g("post_momentum", 0.8), 0.5, 0.0025, 0.0, 3 if y0 is not None else 1, _f(pre), False, b"", 1,
-                    False, b"", 10000, g("verbosity", 0), 10, 0, 0, 0, 1)
+                    False, b"", 10000, g("verbosity", 0), g("print_interval", 10), 0, 0, 0, 1)
     return res

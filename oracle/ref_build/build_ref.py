@@ -18,7 +18,17 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.normpath(os.path.join(HERE, "..", "_ref"))
 LIB = os.path.join(OUT, "libtsnecuda_ref.so")
-DEFAULT_REF = os.environ.get("TSNE_REFERENCE_ROOT", "/root/reference")
+
+
+def find_reference_root():
+    """Where the reference tree lies: TSNE_REFERENCE_ROOT, else a directory named `reference` beside this
+    repository.  Nothing else is searched."""
+    env = os.environ.get("TSNE_REFERENCE_ROOT")
+    if env:
+        return env
+    repo = os.path.normpath(os.path.join(HERE, "..", ".."))
+    return os.path.join(os.path.dirname(repo), "reference")
+
 
 FAISS_HEADERS = ["IndexFlat.h", "IndexIVFFlat.h", "IndexIVFPQ.h", "gpu/GpuIndexFlat.h", "gpu/GpuIndexIVFFlat.h",
                  "gpu/GpuIndexIVFPQ.h", "gpu/StandardGpuResources.h", "gpu/GpuCloner.h"]
@@ -30,7 +40,7 @@ namespace faiss { enum MetricType { METRIC_INNER_PRODUCT = 0, METRIC_L2 = 1, MET
 
 
 def build(force=False, reference_root=None):
-    ref = reference_root or DEFAULT_REF
+    ref = reference_root or find_reference_root()
     src = os.path.join(ref, "src")
     if not os.path.isdir(src):
         return LIB if os.path.exists(LIB) else None

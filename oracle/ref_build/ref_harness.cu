@@ -160,3 +160,21 @@ extern "C" void ref_apply_forces(float *Y, float *attr, float *rep, float *gains
     thrust::copy(g.begin(), g.end(), gains);
     thrust::copy(o.begin(), o.end(), old_forces);
 }
+
+// The reference's whole entry point with a caller-chosen seed (Options::random_seed is a public field that
+// its C symbol never sets: src/include/options.h:104, src/ext/pymodule_ext.cu).  With iterations = 0 the
+// returned embedding is the initial one (src/fit_tsne.cu:181-235 draw order, :610-613 copy-out).
+extern "C" void ref_run_seeded(float *points, int N, int D, int init_type, int seed, int iterations, int num_neighbors,
+                               float perplexity, float *Y_out)
+{
+    tsnecuda::GpuOptions gpu_opt(0);
+    tsnecuda::Options opt(Y_out, points, N, D);
+    opt.random_seed = seed;
+    opt.iterations = iterations;
+    opt.num_neighbors = num_neighbors;
+    opt.perplexity = perplexity;
+    opt.verbosity = 0;
+    opt.initialization = static_cast<tsnecuda::TSNE_INIT>(init_type);
+    opt.return_style = tsnecuda::RETURN_STYLE::ONCE;
+    tsnecuda::RunTsne(opt, gpu_opt);
+}

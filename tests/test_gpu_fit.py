@@ -164,6 +164,23 @@ def test_fit_vs_live_reference(engine, oracle_cpu):
     assert abs(n_m - n_r) < 0.005 + 0.01, (n_m, n_r)
 
 
+def test_library_drawn_initial_embedding_equals_the_reference(engine):
+    """Options::random_seed fixed, zero iterations: the returned embedding is the initial one.  The reference
+    seeds std::default_random_engine, burns 2N normal draws and then draws 2N values (normal * 1e-4, or
+    uniform in [-5, 5)): src/fit_tsne.cu:181-204, src/util/random_utils.cu:17-34."""
+    from oracle import ref
+    if not ref.available():
+        pytest.skip("oracle/_ref/libtsnecuda_ref.so was not built (needs the reference tree)")
+    X = mixture(700, 12, 4)
+    for init_type in (1, 0):          # GAUSSIAN, UNIFORM
+        for seed in (0, 12345):
+            Yr = ref.run_seeded(X, init_type, seed, iterations=0, num_neighbors=30, perplexity=10.0)
+            Ym, _ = engine.fit(X, iterations=0, num_neighbors=30, perplexity=10.0, initialization_type=init_type,
+                               random_seed=seed)
+            assert np.array_equal(Ym, Yr), (init_type, seed)
+            assert Yr.std() > 0
+
+
 def test_snapshots_dump_and_errors(engine, tmp_path, capfd):
     from tsne_cuda_b200 import TSNE
     X = mixture(400, 10, 2)

@@ -37,7 +37,7 @@ class TSNE(object):
                  viz_server="tcp://localhost:5556", dump_points=False, dump_file="dump.txt", dump_interval=1,
                  print_interval=10, device=0, magnitude_factor=5):
         if n_components != 2:
-            raise ValueError("The current barnes-hut implementation does not support projection into dimensions other than 2 for now.")
+            raise NotImplementedError("Only projection into 2 dimensions is supported.")
         self.n_components = int(n_components)
         self.perplexity = float(perplexity)
         self.early_exaggeration = float(early_exaggeration)
@@ -50,9 +50,9 @@ class TSNE(object):
         elif metric == "innerproduct":
             self.metric = 0
         else:
-            raise ValueError("Non-Euclidean metrics are not currently supported. Please use metric='euclidean' for now.")
+            raise NotImplementedError("Only the 'euclidean' ('L2') and 'innerproduct' metrics are supported.")
         if init not in ("random",):
-            raise ValueError("Non-Random initialization is not currently supported. Please use init='random' for now.")
+            raise NotImplementedError("Only init='random' is supported (pass an initial embedding as fit_transform's y).")
         self.init = init
         self.verbose = int(verbose)
         self.device_id = int(device)

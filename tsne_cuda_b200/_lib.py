@@ -51,6 +51,8 @@ SIGNATURES = {
     "b200tsne_perplexity": (C.c_int, [_fp, _i64, C.c_int, C.c_float, C.c_float, C.c_float, _fp, _fp, _fp, C.c_int]),
     "b200tsne_symmetrize": (C.c_int, [_fp, _ip, _i64, C.c_int, _fp, C.c_int]),
     "b200tsne_attractive": (C.c_int, [_fp, _ip, _fp, _i64, C.c_int, _i64, _i64, _fp, C.c_int]),
+    "b200tsne_attractive_blocked": (C.c_int, [_fp, _ip, _fp, _i64, C.c_int, _i64, _i64, _fp, C.c_int, _fp, _fp, C.c_int]),
+    "b200tsne_session_attractive_mode": (C.c_int, [C.c_void_p, _fp]),
     "b200tsne_repulsive": (C.c_int, [_fp, _i64, _fp, _fp, _fp, _fp, C.c_int]),
     "b200tsne_apply_forces": (C.c_int, [_fp, _fp, _fp, _fp, _fp, C.c_float, C.c_float, C.c_float, C.c_float, _i64, C.c_int]),
     "b200tsne_session_create": (C.c_int, [C.POINTER(C.c_void_p), _i64, C.c_int, _i64, _i64, C.c_int]),
@@ -72,6 +74,8 @@ SIGNATURES = {
     "b200tsne_comm_release_all": (None, []),
     "b200tsne_session_exchange_mode": (C.c_int, [C.c_void_p]),
     "b200tsne_release_cached_memory": (C.c_int, [C.c_int]),
+    "b200tsne_session_set_peer_timeout_ms": (C.c_int, [C.c_void_p, C.c_int]),
+    "b200tsne_selftest_bounded_waits": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int), _fp, C.POINTER(C.c_int), _fp]),
 }
 for _name, (_res, _args) in SIGNATURES.items():
     _fn = getattr(lib, _name)
@@ -149,6 +153,23 @@ def attractive(P, ids, Y, row_lo=0, row_hi=None, device=0):
     F = np.empty((2, N), np.float32)
     check(lib.b200tsne_attractive(_f(P), _i(ids), _f(Y), N, K, row_lo, row_hi, _f(F), device))
     return F
+
+
+def attractive_blocked(P, ids, Y, X=None, row_lo=0, row_hi=None, device=0):
+    """The attractive force through the column-blocked copy of P. Returns (F (2,N), entries per row and tile)."""
+    P = _c(P, np.float32)
+    ids = _c(ids, np.int32)
+    Y = _c(Y, np.float32)
+    N, K = P.shape
+    row_hi = N if row_hi is None else row_hi
+    F = np.zeros((2, N), np.float32)
+    epg = C.c_float()
+    D = 0
+    if X is not None:
+        X = _c(X, np.float32)
+        D = X.shape[1]
+    check(lib.b200tsne_attractive_blocked(_f(P), _i(ids), _f(Y), N, K, row_lo, row_hi, _f(X), D, _f(F), C.byref(epg), device))
+    return F, epg.value
 
 
 def repulsive(Y, want_grids=False, device=0):
@@ -278,9 +299,27 @@ class Session(object):
         """0 single GPU, 1 NCCL collectives, 2 peer memory (see include/tsnecuda_b200.h)."""
         return lib.b200tsne_session_exchange_mode(self._h)
 
+    def attractive_mode(self):
+        """(1 if the loop uses the column-blocked copy of P else 0, sampled entries per row and tile)."""
+        epg = C.c_float()
+        m = lib.b200tsne_session_attractive_mode(self._h, C.byref(epg))
+        return m, epg.value
+
+    def set_peer_timeout_ms(self, ms):
+        """Limit of one meeting of the ranks (peer-memory exchange only)."""
+        check(lib.b200tsne_session_set_peer_timeout_ms(self._h, int(ms)))
+
     def attach_comm(self, unique_id, rank, world_size):
         buf = C.create_string_buffer(bytes(unique_id), 128)
         check(lib.b200tsne_session_attach_comm(self._h, buf, rank, world_size))
+
+
+def selftest_bounded_waits(timeout_ms=20, device=0):
+    """Makes the two bounded device-side waits run out on purpose (nothing faults or hangs); returns
+    {"peer": (status, ms), "barrier": (status, ms)} where status -5 means the wait gave up as designed."""
+    ps, bs, pm, bm = C.c_int(), C.c_int(), C.c_float(), C.c_float()
+    check(lib.b200tsne_selftest_bounded_waits(device, int(timeout_ms), C.byref(ps), C.byref(pm), C.byref(bs), C.byref(bm)))
+    return {"peer": (ps.value, pm.value), "barrier": (bs.value, bm.value)}
 
 
 def comm_unique_id():

@@ -1,0 +1,831 @@
+// Attractive force from a column-blocked copy of P, with the neighbour coordinates read from shared memory.
+//
+// The row-major kernel (attractive.cu) fetches one neighbour coordinate pair per stored entry with a fully
+// divergent 8-byte global load; the L1 serves about one such load per clock and SM, which makes that kernel
+// three times slower than the HBM stream of P and ids it has to read.  Here the gathers leave the L1 path:
+//
+//   * The points are renumbered once (order_points_by_cell: Voronoi cells around sample points, cells chained
+//     so that similar cells are adjacent), and the renumbered embedding is cut into tiles of at most 28,672
+//     points = 224 KB of float2, which one block keeps in shared memory.
+//   * At set-up every stored entry (row i, column j, value p) is moved into the stream of the tile that
+//     holds j, ordered by row.  The entries one row has in one tile form a group; a group is padded to a
+//     multiple of four entries so that a lane of a warp (four consecutive entries: one 16-byte load of
+//     values, one 8-byte load of 16-bit columns) never straddles two rows.  6 bytes per entry instead of 8.
+//   * Rows are not stored: bit 15 of a lane's first column says "this lane starts the next row", and a
+//     lane whose first column is 0xffff is a marker that carries an absolute row number (needed where a
+//     row has no entry in the tile); each chunk of 128 entries knows the row it starts in.  A warp finds
+//     its 32 row numbers with one ballot and a population count.
+//   * A block owns a contiguous 1/gridDim of the stream, loads the tile(s) it crosses, and its warps walk
+//     chunks: gather from shared memory, evaluate p / (1 + d^2) * (y_i - y_j), reduce the lanes of a row
+//     with shuffles, and add the row's partial force with one 8-byte reduction per (row, tile).
+//   * The loop is software-pipelined in registers (stream loads two chunks ahead, the row's own coordinate
+//     one chunk ahead): with 32 warps per SM and one block per SM nothing else hides the latency.
+//
+// Arithmetic per entry is that of the reference's ComputePijxQijKernelV3 (src/kernels/attr_forces.cu:129-184);
+// only the order of the additions differs (and varies from run to run in the last bits, as the sums of
+// a row's tiles meet in floating-point reductions).
+//
+// The blocked copy pays off when a row's neighbours fall into few tiles.  The builder measures that on a
+// sample of rows and declines (the caller keeps the row-major kernel) when a group would hold fewer than
+// kMinEntriesPerGroup entries on average, or when there are more than 1,024 tiles.
+#include <limits.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <string>
+
+#include "session.h"
+
+namespace b200 {
+
+namespace {
+
+constexpr int kTileMax = 28672;        // points per tile: 224 KB of float2 (227 KB is the block limit)
+constexpr int kChunk = 128;            // entries per warp step (4 per lane)
+constexpr int kMaxTiles = 1024;        // one bit per tile in a warp-wide bitmap
+constexpr int kBlockedThreads = 1024;
+constexpr float kMinEntriesPerGroup = 2.5f;
+constexpr int kCells = 64;
+
+// ------------------------------------------------------------------------------------------------
+// ordering of the points: nearest of kCells sample points, cells chained greedily by distance
+// ------------------------------------------------------------------------------------------------
+constexpr int kDimChunk = 32;
+constexpr int kAssignThreads = 128;
+
+// centre c = row of X picked from the c-th of `cells` equal stretches at a hashed offset (an even spacing
+// would alias with a periodic ordering of the data)
+__device__ __forceinline__ long long centre_row(int c, int cells, long long N)
+{
+    const long long stretch = N / cells;
+    const unsigned long long h = ((unsigned long long)(c + 1) * 0x9E3779B97F4A7C15ull) >> 20;
+    return (long long)c * stretch + (long long)(h % (unsigned long long)stretch);
+}
+
+// cell[i] = nearest centre (ties: lower index).  A block takes 128 points; coordinates go through shared
+// memory in chunks of 32 dimensions, every thread keeps its 64 partial distances in registers.
+__global__ void __launch_bounds__(kAssignThreads)
+cell_assign_kernel(const float *__restrict__ X, long long N, int D, int cells, unsigned char *__restrict__ cell)
+{
+    __shared__ float s_x[kAssignThreads][kDimChunk + 1];
+    __shared__ float s_c[kCells][kDimChunk];
+    const long long i0 = (long long)blockIdx.x * kAssignThreads;
+    float acc[kCells];
+#pragma unroll
+    for (int c = 0; c < kCells; c++) acc[c] = 0.0f;
+    for (int d0 = 0; d0 < D; d0 += kDimChunk) {
+        const int nd = min(kDimChunk, D - d0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < kAssignThreads * kDimChunk; idx += kAssignThreads) {
+            const int r = idx / kDimChunk, d = idx % kDimChunk;
+            const long long i = i0 + r;
+            s_x[r][d] = (i < N && d < nd) ? X[i * D + d0 + d] : 0.0f;
+        }
+        for (int idx = threadIdx.x; idx < kCells * kDimChunk; idx += kAssignThreads) {
+            const int c = idx / kDimChunk, d = idx % kDimChunk;
+            s_c[c][d] = (c < cells && d < nd) ? X[centre_row(c, cells, N) * D + d0 + d] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int d = 0; d < kDimChunk; d++) {
+            const float x = s_x[threadIdx.x][d];
+#pragma unroll
+            for (int c = 0; c < kCells; c++) {
+                const float t = x - s_c[c][d];
+                acc[c] = fmaf(t, t, acc[c]);
+            }
+        }
+    }
+    const long long i = i0 + threadIdx.x;
+    if (i >= N) return;
+    float best = INFINITY;
+    int bc = 0;
+#pragma unroll
+    for (int c = 0; c < kCells; c++)
+        if (c < cells && acc[c] < best) { best = acc[c]; bc = c; }
+    cell[i] = (unsigned char)bc;
+}
+
+// rank[c] = position of cell c in a greedy nearest-neighbour chain through the centres (start: cell 0), so
+// that cells of one cluster end up next to each other.  One block.
+__global__ void __launch_bounds__(kCells)
+cell_chain_kernel(const float *__restrict__ X, long long N, int D, int cells, int *__restrict__ rank)
+{
+    __shared__ float s_d[kCells][kCells + 1];
+    const int a = threadIdx.x;
+    if (a < cells) {
+        const float *xa = X + centre_row(a, cells, N) * D;
+        for (int b = 0; b < cells; b++) {
+            const float *xb = X + centre_row(b, cells, N) * D;
+            float acc = 0.0f;
+            for (int d = 0; d < D; d++) {
+                const float t = xa[d] - xb[d];
+                acc = fmaf(t, t, acc);
+            }
+            s_d[a][b] = acc;
+        }
+    }
+    __syncthreads();
+    if (a != 0) return;
+    bool used[kCells];
+    for (int c = 0; c < kCells; c++) used[c] = false;
+    int cur = 0;
+    used[0] = true;
+    rank[0] = 0;
+    for (int k = 1; k < cells; k++) {
+        int best = -1;
+        float bd = INFINITY;
+        for (int c = 0; c < cells; c++)
+            if (!used[c] && (best < 0 || s_d[cur][c] < bd)) { bd = s_d[cur][c]; best = c; }
+        used[best] = true;
+        rank[best] = k;
+        cur = best;
+    }
+}
+
+// Stable counting sort of the points by rank[cell]: a block takes kSortPerBlock consecutive points, each of
+// its warps a contiguous share of them.
+constexpr int kSortWarps = 8;
+constexpr int kSortPerWarp = 512;
+constexpr int kSortPerBlock = kSortWarps * kSortPerWarp;
+
+__global__ void __launch_bounds__(kSortWarps * 32)
+cell_hist_kernel(const unsigned char *__restrict__ cell, const int *__restrict__ rank, long long N, int *__restrict__ hist /* [kCells][nblocks] */)
+{
+    __shared__ int s_h[kCells];
+    for (int c = threadIdx.x; c < kCells; c += blockDim.x) s_h[c] = 0;
+    __syncthreads();
+    const long long lo = (long long)blockIdx.x * kSortPerBlock;
+    for (int k = threadIdx.x; k < kSortPerBlock; k += blockDim.x)
+        if (lo + k < N) atomicAdd(&s_h[rank[cell[lo + k]]], 1);
+    __syncthreads();
+    for (int c = threadIdx.x; c < kCells; c += blockDim.x) hist[(size_t)c * gridDim.x + blockIdx.x] = s_h[c];
+}
+
+// exclusive scan of n ints in place; one block (the tables it serves are small)
+__global__ void __launch_bounds__(1024)
+scan_inplace_kernel(int *__restrict__ hist, long long n)
+{
+    __shared__ int s_w[32];
+    __shared__ int s_carry;
+    if (threadIdx.x == 0) s_carry = 0;
+    __syncthreads();
+    for (long long base = 0; base < n; base += 1024) {
+        const long long i = base + threadIdx.x;
+        const int v = (i < n) ? hist[i] : 0;
+        int incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, d);
+            if ((threadIdx.x & 31) >= d) incl += t;
+        }
+        if ((threadIdx.x & 31) == 31) s_w[threadIdx.x >> 5] = incl;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            int w = s_w[threadIdx.x];
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, w, d);
+                if (threadIdx.x >= d) w += t;
+            }
+            s_w[threadIdx.x] = w;
+        }
+        __syncthreads();
+        const int carry = s_carry;
+        const int wbase = (threadIdx.x >> 5) ? s_w[(threadIdx.x >> 5) - 1] : 0;
+        if (i < n) hist[i] = carry + wbase + incl - v;
+        __syncthreads();
+        if (threadIdx.x == 1023) s_carry = carry + wbase + incl;
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(kSortWarps * 32)
+cell_scatter_kernel(const unsigned char *__restrict__ cell, const int *__restrict__ rank, long long N, const int *__restrict__ offs,
+                    int32_t *__restrict__ perm)
+{
+    __shared__ int s_cnt[kSortWarps][kCells], s_base[kSortWarps][kCells];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    for (int c = lane; c < kCells; c += 32) s_cnt[w][c] = 0;
+    __syncwarp();
+    const long long lo = (long long)blockIdx.x * kSortPerBlock + (long long)w * kSortPerWarp;
+    for (int k = lane; k < kSortPerWarp; k += 32)
+        if (lo + k < N) atomicAdd(&s_cnt[w][rank[cell[lo + k]]], 1);
+    __syncthreads();
+    // first position of (block, warp, cell) = block offset + counts of the warps before this one
+    for (int c = lane; c < kCells; c += 32) {
+        int base = offs[(size_t)c * gridDim.x + blockIdx.x];
+        for (int v = 0; v < w; v++) base += s_cnt[v][c];
+        s_base[w][c] = base;
+    }
+    __syncwarp();
+    for (int k0 = 0; k0 < kSortPerWarp; k0 += 32) {
+        const long long i = lo + k0 + lane;
+        const bool in = i < N;
+        const int r = in ? rank[cell[i]] : -1 - lane;   // lanes out of range never match
+        const unsigned m = __match_any_sync(0xffffffffu, r);
+        const int before = __popc(m & ((1u << lane) - 1u));
+        int base = 0;
+        if (in) base = s_base[w][r];
+        __syncwarp();
+        if (in) {
+            perm[base + before] = (int32_t)i;
+            if (before == __popc(m) - 1) s_base[w][r] = base + __popc(m);
+        }
+        __syncwarp();
+    }
+}
+
+}  // namespace
+
+// perm[q] = the point at position q of the cell order.  X: [N][D] on the device.
+int order_points_by_cell(const float *X, int64_t N, int D, int32_t *perm, cudaStream_t st)
+{
+    if (N <= 0 || D <= 0) { set_error("order_points_by_cell: invalid sizes"); return -1; }
+    const int cells = (int)std::min<int64_t>(kCells, N);
+    const unsigned nblocks = (unsigned)((N + kSortPerBlock - 1) / kSortPerBlock);
+    DeviceArena tmp;
+    tmp.serve(st);
+    unsigned char *cell = nullptr;
+    int *rank = nullptr, *hist = nullptr;
+    B200_TRY(tmp.alloc((void **)&cell, (size_t)N));
+    B200_TRY(tmp.alloc((void **)&rank, sizeof(int) * kCells));
+    B200_TRY(tmp.alloc((void **)&hist, sizeof(int) * (size_t)kCells * nblocks));
+    B200_CUDA(cudaMemsetAsync(rank, 0, sizeof(int) * kCells, st));
+    cell_assign_kernel<<<(unsigned)((N + kAssignThreads - 1) / kAssignThreads), kAssignThreads, 0, st>>>(X, N, D, cells, cell);
+    cell_chain_kernel<<<1, kCells, 0, st>>>(X, N, D, cells, rank);
+    cell_hist_kernel<<<nblocks, kSortWarps * 32, 0, st>>>(cell, rank, N, hist);
+    scan_inplace_kernel<<<1, 1024, 0, st>>>(hist, (long long)kCells * nblocks);
+    cell_scatter_kernel<<<nblocks, kSortWarps * 32, 0, st>>>(cell, rank, N, hist, perm);
+    B200_CUDA(cudaGetLastError());
+    B200_CUDA(cudaStreamSynchronize(st));
+    return 0;
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// the blocked stream
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+struct BlockedStream {   // what the kernels need, by value
+    const float *ev;          // [E] values; a marker lane's first value holds the row number's bits
+    const uint16_t *ec;       // [E] column inside the tile | 0x8000 on a lane's first entry = "next row starts here"; 0xffff = marker
+    const int *chunk_row0;    // [C] row in force before the chunk's first lane
+    const int *tile_chunk0;   // [ntiles + 1] first chunk of every tile
+    int ntiles, T, C;
+};
+
+// inverse of a permutation
+__global__ void invert_perm_kernel(const int32_t *__restrict__ perm, long long N, int32_t *__restrict__ pos)
+{
+    const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (q < N) pos[perm ? perm[q] : q] = (int32_t)q;
+}
+__global__ void iota_kernel(int32_t *__restrict__ a, long long n)
+{
+    const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (q < n) a[q] = (int32_t)q;
+}
+
+// own rows in permuted order (multi-GPU: a rank owns rows [row_lo, row_hi) of the original numbering):
+// stable compaction of perm in three launches
+constexpr int kCompactPerBlock = 4096;
+__global__ void __launch_bounds__(1024)
+own_count_kernel(const int32_t *__restrict__ perm, long long N, long long row_lo, long long row_hi, int *__restrict__ bcount)
+{
+    const long long lo = (long long)blockIdx.x * kCompactPerBlock;
+    int c = 0;
+    for (int k = threadIdx.x; k < kCompactPerBlock; k += 1024) {
+        const long long q = lo + k;
+        if (q < N) { const int i = perm[q]; c += (i >= row_lo && i < row_hi); }
+    }
+    c = __reduce_add_sync(0xffffffffu, c);
+    __shared__ int s[32];
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int t = __reduce_add_sync(0xffffffffu, s[threadIdx.x]);
+        if (threadIdx.x == 0) bcount[blockIdx.x] = t;
+    }
+}
+// one warp per block walks the block's 4096 positions in order (small work; keeps the order without a block scan)
+__global__ void __launch_bounds__(32)
+own_scatter_kernel(const int32_t *__restrict__ perm, long long N, long long row_lo, long long row_hi, const int *__restrict__ boff,
+                   int32_t *__restrict__ own_perm, int32_t *__restrict__ own_pos)
+{
+    const int lane = threadIdx.x;
+    const long long lo = (long long)blockIdx.x * kCompactPerBlock;
+    int base = boff[blockIdx.x];
+    for (int k0 = 0; k0 < kCompactPerBlock; k0 += 32) {
+        const long long q = lo + k0 + lane;
+        const int i = (q < N) ? perm[q] : -1;
+        const bool own = i >= row_lo && i < row_hi;
+        const unsigned m = __ballot_sync(0xffffffffu, own);
+        if (own) {
+            const int lr = base + __popc(m & ((1u << lane) - 1u));
+            own_perm[lr] = i;
+            own_pos[i - row_lo] = lr;
+        }
+        base += __popc(m);
+    }
+}
+
+// ---- walking the rows of a range: per-warp scratch ----
+constexpr int kWalkWarps = 2;
+constexpr int kMaxK = 1024;
+struct WalkScratch {
+    long long run[kMaxTiles];      // count pass: entries this range adds to the tile; fill pass: next free entry of the tile
+    int rowcnt[kMaxTiles];         // entries of the current row per tile
+    unsigned slot[kMaxK];          // per slot of the current row: tile << 16 | rank inside (row, tile); 0xffffffff = unused slot
+    unsigned short col[kMaxK];     // per slot: column inside the tile
+    unsigned bitmap[2][32];        // tiles touched by the previous / the current row
+};
+
+struct WalkArgs {
+    const float *P_rows;           // [rows][K]
+    const int32_t *ids_rows;
+    const int32_t *pos;            // [N] point -> permuted position
+    const int32_t *own_perm;       // [rows] local permuted position -> point
+    long long N, row_lo, rows;
+    int K, T, ntiles, range_rows;
+    long long n_ranges;
+};
+
+// slot table, per-tile counts and the tile bitmap of one row
+__device__ __forceinline__ void analyse_row(const WalkArgs &a, long long lr, WalkScratch &s, unsigned *bitmap, int lane)
+{
+    const long long r = (long long)a.own_perm[lr] - a.row_lo;
+    for (int k0 = 0; k0 < a.K; k0 += 32) {
+        const int sl = k0 + lane;
+        int j = (sl < a.K) ? a.ids_rows[r * a.K + sl] : -1;
+        const bool valid = (unsigned long long)(long long)j < (unsigned long long)a.N && j >= 0;
+        int t = -1 - lane, c = 0;
+        if (valid) {
+            const int q = a.pos[j];
+            t = q / a.T;
+            c = q - t * a.T;
+        }
+        const unsigned m = __match_any_sync(0xffffffffu, t);
+        const int before = __popc(m & ((1u << lane) - 1u));
+        const int base = valid ? s.rowcnt[t] : 0;
+        __syncwarp();
+        if (valid) {
+            if (before == __popc(m) - 1) s.rowcnt[t] = base + __popc(m);
+            if (before == 0 && base == 0) atomicOr(&bitmap[t >> 5], 1u << (t & 31));
+        }
+        __syncwarp();
+        if (sl < a.K) {
+            s.slot[sl] = valid ? (((unsigned)t << 16) | (unsigned)(base + before)) : 0xffffffffu;
+            s.col[sl] = (unsigned short)c;
+        }
+    }
+    __syncwarp();
+}
+
+// FILL = false: add the row's groups to run[] (sizes) and count them.  FILL = true: write the row's entries.
+template <bool FILL>
+__device__ __forceinline__ void emit_row(const WalkArgs &a, long long lr, WalkScratch &s, const unsigned *prev, int lane,
+                                         float *__restrict__ ev, uint16_t *__restrict__ ec, int *__restrict__ chunk_row0,
+                                         unsigned long long &n_groups)
+{
+    const long long r = (long long)a.own_perm[lr] - a.row_lo;
+    if (FILL) {
+        for (int k0 = 0; k0 < a.K; k0 += 32) {
+            const int sl = k0 + lane;
+            const unsigned info = (sl < a.K) ? s.slot[sl] : 0xffffffffu;
+            if (info == 0xffffffffu) continue;
+            const int t = info >> 16, rank = info & 0xffffu;
+            const bool marker = !((prev[t >> 5] >> (t & 31)) & 1u);
+            const long long gs = s.run[t];
+            const long long off = gs + (marker ? 4 : 0) + rank;
+            ev[off] = a.P_rows[r * a.K + sl];
+            ec[off] = (uint16_t)(s.col[sl] | ((rank == 0 && !marker) ? 0x8000u : 0u));
+            if (rank == 0) {
+                if (marker) { ev[gs] = __int_as_float((int)lr); ec[gs] = 0xffffu; }
+                const int size = ((s.rowcnt[t] + 3) & ~3) + (marker ? 4 : 0);
+                for (long long m = (gs + kChunk - 1) / kChunk * kChunk; m < gs + size; m += kChunk)
+                    chunk_row0[m / kChunk] = (m == gs && !marker) ? (int)lr - 1 : (int)lr;
+            }
+        }
+        __syncwarp();
+    }
+    // group leaders close the row: advance the tile's cursor, clear the row's count
+    for (int k0 = 0; k0 < a.K; k0 += 32) {
+        const int sl = k0 + lane;
+        const unsigned info = (sl < a.K) ? s.slot[sl] : 0xffffffffu;
+        if (info == 0xffffffffu || (info & 0xffffu) != 0) continue;
+        const int t = info >> 16;
+        const bool marker = !((prev[t >> 5] >> (t & 31)) & 1u);
+        s.run[t] += ((s.rowcnt[t] + 3) & ~3) + (marker ? 4 : 0);
+        s.rowcnt[t] = 0;
+        n_groups++;
+    }
+    __syncwarp();
+}
+
+// A warp walks the rows of one range in order.  Count pass: range_size[t][range] = entries (padding and
+// markers included) the range puts into tile t.  Fill pass: starts from tile_start[t] + range_off[t][range].
+template <bool FILL>
+__global__ void __launch_bounds__(kWalkWarps * 32)
+walk_kernel(WalkArgs a, unsigned *__restrict__ range_size, const unsigned *__restrict__ range_off, const long long *__restrict__ tile_start,
+            float *__restrict__ ev, uint16_t *__restrict__ ec, int *__restrict__ chunk_row0, unsigned long long *__restrict__ totals)
+{
+    __shared__ WalkScratch scratch[kWalkWarps];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    WalkScratch &s = scratch[w];
+    const long long range = (long long)blockIdx.x * kWalkWarps + w;
+    if (range >= a.n_ranges) return;
+    for (int t = lane; t < a.ntiles; t += 32) {
+        s.rowcnt[t] = 0;
+        s.run[t] = FILL ? tile_start[t] + (long long)range_off[(size_t)t * a.n_ranges + range] : 0;
+    }
+    s.bitmap[0][lane] = 0u;
+    s.bitmap[1][lane] = 0u;
+    __syncwarp();
+    const long long lr0 = range * a.range_rows, lr1 = min(a.rows, lr0 + (long long)a.range_rows);
+    unsigned long long n_groups = 0;
+    int cur = 0;
+    if (lr0 > 0) {   // the tiles of the row before the range decide the first row's markers
+        analyse_row(a, lr0 - 1, s, s.bitmap[0], lane);
+        for (int k0 = 0; k0 < a.K; k0 += 32) {
+            const int sl = k0 + lane;
+            const unsigned info = (sl < a.K) ? s.slot[sl] : 0xffffffffu;
+            if (info != 0xffffffffu && (info & 0xffffu) == 0) s.rowcnt[info >> 16] = 0;
+        }
+        __syncwarp();
+        cur = 1;
+    }
+    for (long long lr = lr0; lr < lr1; lr++) {
+        s.bitmap[cur][lane] = 0u;
+        __syncwarp();
+        analyse_row(a, lr, s, s.bitmap[cur], lane);
+        emit_row<FILL>(a, lr, s, s.bitmap[cur ^ 1], lane, ev, ec, chunk_row0, n_groups);
+        cur ^= 1;
+    }
+    if (!FILL) {
+        for (int t = lane; t < a.ntiles; t += 32) range_size[(size_t)t * a.n_ranges + range] = (unsigned)s.run[t];
+        n_groups = __reduce_add_sync(0xffffffffu, (unsigned)n_groups);
+        if (lane == 0) atomicAdd(&totals[0], n_groups);
+    }
+}
+
+// distinct tiles and valid entries of a sample of rows: totals[1] += groups, totals[2] += entries
+__global__ void __launch_bounds__(kWalkWarps * 32)
+sample_kernel(WalkArgs a, long long n_samples, unsigned long long *__restrict__ totals)
+{
+    __shared__ WalkScratch scratch[kWalkWarps];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    WalkScratch &s = scratch[w];
+    const long long k = (long long)blockIdx.x * kWalkWarps + w;
+    if (k >= n_samples) return;
+    for (int t = lane; t < a.ntiles; t += 32) s.rowcnt[t] = 0;
+    s.bitmap[0][lane] = 0u;
+    __syncwarp();
+    const long long lr = k * (a.rows / n_samples);
+    analyse_row(a, lr, s, s.bitmap[0], lane);
+    unsigned groups = 0, entries = 0;
+    for (int k0 = 0; k0 < a.K; k0 += 32) {
+        const int sl = k0 + lane;
+        const unsigned info = (sl < a.K) ? s.slot[sl] : 0xffffffffu;
+        if (info == 0xffffffffu) continue;
+        entries++;
+        groups += (info & 0xffffu) == 0;
+    }
+    groups = __reduce_add_sync(0xffffffffu, groups);
+    entries = __reduce_add_sync(0xffffffffu, entries);
+    if (lane == 0) { atomicAdd(&totals[1], (unsigned long long)groups); atomicAdd(&totals[2], (unsigned long long)entries); }
+}
+
+// per tile: exclusive scan of the ranges' sizes (in place) and the tile's total; one block per tile
+__global__ void __launch_bounds__(1024)
+tile_scan_kernel(unsigned *__restrict__ range_size, long long n_ranges, unsigned long long *__restrict__ tile_total)
+{
+    __shared__ unsigned long long s_w[32];
+    __shared__ unsigned long long s_carry;
+    unsigned *row = range_size + (size_t)blockIdx.x * n_ranges;
+    if (threadIdx.x == 0) s_carry = 0;
+    __syncthreads();
+    for (long long base = 0; base < n_ranges; base += 1024) {
+        const long long i = base + threadIdx.x;
+        const unsigned long long v = (i < n_ranges) ? row[i] : 0;
+        unsigned long long incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const unsigned long long t = __shfl_up_sync(0xffffffffu, incl, d);
+            if ((threadIdx.x & 31) >= d) incl += t;
+        }
+        if ((threadIdx.x & 31) == 31) s_w[threadIdx.x >> 5] = incl;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            unsigned long long wv = s_w[threadIdx.x];
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const unsigned long long t = __shfl_up_sync(0xffffffffu, wv, d);
+                if (threadIdx.x >= d) wv += t;
+            }
+            s_w[threadIdx.x] = wv;
+        }
+        __syncthreads();
+        const unsigned long long carry = s_carry;
+        const unsigned long long wbase = (threadIdx.x >> 5) ? s_w[(threadIdx.x >> 5) - 1] : 0;
+        if (i < n_ranges) row[i] = (unsigned)(carry + wbase + incl - v);
+        __syncthreads();
+        if (threadIdx.x == 1023) s_carry = carry + wbase + incl;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) tile_total[blockIdx.x] = s_carry;
+}
+
+// tile t's entries start at a multiple of the chunk size; totals[3] = all entries, totals[4] = 1 if a tile overflows 32 bits
+__global__ void tile_layout_kernel(const unsigned long long *__restrict__ tile_total, int ntiles, long long *__restrict__ tile_start,
+                                   int *__restrict__ tile_chunk0, unsigned long long *__restrict__ totals)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    long long e = 0;
+    unsigned long long bad = 0;
+    for (int t = 0; t < ntiles; t++) {
+        tile_start[t] = e;
+        tile_chunk0[t] = (int)(e / kChunk);
+        if (tile_total[t] >= 0xffffffffull) bad = 1;
+        e += (long long)((tile_total[t] + kChunk - 1) / kChunk * kChunk);
+    }
+    tile_start[ntiles] = e;
+    tile_chunk0[ntiles] = (int)(e / kChunk);
+    totals[3] = (unsigned long long)e;
+    totals[4] = bad;
+}
+
+// ---- per iteration ----
+// Yp[q] = Y[perm[q]] for all points; Yown[lr] = Y[own_perm[lr]] and Fp[lr] = 0 for the owned rows
+__global__ void __launch_bounds__(256)
+permute_kernel(const float2 *__restrict__ Y2, const int32_t *__restrict__ perm, long long N, float2 *__restrict__ Yp,
+               const int32_t *__restrict__ own_perm, long long rows, float2 *__restrict__ Yown, float2 *__restrict__ Fp)
+{
+    const long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (q < N) Yp[q] = Y2[perm[q]];
+    if (q < rows) {
+        if (Yown != Yp) Yown[q] = Y2[own_perm[q]];
+        Fp[q] = make_float2(0.0f, 0.0f);
+    }
+}
+__global__ void __launch_bounds__(256)
+unpermute_kernel(const float2 *__restrict__ Fp, const int32_t *__restrict__ own_pos, long long row_lo, long long rows, float2 *__restrict__ F2)
+{
+    const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < rows) F2[row_lo + r] = Fp[own_pos[r]];
+}
+
+struct ChunkRegs {
+    float4 p;
+    uint2 c;
+    int row0;
+};
+__device__ __forceinline__ ChunkRegs load_chunk(const BlockedStream &b, int cc, int lane)
+{
+    ChunkRegs r;
+    r.p = __ldcs(reinterpret_cast<const float4 *>(b.ev) + (size_t)cc * 32 + lane);
+    r.c = __ldcs(reinterpret_cast<const uint2 *>(b.ec) + (size_t)cc * 32 + lane);
+    r.row0 = __ldg(b.chunk_row0 + cc);
+    return r;
+}
+
+__device__ __forceinline__ void add_entry(float2 yi, float2 yj, float p, float &ox, float &oy)
+{
+    const float dx = yi.x - yj.x, dy = yi.y - yj.y;
+    const float pq = __fdividef(p, 1.0f + dx * dx + dy * dy);
+    ox = fmaf(pq, dx, ox);
+    oy = fmaf(pq, dy, oy);
+}
+
+__device__ __forceinline__ void process_chunk(const ChunkRegs &R, const float2 *__restrict__ tile, const float2 *__restrict__ Yown,
+                                              float2 *__restrict__ Fp, int lane)
+{
+    const unsigned e0 = R.c.x & 0xffffu, e1 = R.c.x >> 16, e2 = R.c.y & 0xffffu, e3 = R.c.y >> 16;
+    const bool head = e0 >> 15;
+    const bool marker = e0 == 0xffffu;
+    const unsigned hm = __ballot_sync(0xffffffffu, head);
+    int r;
+    if (!__any_sync(0xffffffffu, marker)) {
+        r = R.row0 + __popc(hm & (0xffffffffu >> (31 - lane)));
+    } else {
+        // rows as a scan over (absolute row set by a marker, heads since)
+        int s = marker ? __float_as_int(R.p.x) : INT_MIN, n = (head && !marker) ? 1 : 0;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int sa = __shfl_up_sync(0xffffffffu, s, d), na = __shfl_up_sync(0xffffffffu, n, d);
+            if (lane >= d && s == INT_MIN) { s = sa; n += na; }
+        }
+        r = (s == INT_MIN ? R.row0 : s) + n;
+    }
+    const float2 yi = __ldg(Yown + r);
+    const float2 yj0 = tile[marker ? 0u : (e0 & 0x7fffu)], yj1 = tile[e1], yj2 = tile[e2], yj3 = tile[e3];
+    float ox = 0.0f, oy = 0.0f;
+    add_entry(yi, yj0, marker ? 0.0f : R.p.x, ox, oy);
+    add_entry(yi, yj1, R.p.y, ox, oy);
+    add_entry(yi, yj2, R.p.z, ox, oy);
+    add_entry(yi, yj3, R.p.w, ox, oy);
+    // lanes of one row are neighbours: a run starts at lane 0 and at every head
+    const unsigned starts = hm | 1u;
+    const unsigned above = (lane == 31) ? 0u : (starts & (0xffffffffu << (lane + 1)));
+    const int run_end = above ? (__ffs(above) - 2) : 31;
+    const bool is_start = (starts >> lane) & 1u;
+    const int maxlen = __reduce_max_sync(0xffffffffu, is_start ? run_end - lane : 0);
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        if (d > maxlen) break;
+        const float tx = __shfl_down_sync(0xffffffffu, ox, d), ty = __shfl_down_sync(0xffffffffu, oy, d);
+        if (lane + d <= run_end) { ox += tx; oy += ty; }
+    }
+    if (is_start) atomicAdd(Fp + r, make_float2(ox, oy));
+}
+
+__global__ void __launch_bounds__(kBlockedThreads, 1)
+attractive_blocked_kernel(BlockedStream b, const float2 *__restrict__ Yp, const float2 *__restrict__ Yown, long long N,
+                          float2 *__restrict__ Fp)
+{
+    extern __shared__ float2 tile[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int nwarps = kBlockedThreads / 32;
+    const int c_lo = (int)((long long)b.C * blockIdx.x / gridDim.x), c_hi = (int)((long long)b.C * (blockIdx.x + 1) / gridDim.x);
+    if (c_lo >= c_hi) return;
+    int t = 0;
+    {
+        int lo = 0, hi = b.ntiles;
+        while (hi - lo > 1) {
+            const int m = (lo + hi) >> 1;
+            if (b.tile_chunk0[m] <= c_lo) lo = m; else hi = m;
+        }
+        t = lo;
+    }
+    int c = c_lo, cc = c_lo + warp;
+    ChunkRegs next = load_chunk(b, min(cc, b.C - 1), lane);
+    while (c < c_hi) {
+        while (b.tile_chunk0[t + 1] <= c) t++;
+        const int c_end = min(c_hi, b.tile_chunk0[t + 1]);
+        const long long base = (long long)t * b.T;
+        const int cnt = (int)min((long long)b.T, N - base);
+        __syncthreads();   // every warp is done with the previous tile
+        {
+            const float4 *src = reinterpret_cast<const float4 *>(Yp + base);   // base is even: 16-byte aligned
+            float4 *dst = reinterpret_cast<float4 *>(tile);
+            const int n4 = cnt >> 1;
+            for (int i = threadIdx.x; i < n4; i += kBlockedThreads) dst[i] = __ldg(src + i);
+            if ((cnt & 1) && threadIdx.x == 0) tile[cnt - 1] = Yp[base + cnt - 1];
+        }
+        __syncthreads();
+        for (; cc < c_end; cc += nwarps) {
+            const ChunkRegs cur = next;
+            next = load_chunk(b, min(cc + nwarps, b.C - 1), lane);
+            process_chunk(cur, tile, Yown, Fp, lane);
+        }
+        c = c_end;
+    }
+}
+
+}  // namespace
+
+void BlockedAttractive::clear() { *this = BlockedAttractive(); }
+
+// Builds the blocked copy of the owned rows' fixed-width P.  perm (device, [N]; null = identity) is the order
+// of the points; persistent buffers come from `arena`.  On return b->ready says whether the copy was built;
+// it is not when the sampled rows average fewer than kMinEntriesPerGroup entries per (row, tile), when there
+// are too many tiles, or when K exceeds 1,024 - none of which is an error.
+int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const float *P_rows, const int32_t *ids_rows, int64_t N, int K,
+                             int64_t row_lo, int64_t row_hi, const int32_t *perm_in, cudaStream_t st)
+{
+    b->clear();
+    const int64_t rows = row_hi - row_lo;
+    if (rows <= 0 || N <= 0 || K <= 0) return 0;
+    const char *mode = getenv("B200TSNE_ATTRACTIVE");   // "rows": never build; "blocked": build whatever the sample says
+    if (mode && strcmp(mode, "rows") == 0) return 0;
+    const bool forced = mode && strcmp(mode, "blocked") == 0;
+    int ntiles = (int)((N + kTileMax - 1) / kTileMax);
+    if (ntiles > kMaxTiles || K > kMaxK) return 0;
+    int T = (int)(((N + ntiles - 1) / ntiles + 31) / 32 * 32);
+    ntiles = (int)((N + T - 1) / T);
+
+    DeviceArena tmp;
+    tmp.serve(st);
+    int32_t *perm = nullptr, *pos = nullptr, *own_perm = nullptr, *own_pos = nullptr;
+    B200_TRY(arena.alloc((void **)&perm, sizeof(int32_t) * N));
+    B200_TRY(tmp.alloc((void **)&pos, sizeof(int32_t) * N));
+    const unsigned gN = (unsigned)((N + 255) / 256);
+    if (perm_in) B200_CUDA(cudaMemcpyAsync(perm, perm_in, sizeof(int32_t) * N, cudaMemcpyDeviceToDevice, st));
+    else iota_kernel<<<gN, 256, 0, st>>>(perm, N);
+    invert_perm_kernel<<<gN, 256, 0, st>>>(perm, N, pos);
+    if (rows == N) {
+        own_perm = perm;
+        B200_TRY(arena.alloc((void **)&own_pos, sizeof(int32_t) * N));
+        B200_CUDA(cudaMemcpyAsync(own_pos, pos, sizeof(int32_t) * N, cudaMemcpyDeviceToDevice, st));
+    } else {
+        B200_TRY(arena.alloc((void **)&own_perm, sizeof(int32_t) * rows));
+        B200_TRY(arena.alloc((void **)&own_pos, sizeof(int32_t) * rows));
+        const unsigned nb = (unsigned)((N + kCompactPerBlock - 1) / kCompactPerBlock);
+        int *bcount = nullptr;
+        B200_TRY(tmp.alloc((void **)&bcount, sizeof(int) * nb));
+        own_count_kernel<<<nb, 1024, 0, st>>>(perm, N, row_lo, row_hi, bcount);
+        scan_inplace_kernel<<<1, 1024, 0, st>>>(bcount, nb);
+        own_scatter_kernel<<<nb, 32, 0, st>>>(perm, N, row_lo, row_hi, bcount, own_perm, own_pos);
+    }
+    B200_CUDA(cudaGetLastError());
+
+    WalkArgs a;
+    a.P_rows = P_rows; a.ids_rows = ids_rows; a.pos = pos; a.own_perm = own_perm;
+    a.N = N; a.row_lo = row_lo; a.rows = rows; a.K = K; a.T = T; a.ntiles = ntiles;
+    a.range_rows = 64;
+    while ((rows + a.range_rows - 1) / a.range_rows * ntiles > (1ll << 24)) a.range_rows *= 2;
+    a.n_ranges = (rows + a.range_rows - 1) / a.range_rows;
+
+    unsigned long long *totals = nullptr, h_tot[5] = {0, 0, 0, 0, 0};
+    B200_TRY(tmp.alloc((void **)&totals, sizeof(h_tot)));
+    B200_CUDA(cudaMemsetAsync(totals, 0, sizeof(h_tot), st));
+    const long long n_samples = std::min<long long>(rows, 4096);
+    sample_kernel<<<(unsigned)((n_samples + kWalkWarps - 1) / kWalkWarps), kWalkWarps * 32, 0, st>>>(a, n_samples, totals);
+    B200_CUDA(cudaGetLastError());
+    B200_CUDA(cudaMemcpyAsync(h_tot, totals, sizeof(h_tot), cudaMemcpyDeviceToHost, st));
+    B200_CUDA(cudaStreamSynchronize(st));
+    b->entries_per_group = h_tot[1] ? (float)((double)h_tot[2] / (double)h_tot[1]) : 0.0f;
+    if (h_tot[1] == 0 || (!forced && b->entries_per_group < kMinEntriesPerGroup)) return 0;
+
+    unsigned *range_size = nullptr;
+    unsigned long long *tile_total = nullptr;
+    long long *tile_start = nullptr;
+    int *tile_chunk0 = nullptr;
+    B200_TRY(tmp.alloc((void **)&range_size, sizeof(unsigned) * (size_t)ntiles * a.n_ranges));
+    B200_TRY(tmp.alloc((void **)&tile_total, sizeof(unsigned long long) * ntiles));
+    B200_TRY(tmp.alloc((void **)&tile_start, sizeof(long long) * (ntiles + 1)));
+    B200_TRY(arena.alloc((void **)&tile_chunk0, sizeof(int) * (ntiles + 1)));
+    const unsigned walk_blocks = (unsigned)((a.n_ranges + kWalkWarps - 1) / kWalkWarps);
+    walk_kernel<false><<<walk_blocks, kWalkWarps * 32, 0, st>>>(a, range_size, nullptr, nullptr, nullptr, nullptr, nullptr, totals);
+    tile_scan_kernel<<<ntiles, 1024, 0, st>>>(range_size, a.n_ranges, tile_total);
+    tile_layout_kernel<<<1, 1, 0, st>>>(tile_total, ntiles, tile_start, tile_chunk0, totals);
+    B200_CUDA(cudaGetLastError());
+    B200_CUDA(cudaMemcpyAsync(h_tot, totals, sizeof(h_tot), cudaMemcpyDeviceToHost, st));
+    B200_CUDA(cudaStreamSynchronize(st));
+    const long long E = (long long)h_tot[3];
+    if (E <= 0 || h_tot[4] || E / kChunk >= INT_MAX) return 0;
+
+    float *ev = nullptr;
+    uint16_t *ec = nullptr;
+    int *chunk_row0 = nullptr;
+    float2 *Yp = nullptr, *Yown = nullptr, *Fp = nullptr;
+    B200_TRY(arena.alloc((void **)&ev, sizeof(float) * E));
+    B200_TRY(arena.alloc((void **)&ec, sizeof(uint16_t) * E));
+    B200_TRY(arena.alloc((void **)&chunk_row0, sizeof(int) * (E / kChunk)));
+    B200_TRY(arena.alloc((void **)&Yp, sizeof(float2) * (size_t)ntiles * T));
+    if (rows == N) Yown = Yp;
+    else B200_TRY(arena.alloc((void **)&Yown, sizeof(float2) * rows));
+    B200_TRY(arena.alloc((void **)&Fp, sizeof(float2) * rows));
+    B200_CUDA(cudaMemsetAsync(ev, 0, sizeof(float) * E, st));
+    B200_CUDA(cudaMemsetAsync(ec, 0, sizeof(uint16_t) * E, st));
+    B200_CUDA(cudaMemsetAsync(chunk_row0, 0, sizeof(int) * (E / kChunk), st));
+    B200_CUDA(cudaMemsetAsync(Yp, 0, sizeof(float2) * (size_t)ntiles * T, st));
+    walk_kernel<true><<<walk_blocks, kWalkWarps * 32, 0, st>>>(a, nullptr, range_size, tile_start, ev, ec, chunk_row0, totals);
+    B200_CUDA(cudaGetLastError());
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        B200_CUDA(cudaFuncSetAttribute(attractive_blocked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileMax * (int)sizeof(float2)));
+        attr_set[dev] = true;
+    }
+    B200_CUDA(cudaStreamSynchronize(st));   // the temporaries go away with `tmp`
+
+    b->ev = ev; b->ec = ec; b->chunk_row0 = chunk_row0; b->tile_chunk0 = tile_chunk0;
+    b->perm = perm; b->own_perm = own_perm; b->own_pos = own_pos;
+    b->Yp = Yp; b->Yown = Yown; b->Fp = Fp;
+    b->ntiles = ntiles; b->T = T; b->C = (int)(E / kChunk); b->E = E; b->groups = (int64_t)h_tot[0];
+    b->N = N; b->row_lo = row_lo; b->rows = rows;
+    b->ready = true;
+    return 0;
+}
+
+// F2[row_lo + r] = attractive force of the owned rows on the embedding Y2 (three launches)
+int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st)
+{
+    if (!b.ready) { set_error("attractive: the blocked copy of P was not built"); return -1; }
+    const unsigned gN = (unsigned)((std::max(b.N, b.rows) + 255) / 256);
+    permute_kernel<<<gN, 256, 0, st>>>(Y2, b.perm, b.N, b.Yp, b.own_perm, b.rows, b.Yown, b.Fp);
+    BlockedStream s;
+    s.ev = b.ev; s.ec = b.ec; s.chunk_row0 = b.chunk_row0; s.tile_chunk0 = b.tile_chunk0;
+    s.ntiles = b.ntiles; s.T = b.T; s.C = b.C;
+    int sms = 148;
+    {
+        static int cached[64] = {0};
+        int dev = 0;
+        B200_CUDA(cudaGetDevice(&dev));
+        if (dev >= 0 && dev < 64) {
+            if (!cached[dev]) B200_CUDA(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
+            sms = cached[dev];
+        }
+    }
+    const int grid = std::max(1, std::min(sms, b.C));
+    attractive_blocked_kernel<<<grid, kBlockedThreads, (size_t)b.T * sizeof(float2), st>>>(s, b.Yp, b.Yown, b.N, b.Fp);
+    unpermute_kernel<<<(unsigned)((b.rows + 255) / 256), 256, 0, st>>>(b.Fp, b.own_pos, b.row_lo, b.rows, F2);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace b200

@@ -5,9 +5,11 @@
 
 #include <algorithm>
 #include <new>
+#include <string>
 
 #include "../../include/tsnecuda_b200.h"
 #include "comm.h"
+#include "peer.h"
 #include "session.h"
 
 using namespace b200;
@@ -68,6 +70,7 @@ int b200tsne_knn(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t 
     StreamGuard sg;
     B200_TRY(sg.create());
     DeviceArena a;
+    a.serve(sg.st);
     float *dX = nullptr, *dd = nullptr;
     int32_t *di = nullptr;
     const size_t nq = (size_t)(q_hi - q_lo);
@@ -93,6 +96,7 @@ int b200tsne_perplexity(const float *d2, int64_t N, int K, float perplexity, flo
     StreamGuard sg;
     B200_TRY(sg.create());
     DeviceArena a;
+    a.serve(sg.st);
     float *dd = nullptr, *dp = nullptr, *db = nullptr;
     unsigned int *dm = nullptr;
     const size_t n = (size_t)N * K;
@@ -120,6 +124,7 @@ int b200tsne_symmetrize(const float *p, const int32_t *ids, int64_t N, int K, fl
     StreamGuard sg;
     B200_TRY(sg.create());
     DeviceArena a;
+    a.serve(sg.st);
     float *dp = nullptr, *dP = nullptr;
     int32_t *di = nullptr;
     const size_t n = (size_t)N * K;
@@ -143,6 +148,7 @@ int b200tsne_attractive(const float *P, const int32_t *ids, const float *Y, int6
     StreamGuard sg;
     B200_TRY(sg.create());
     DeviceArena a;
+    a.serve(sg.st);
     float *dP = nullptr, *dY = nullptr, *dF = nullptr;
     float2 *dY2 = nullptr, *dF2 = nullptr;
     int32_t *di = nullptr;
@@ -162,6 +168,57 @@ int b200tsne_attractive(const float *P, const int32_t *ids, const float *Y, int6
     return 0;
 }
 
+int b200tsne_attractive_blocked(const float *P, const int32_t *ids, const float *Y, int64_t N, int K, int64_t row_lo,
+                                int64_t row_hi, const float *X, int D, float *F, float *entries_per_group, int device)
+{
+    if (!P || !ids || !Y || !F || N <= 0 || K <= 0 || row_lo < 0 || row_hi > N || row_lo > row_hi || (X && D <= 0)) {
+        set_error("b200tsne_attractive_blocked: invalid arguments");
+        return B200TSNE_ERR_INVALID;
+    }
+    B200_TRY(check_device(device));
+    StreamGuard sg;
+    B200_TRY(sg.create());
+    DeviceArena a;
+    a.serve(sg.st);
+    float *dP = nullptr, *dY = nullptr, *dF = nullptr, *dX = nullptr;
+    float2 *dY2 = nullptr, *dF2 = nullptr;
+    int32_t *di = nullptr, *perm = nullptr;
+    const size_t rows = (size_t)(row_hi - row_lo);
+    B200_TRY(up(a, &dP, P + (size_t)row_lo * K, rows * K, sg.st));
+    B200_TRY(up(a, &di, ids + (size_t)row_lo * K, rows * K, sg.st));
+    B200_TRY(up(a, &dY, Y, (size_t)2 * N, sg.st));
+    B200_TRY(a.alloc((void **)&dY2, sizeof(float2) * N));
+    B200_TRY(a.alloc((void **)&dF2, sizeof(float2) * N));
+    B200_TRY(a.alloc((void **)&dF, sizeof(float) * 2 * N));
+    if (X) {
+        B200_TRY(up(a, &dX, X, (size_t)N * D, sg.st));
+        B200_TRY(a.alloc((void **)&perm, sizeof(int32_t) * N));
+        B200_TRY(order_points_by_cell(dX, N, D, perm, sg.st));
+    }
+    B200_CUDA(cudaMemsetAsync(dF2, 0, sizeof(float2) * N, sg.st));
+    B200_TRY(launch_soa_to_aos(dY, dY2, N, sg.st));
+    BlockedAttractive blk;
+    B200_TRY(blocked_attractive_build(&blk, a, dP, di, N, K, row_lo, row_hi, perm, sg.st));
+    if (entries_per_group) *entries_per_group = blk.entries_per_group;
+    if (!blk.ready) {
+        set_error("b200tsne_attractive_blocked: the blocked copy was not built for this graph (entries per row and tile: " +
+                  std::to_string(blk.entries_per_group) + "); use b200tsne_attractive");
+        return B200TSNE_ERR_UNSUPPORTED;
+    }
+    B200_TRY(launch_attractive_blocked(blk, dY2, dF2, sg.st));
+    B200_TRY(launch_aos_to_soa(dF2, dF, N, sg.st));
+    B200_TRY(down(F, dF, (size_t)2 * N, sg.st));
+    B200_CUDA(cudaStreamSynchronize(sg.st));
+    return 0;
+}
+
+int b200tsne_session_attractive_mode(b200tsne_session *h, float *entries_per_group)
+{
+    if (!h) return 0;
+    if (entries_per_group) *entries_per_group = h->s.blocked.entries_per_group;
+    return h->s.blocked.ready ? 1 : 0;
+}
+
 int b200tsne_repulsive(const float *Y, int64_t N, float *Frep, float *Z, float *w_out, float *ytilde_out, int device)
 {
     if (!Y || !Frep || !Z || N <= 0) { set_error("b200tsne_repulsive: invalid arguments"); return B200TSNE_ERR_INVALID; }
@@ -169,6 +226,7 @@ int b200tsne_repulsive(const float *Y, int64_t N, float *Frep, float *Z, float *
     StreamGuard sg;
     B200_TRY(sg.create());
     DeviceArena a;
+    a.serve(sg.st);
     float *dY = nullptr, *dF = nullptr;
     float2 *dY2 = nullptr, *dF2 = nullptr;
     float4 *dw = nullptr, *dyt = nullptr;
@@ -223,6 +281,7 @@ int b200tsne_apply_forces(float *Y, float *attr, float *rep, float *gains, float
     StreamGuard sg;
     B200_TRY(sg.create());
     DeviceArena a;
+    a.serve(sg.st);
     float *d[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     float *h[5] = {Y, attr, rep, gains, old_forces};
     for (int k = 0; k < 5; k++) B200_TRY(up(a, &d[k], (const float *)h[k], (size_t)2 * N, sg.st));
@@ -280,7 +339,8 @@ int b200tsne_session_set_affinities(b200tsne_session *h, const float *P_rows, co
     B200_CUDA(cudaMemcpyAsync(s.P, P_rows, sizeof(float) * n, cudaMemcpyHostToDevice, s.stream));
     B200_CUDA(cudaMemcpyAsync(s.ids, ids_rows, sizeof(int32_t) * n, cudaMemcpyHostToDevice, s.stream));
     B200_CUDA(cudaStreamSynchronize(s.stream));
-    return 0;
+    s.cell_order = nullptr;   // no points to order by: the blocked copy, if the graph suits it, uses the natural order
+    return s.build_blocked();
 }
 
 int b200tsne_session_get_affinities(b200tsne_session *h, float *P_rows, int32_t *ids_rows)
@@ -393,6 +453,30 @@ int b200tsne_session_exchange_mode(b200tsne_session *h)
 {
     if (!h || !h->s.comm || h->s.comm->world < 2) return 0;
     return h->s.px ? 2 : 1;
+}
+
+int b200tsne_session_set_peer_timeout_ms(b200tsne_session *h, int timeout_ms)
+{
+    if (!h || timeout_ms <= 0) { set_error("set_peer_timeout_ms: invalid arguments"); return B200TSNE_ERR_INVALID; }
+    if (!h->s.px) return 0;   // nothing to bound: single GPU or collectives
+    h->s.px->timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
+    h->s.drop_graphs();       // the limit is a launch argument frozen into captured iterations
+    return 0;
+}
+
+int b200tsne_selftest_bounded_waits(int device, int timeout_ms, int *peer_status, float *peer_ms, int *barrier_status,
+                                    float *barrier_ms)
+{
+    B200_TRY(check_device(device));
+    StreamGuard sg;
+    B200_TRY(sg.create());
+    const int ps = peer_wait_selftest(timeout_ms, peer_ms, sg.st);
+    if (ps != 0 && ps != B200TSNE_ERR_COMM) return ps;
+    const int bs = mbar_wait_selftest(timeout_ms, barrier_ms, sg.st);
+    if (bs != 0 && bs != B200TSNE_ERR_COMM) return bs;
+    if (peer_status) *peer_status = ps;
+    if (barrier_status) *barrier_status = bs;
+    return 0;
 }
 
 }  // extern "C"

@@ -85,6 +85,7 @@ size_t knn_tc_workspace_bytes(int D, int K, int64_t nq, int64_t nd);
 int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_hi, int64_t db_lo, int64_t db_hi,
                   int32_t *ids, float *d2, void *workspace, int **failed_list, int *n_failed_host, float *err_ratio_host,
                   cudaStream_t st);
+int mbar_wait_selftest(int timeout_ms, float *waited_ms, cudaStream_t st);   // see b200tsne_selftest_bounded_waits
 struct KnnStats {
     int tensor_core = 0;            // 1 when the tensor-core path ran
     int rows_recomputed = 0;        // rows the proof could not certify, recomputed by the SIMT search
@@ -110,6 +111,25 @@ int launch_symmetrize(const float *p_all, const int32_t *ids_all, int64_t N, int
 // attractive.cu   (Y2: AoS float2 [N]; F2: AoS float2, rows [row_lo,row_hi) written at their global index)
 int launch_attractive(const float *P_rows, const int32_t *ids_rows, const float2 *Y2, int64_t N, int K, int64_t row_lo,
                       int64_t row_hi, float2 *F2, cudaStream_t st);
+
+// attractive_blocked.cu: column-blocked copy of P whose gathers come from shared memory (see that file)
+struct DeviceArena;
+struct BlockedAttractive {
+    const float *ev = nullptr;
+    const uint16_t *ec = nullptr;
+    const int *chunk_row0 = nullptr, *tile_chunk0 = nullptr;
+    const int32_t *perm = nullptr, *own_perm = nullptr, *own_pos = nullptr;
+    float2 *Yp = nullptr, *Yown = nullptr, *Fp = nullptr;
+    int ntiles = 0, T = 0, C = 0;
+    int64_t E = 0, groups = 0, N = 0, row_lo = 0, rows = 0;
+    float entries_per_group = 0.0f;   // of the sampled rows, under the chosen order
+    bool ready = false;
+    void clear();
+};
+int order_points_by_cell(const float *X, int64_t N, int D, int32_t *perm, cudaStream_t st);
+int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const float *P_rows, const int32_t *ids_rows, int64_t N, int K,
+                             int64_t row_lo, int64_t row_hi, const int32_t *perm, cudaStream_t st);
+int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st);
 
 // repulsive.cu
 struct FftWorkspace {

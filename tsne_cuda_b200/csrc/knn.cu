@@ -22,6 +22,8 @@
 #include <string>
 
 #include "common.cuh"
+
+#include <atomic>
 #include "session.h"
 
 namespace b200 {
@@ -390,6 +392,7 @@ int knn_search(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t q_
     const char *force = getenv("B200TSNE_KNN");
     const bool want_tc = knn_tc_supported(db_hi - db_lo, D, K) && !(force && strcmp(force, "simt") == 0);
     DeviceArena tmp;
+    tmp.serve(st);
     float *XT = nullptr;
     auto ensure_xt = [&]() -> int {
         if (XT) return 0;
@@ -445,16 +448,16 @@ static __device__ __align__(256) float g_noalloc_xt[kNoAllocMaxElems];
 // differs per device.  Looked up once per device, with that device current.
 static int noalloc_scratch(float **out)
 {
-    static float *cached[64] = {nullptr};
+    static std::atomic<float *> cached[64];   // zero-initialised; two threads racing here store the same address
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) { set_error("knn_noalloc: device ordinal out of range"); return -4; }
-    if (!cached[dev]) {
-        float *p = nullptr;
+    float *p = cached[dev].load(std::memory_order_acquire);
+    if (!p) {
         B200_CUDA(cudaGetSymbolAddress((void **)&p, g_noalloc_xt));
-        cached[dev] = p;
+        cached[dev].store(p, std::memory_order_release);
     }
-    *out = cached[dev];
+    *out = p;
     return 0;
 }
 
@@ -464,6 +467,7 @@ long long knn_noalloc_max_elems() { return kNoAllocMaxElems; }
 int knn_noalloc(const float *X, int64_t N, int D, int K, int32_t *ids, float *d2, cudaStream_t st)
 {
     if (N <= 0 || D <= 0 || K <= 0) { set_error("knn_noalloc: invalid sizes"); return -1; }
+    if (D > 65535 * 32) { set_error("knn_noalloc: more than 2,097,120 dimensions are not supported"); return -4; }
     if ((long long)N * D > kNoAllocMaxElems) {
         set_error("knn_noalloc: N * D = " + std::to_string((long long)N * D) + " exceeds the built-in scratch of " +
                   std::to_string(kNoAllocMaxElems) + " floats; use b200tsne_knn");

@@ -111,7 +111,8 @@ __device__ __forceinline__ unsigned long long global_ns()
 // Bounded wait: gives up after 4 s or as soon as another thread of the block has given up.  A waiting
 // thread sleeps between polls: the producer and the MMA issuer share their schedulers with epilogue
 // warps, and a busy poll would take every other issue slot from them.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned sleep_ns = 128)
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned sleep_ns = 128,
+                                          unsigned long long limit_ns = 4000000000ull)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
@@ -120,7 +121,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
         __nanosleep(sleep_ns);
         if ((++spins & 63) == 0) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > 4000000000ull) { *abort_flag = 1; return false; }
+            if (global_ns() - t0 > limit_ns) { *abort_flag = 1; return false; }
         }
     }
     return true;
@@ -1335,6 +1336,22 @@ __global__ void knn_tc_collect_failed_kernel(const int *__restrict__ failed, lon
     if (q < nq && failed[q]) list[atomicAdd(count, 1)] = qlist[q];
 }
 
+
+// Exercises mbar_wait's limit: a barrier that expects one arrival and never gets it.  Every thread of the
+// block must come back with `false` after limit_ns and the block must exit normally.
+__global__ void mbar_wait_selftest_kernel(int *abort_flag, int *gave_up, unsigned long long limit_ns)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const bool ok = mbar_wait(&bar, 0, abort_flag, 128, limit_ns);
+    if (!ok) atomicAdd(gave_up, 1);
+    __syncthreads();
+    if (threadIdx.x == 0) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar)) : "memory");
+}
 }  // namespace
 
 // wide points: the inner dimension (D + 1) does not fit the narrow kernel's shared-memory images
@@ -1614,6 +1631,33 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     *n_failed_host = h[2];
     *failed_list = flist;
     if (err_ratio_host) memcpy(err_ratio_host, &h[3], sizeof(float));
+    return 0;
+}
+
+
+// Runs mbar_wait_selftest_kernel: returns -5 when all 64 threads gave up within the limit (the expected
+// outcome), 0 if any of them (wrongly) got through.
+int mbar_wait_selftest(int timeout_ms, float *waited_ms, cudaStream_t st)
+{
+    if (timeout_ms <= 0 || timeout_ms > 2000) { set_error("mbarrier wait self-test: timeout must be 1..2000 ms"); return -1; }
+    int *d = nullptr;
+    cudaEvent_t a = nullptr, b = nullptr;
+    struct Free { int *&d; cudaEvent_t &a, &b; ~Free() { if (d) cudaFree(d); if (a) cudaEventDestroy(a); if (b) cudaEventDestroy(b); } } guard{d, a, b};
+    B200_CUDA(cudaMalloc((void **)&d, sizeof(int) * 2));
+    B200_CUDA(cudaMemsetAsync(d, 0, sizeof(int) * 2, st));
+    B200_CUDA(cudaEventCreate(&a));
+    B200_CUDA(cudaEventCreate(&b));
+    B200_CUDA(cudaEventRecord(a, st));
+    mbar_wait_selftest_kernel<<<1, 64, 0, st>>>(d, d + 1, (unsigned long long)timeout_ms * 1000000ull);
+    B200_CUDA(cudaGetLastError());
+    B200_CUDA(cudaEventRecord(b, st));
+    B200_CUDA(cudaStreamSynchronize(st));
+    float ms = 0.0f;
+    B200_CUDA(cudaEventElapsedTime(&ms, a, b));
+    if (waited_ms) *waited_ms = ms;
+    int h[2] = {0, 0};
+    B200_CUDA(cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost));
+    if (h[0] == 1 && h[1] == 64) { set_error("kNN pipeline: a barrier wait ran out (self-test)"); return -5; }
     return 0;
 }
 

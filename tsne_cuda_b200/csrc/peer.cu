@@ -1,5 +1,6 @@
 #include "peer.h"
 
+#include <stdlib.h>
 #include <string.h>
 #include <time.h>
 
@@ -14,6 +15,12 @@ namespace {
 constexpr size_t kAlign = 256;
 size_t round_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
 
+// Flag words of a rank: [kind][writer rank] epochs, then [writer rank][2] the writers' min/max encodings, then one
+// abort word that a rank whose wait expired sets in every rank's block.
+constexpr int kMinMaxOffset = 2 * kMaxPeers;
+constexpr int kAbortOffset = 4 * kMaxPeers;
+constexpr int kFlagWords = 4 * kMaxPeers + 16;
+
 struct Layout {
     size_t w[2], y[2], flags, total;
 };
@@ -24,7 +31,7 @@ Layout block_layout(int64_t npad)
     for (int b = 0; b < 2; b++) { l.w[b] = o; o += round_up(sizeof(float4) * (size_t)kG * kG); }
     for (int b = 0; b < 2; b++) { l.y[b] = o; o += round_up(sizeof(float2) * (size_t)npad); }
     l.flags = o;
-    o += round_up(sizeof(unsigned int) * 4 * kMaxPeers);   // epochs [2][ranks], min/max [ranks][2]
+    o += round_up(sizeof(unsigned int) * kFlagWords);   // epochs [2][ranks], min/max [ranks][2], abort word
     l.total = o;
     return l;
 }
@@ -36,16 +43,21 @@ __device__ __forceinline__ unsigned long long peer_global_ns()
     return t;
 }
 
-// Flag words of a rank: [kind][writer rank] epochs, then [writer rank][2] the writers' min/max encodings.
-constexpr int kMinMaxOffset = 2 * kMaxPeers;
-
 // One warp, one launch per meeting: lane r publishes `value` in this rank's slot of rank r's flag array, then
 // waits until rank r's slot of the local array has reached it; gives up after 2 s.  With `state` the ranks also
 // exchange the min/max of the rows they have just updated (IterState slot mm_slot) and leave the global
 // min/max there, which replaces a pass over the whole embedding.
-__global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int *epochs, IterState *state, int mm_slot, int *err)
+__global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int *epochs, IterState *state, int mm_slot, int *err,
+                                    int *err_host, unsigned long long timeout_ns)
 {
     const int lane = threadIdx.x;
+    // An earlier meeting of this exchange gave up, here or on a peer (which then set the abort word in every
+    // rank's block): publish (a live peer may still wait for it) but do not wait again.
+    bool dead = *reinterpret_cast<volatile int *>(err) != 0;
+    if (!dead && *reinterpret_cast<volatile unsigned int *>(tab.flags[tab.rank] + kAbortOffset) != 0) {
+        dead = true;
+        if (lane == 0) { atomicExch(err, 1); *reinterpret_cast<volatile int *>(err_host) = 1; }
+    }
     // the meeting's number: a device counter per kind that every rank advances alike (a launch parameter
     // would be frozen into a captured graph)
     unsigned int value = 0;
@@ -64,6 +76,7 @@ __global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int *epoch
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(value) : "memory");
     }
     unsigned int mn = 0xffffffffu, mx = 0u;
+    if (dead) return;
     if (lane < tab.world) {
         const unsigned int *mine = tab.flags[tab.rank];
         const unsigned int *f = mine + kind * kMaxPeers + lane;
@@ -74,10 +87,18 @@ __global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int *epoch
             unsigned int v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
             if ((int)(v - value) >= 0) break;
-            if ((++spins & 255) == 0 && peer_global_ns() - t0 > 2000000000ull) {
-                atomicExch(err, 1);
-                ok = false;
-                break;
+            if ((++spins & 255) == 0) {
+                const bool aborted = *reinterpret_cast<const volatile unsigned int *>(mine + kAbortOffset) != 0;
+                if (aborted || peer_global_ns() - t0 > timeout_ns) {
+                    atomicExch(err, 1);
+                    *reinterpret_cast<volatile int *>(err_host) = 1;
+                    // tell every rank: whoever still waits, or meets later, gives up too instead of carrying on
+                    // with what this rank computes from now on
+                    for (int r = 0; r < tab.world; r++)
+                        *reinterpret_cast<volatile unsigned int *>(tab.flags[r] + kAbortOffset) = 1u;
+                    ok = false;
+                    break;
+                }
             }
         }
         if (state && ok) {
@@ -150,7 +171,8 @@ grid_z_kernel(const float4 *__restrict__ w_sum, const float4 *__restrict__ ytild
 void peer_exchange_release(PeerExchange *px, Comm *comm)
 {
     if (!px) return;
-    if (comm && !comm->px_idle) comm->px_idle = px;   // every rank releases and acquires in the same order
+    // a block whose meeting gave up keeps its error word and diverged epochs: never cache it
+    if (comm && !comm->px_idle && !px->failed && !*px->err_host) comm->px_idle = px;   // every rank releases and acquires in the same order
     else peer_exchange_destroy(px, comm, nullptr);
 }
 
@@ -174,9 +196,31 @@ int peer_exchange_acquire(PeerExchange **out, Comm *comm, int64_t npad, cudaStre
     PeerExchange *px = new PeerExchange();
     px->npad = npad;
     for (int r = 0; r < kMaxPeers; r++) px->mapped[r] = nullptr;
-    struct Fail { PeerExchange *px; bool armed = true; ~Fail() { if (armed) { if (px->local) cudaFree(px->local); if (px->err) cudaFree(px->err); delete px; } } } fail{px};
+    struct Fail {
+        PeerExchange *px;
+        bool armed = true;
+        ~Fail()
+        {
+            if (!armed) return;
+            if (px->local) cudaFree(px->local);
+            if (px->err) cudaFree(px->err);
+            if (px->err_host) cudaFreeHost(const_cast<int *>(px->err_host));
+            delete px;
+        }
+    } fail{px};
+    if (const char *e = getenv("B200TSNE_PEER_TIMEOUT_MS")) {
+        const long long ms = atoll(e);
+        if (ms > 0) px->timeout_ns = (unsigned long long)ms * 1000000ull;
+    }
     B200_CUDA(cudaMalloc(&px->local, lay.total));
     B200_CUDA(cudaMalloc((void **)&px->err, sizeof(int) * 4));
+    {
+        int *h = nullptr;
+        B200_CUDA(cudaHostAlloc((void **)&h, sizeof(int), cudaHostAllocMapped));
+        *h = 0;
+        px->err_host = h;
+        B200_CUDA(cudaHostGetDevicePointer((void **)&px->err_host_dev, h, 0));
+    }
     B200_CUDA(cudaMemsetAsync(px->local, 0, lay.total, st));
     B200_CUDA(cudaMemsetAsync(px->err, 0, sizeof(int) * 4, st));
 
@@ -210,6 +254,9 @@ int peer_exchange_acquire(PeerExchange **out, Comm *comm, int64_t npad, cudaStre
     if (h_flag) {
         for (int r = 0; r < W; r++)
             if (px->mapped[r]) cudaIpcCloseMemHandle(px->mapped[r]);
+        // nobody may free a block that a slower peer still has mapped: meet once more after closing
+        B200_TRY(comm->all_reduce_max_u32(d_flag, 1, st));
+        B200_CUDA(cudaStreamSynchronize(st));
         return 0;   // `fail` frees the rest; the caller keeps the collectives
     }
     px->tab.world = W;
@@ -252,14 +299,61 @@ void peer_exchange_destroy(PeerExchange *px, Comm *comm, cudaStream_t st)
     if (met) {
         cudaFree(px->local);
         cudaFree(px->err);
+        if (px->err_host) cudaFreeHost(const_cast<int *>(px->err_host));
     }
     delete px;
 }
 
 int launch_peer_barrier(PeerExchange *px, int kind, IterState *state, int mm_slot, cudaStream_t st)
 {
-    peer_barrier_kernel<<<1, 32, 0, st>>>(px->tab, kind, reinterpret_cast<unsigned int *>(px->err) + 2, state, mm_slot, px->err);
+    peer_barrier_kernel<<<1, 32, 0, st>>>(px->tab, kind, reinterpret_cast<unsigned int *>(px->err) + 2, state, mm_slot, px->err,
+                                          px->err_host_dev, px->timeout_ns);
     B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int peer_wait_selftest(int timeout_ms, float *waited_ms, cudaStream_t st)
+{
+    if (timeout_ms <= 0 || timeout_ms > 2000) { set_error("peer wait self-test: timeout must be 1..2000 ms"); return -1; }
+    // "rank 0" and "rank 1" are two local flag arrays; nothing ever writes rank 1's epoch into rank 0's array
+    unsigned int *flags = nullptr;
+    int *err = nullptr, *err_host = nullptr, *err_host_dev = nullptr;
+    cudaEvent_t a = nullptr, b = nullptr;
+    struct Free {
+        unsigned int *&f; int *&e; int *&h; cudaEvent_t &a, &b;
+        ~Free() { if (f) cudaFree(f); if (e) cudaFree(e); if (h) cudaFreeHost(h); if (a) cudaEventDestroy(a); if (b) cudaEventDestroy(b); }
+    } guard{flags, err, err_host, a, b};
+    const size_t words = kFlagWords;
+    B200_CUDA(cudaMalloc((void **)&flags, sizeof(unsigned int) * words * 2));
+    B200_CUDA(cudaMalloc((void **)&err, sizeof(int) * 4));
+    B200_CUDA(cudaHostAlloc((void **)&err_host, sizeof(int), cudaHostAllocMapped));
+    *err_host = 0;
+    B200_CUDA(cudaHostGetDevicePointer((void **)&err_host_dev, err_host, 0));
+    B200_CUDA(cudaMemsetAsync(flags, 0, sizeof(unsigned int) * words * 2, st));
+    B200_CUDA(cudaMemsetAsync(err, 0, sizeof(int) * 4, st));
+    B200_CUDA(cudaEventCreate(&a));
+    B200_CUDA(cudaEventCreate(&b));
+    PeerTable tab;
+    memset(&tab, 0, sizeof(tab));
+    tab.world = 2;
+    tab.rank = 0;
+    tab.flags[0] = flags;
+    tab.flags[1] = flags + words;
+    const unsigned long long ns = (unsigned long long)timeout_ms * 1000000ull;
+    B200_CUDA(cudaEventRecord(a, st));
+    peer_barrier_kernel<<<1, 32, 0, st>>>(tab, kFlagSpread, reinterpret_cast<unsigned int *>(err) + 2, nullptr, 0, err, err_host_dev, ns);
+    B200_CUDA(cudaGetLastError());
+    // a second meeting on the failed exchange must return at once (it sees the error word on entry)
+    peer_barrier_kernel<<<1, 32, 0, st>>>(tab, kFlagUpdate, reinterpret_cast<unsigned int *>(err) + 2, nullptr, 0, err, err_host_dev, ns);
+    B200_CUDA(cudaGetLastError());
+    B200_CUDA(cudaEventRecord(b, st));
+    B200_CUDA(cudaStreamSynchronize(st));
+    float ms = 0.0f;
+    B200_CUDA(cudaEventElapsedTime(&ms, a, b));
+    if (waited_ms) *waited_ms = ms;
+    int d_err = 0;
+    B200_CUDA(cudaMemcpy(&d_err, err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (d_err && *err_host) { set_error("peer exchange: a rank did not arrive within the limit (self-test)"); return -5; }
     return 0;
 }
 

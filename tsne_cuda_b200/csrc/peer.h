@@ -11,9 +11,13 @@
 //     rank.
 // Ranks meet twice per iteration ("all spreads done", "all updates done") through flag words: a one-warp
 // kernel stores the iteration's epoch into its slot of every rank's flag array (release, system scope) and
-// then polls the local array until all slots carry it (acquire).  The polls are bounded (2 s); on expiry
-// an error word is set that the host reads when the run returns.  The second meeting also carries the
-// min/max of each rank's new rows, so the bounding box of the next grid needs no pass over the embedding.
+// then polls the local array until all slots carry it (acquire).  The polls are bounded (2 s unless
+// B200TSNE_PEER_TIMEOUT_MS or the session says otherwise).  On expiry the kernel sets an error word in device
+// memory and a second one in mapped host memory: every later meeting sees the first on entry and returns at
+// once instead of waiting again, and the host sees the second without synchronising, stops queueing
+// iterations and returns status -5.  An exchange that has failed is never reused.  The second meeting also
+// carries the min/max of each rank's new rows, so the bounding box of the next grid needs no pass over the
+// embedding.
 //
 // Buffers are double-buffered by iteration parity so that a fast rank never overwrites what a slow rank
 // still reads: grid buffer b is written by the spread of iterations with parity b and read by the peers in
@@ -45,6 +49,10 @@ struct PeerExchange {
     void *local = nullptr;       // this rank's block
     void *mapped[kMaxPeers];     // peers' blocks as mapped here (null for this rank)
     int *err = nullptr;          // device words: [0] a bounded wait expired, [1] scratch of the closing meeting, [2], [3] epoch counters per kind
+    volatile int *err_host = nullptr;   // mapped host word the kernel sets on expiry (read by the host without a sync)
+    int *err_host_dev = nullptr;        // the same word as the device addresses it
+    unsigned long long timeout_ns = 2000000000ull;   // limit of one meeting
+    bool failed = false;         // a wait expired: the block is destroyed, not cached, when it is released
     int parity = 0;              // which of the two buffers holds the current embedding / grid (alike on all ranks)
     int64_t npad = 0;
 
@@ -64,6 +72,10 @@ void peer_exchange_destroy(PeerExchange *px, Comm *comm, cudaStream_t st);
 // All ranks meet: publish the next epoch of `kind` everywhere, wait (bounded) until every rank has.  With `state`, the
 // ranks' min/max encodings in IterState slot mm_slot are combined across the ranks on the way.
 int launch_peer_barrier(PeerExchange *px, int kind, IterState *state, int mm_slot, cudaStream_t st);
+// Exercises the bounded wait on one GPU without a peer: a two-rank table whose second rank is local memory
+// that nothing writes.  The meeting must give up after timeout_ms, set both error words and leave the device
+// usable; returns -5 when it did, 0 when the wait (wrongly) succeeded.
+int peer_wait_selftest(int timeout_ms, float *waited_ms, cudaStream_t st);
 // w_sum[node] = sum over ranks (in rank order) of their partial grid `buf`
 int launch_peer_grid_reduce(PeerExchange *px, int buf, float4 *w_sum, cudaStream_t st);
 // state->zsum[slot] += sum over nodes of the bilinear form of charges w_sum and potentials ytilde

@@ -85,6 +85,10 @@ int DeviceArena::alloc(void **p, size_t bytes)
 }
 void DeviceArena::release()
 {
+    // also on error paths, where kernels queued on a consumer stream may still be running
+    if (!ptrs.empty())
+        for (cudaStream_t st : consumers) cudaStreamSynchronize(st);
+    consumers.clear();
     for (void *p : ptrs) cudaFreeAsync(p, cudaStreamPerThread);
     if (!ptrs.empty()) cudaStreamSynchronize(cudaStreamPerThread);
     ptrs.clear();
@@ -105,6 +109,10 @@ int Session::init(int64_t N_, int K_, int64_t lo, int64_t hi, int device_)
     B200_CUDA(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
     B200_CUDA(cudaEventCreate(&ev_t0));
     B200_CUDA(cudaEventCreate(&ev_t1));
+    arena.serve(stream);
+    arena.serve(stream2);
+    blocked_arena.serve(stream);
+    blocked_arena.serve(stream2);
     // Y2 and the force arrays are padded so that an in-place all-gather over up to 16 ranks fits
     const int64_t npad = N + 16;
     const int64_t r = std::max<int64_t>(rows(), 1);
@@ -152,6 +160,8 @@ void Session::destroy()
     drop_graphs();
     if (px) { peer_exchange_release(px, comm); px = nullptr; }
     comm = nullptr;  // owned by the communicator cache (comm.h)
+    blocked.clear();
+    blocked_arena.release();
     arena.release();
     if (h_state) cudaFreeHost(h_state);
     if (ev_fork) cudaEventDestroy(ev_fork);
@@ -240,9 +250,9 @@ int Session::one_iteration(bool want_norm)
     if (!stage_timers) {
         B200_CUDA(cudaEventRecord(ev_fork, stream));
         B200_CUDA(cudaStreamWaitEvent(stream2, ev_fork, 0));
-        B200_TRY(launch_attractive(P, ids, Y2, N, K, row_lo, row_hi, Fattr, sa));
+        B200_TRY(attractive(sa));
         B200_CUDA(cudaEventRecord(ev_join, stream2));
-        launches += 1;
+        launches += blocked.ready ? 3 : 1;
     }
 
     // The embedding reshuffles quickly while it is being exaggerated and slowly afterwards: sort every
@@ -285,8 +295,8 @@ int Session::one_iteration(bool want_norm)
     }
     if (stage_timers) {
         clk.begin(stream);
-        B200_TRY(launch_attractive(P, ids, Y2, N, K, row_lo, row_hi, Fattr, stream));
-        clk.end(stream, kStAttractive, 1);
+        B200_TRY(attractive(stream));
+        clk.end(stream, kStAttractive, blocked.ready ? 3 : 1);
     } else {
         B200_CUDA(cudaStreamWaitEvent(stream, ev_join, 0));
     }
@@ -318,6 +328,24 @@ int Session::one_iteration(bool want_norm)
     }
     step++;
     return 0;
+}
+
+int Session::attractive(cudaStream_t st)
+{
+    if (blocked.ready) return launch_attractive_blocked(blocked, Y2, Fattr, st);
+    return launch_attractive(P, ids, Y2, N, K, row_lo, row_hi, Fattr, st);
+}
+
+int Session::build_blocked()
+{
+    B200_CUDA(cudaStreamSynchronize(stream));
+    B200_CUDA(cudaStreamSynchronize(stream2));
+    drop_graphs();   // captured iterations hold the pointers of the previous copy
+    blocked.clear();
+    blocked_arena.release();
+    blocked_arena.serve(stream);
+    blocked_arena.serve(stream2);
+    return blocked_attractive_build(&blocked, blocked_arena, P, ids, N, K, row_lo, row_hi, cell_order, stream);
 }
 
 void Session::drop_graphs()
@@ -402,6 +430,8 @@ int Session::iterate(int n_iters, float min_gradient_norm, float *elapsed_ms, in
     int done = 0;
     B200_CUDA(cudaEventRecord(ev_t0, stream));
     for (int it = 0; it < n_iters; it++) {
+        // a meeting of the ranks gave up (the kernel says so in mapped host memory): queue nothing more
+        if (px && *px->err_host) break;
         int kind = 0;
         const int block = graph_block(n_iters - it, want_norm, &kind);
         if (block > 0) {
@@ -439,7 +469,11 @@ int Session::iterate(int n_iters, float min_gradient_norm, float *elapsed_ms, in
     if (px) {
         int expired = 0;
         B200_CUDA(cudaMemcpy(&expired, px->err, sizeof(int), cudaMemcpyDeviceToHost));
-        if (expired) { set_error("peer exchange: a rank did not arrive within 2 s"); return -5; }
+        if (expired || *px->err_host) {
+            px->failed = true;
+            set_error("peer exchange: a rank did not arrive within " + std::to_string(px->timeout_ns / 1000000ull) + " ms");
+            return -5;
+        }
     }
     return 0;
 }
@@ -468,6 +502,7 @@ int Session::affinities_from_points(const float *X_host, int D, float perplexity
     if (K > N) { set_error("affinities: num_neighbors exceeds num_points"); return -1; }
     const bool multi = comm && comm->world > 1;
     DeviceArena tmp;
+    tmp.serve(stream);
     float *X = nullptr, *d2 = nullptr, *p_all = nullptr;
     int32_t *ids_all = nullptr;
     unsigned int *max_enc = nullptr;
@@ -509,6 +544,16 @@ int Session::affinities_from_points(const float *X_host, int D, float perplexity
     clk.end(stream, kStKnn, 4);
 
     clk.begin(stream);
+    // the order in which the attractive force's blocked copy of P numbers the points (every rank computes the same)
+    {
+        const char *mode = getenv("B200TSNE_ATTRACTIVE");
+        if (!(mode && strcmp(mode, "rows") == 0)) {
+            if (!cell_order) B200_TRY(arena.alloc((void **)&cell_order, sizeof(int32_t) * N));
+            B200_TRY(order_points_by_cell(X, N, D, cell_order, stream));
+        }
+    }
+
+    clk.begin(stream);
     const unsigned int zero_enc = enc_float(0.0f);
     B200_CUDA(cudaMemcpyAsync(max_enc, &zero_enc, sizeof(unsigned int), cudaMemcpyHostToDevice, stream));
     B200_TRY(launch_absmax(d2, r * K, max_enc, stream));
@@ -526,6 +571,7 @@ int Session::affinities_from_points(const float *X_host, int D, float perplexity
         ids_for_sym = ids_all;
     }
     B200_TRY(launch_symmetrize(p_all, ids_for_sym, N, K, row_lo, row_hi, P, stream));
+    B200_TRY(build_blocked());
     clk.end(stream, kStAffinities, 3);
     B200_CUDA(cudaStreamSynchronize(stream));
     return 0;

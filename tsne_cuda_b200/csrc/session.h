@@ -16,7 +16,9 @@ enum Stage { kStSpread = 0, kStConvolve, kStGather, kStAttractive, kStUpdate, kS
 // RAII holder for device allocations of a session
 struct DeviceArena {
     std::vector<void *> ptrs;
+    std::vector<cudaStream_t> consumers;   // streams whose work uses this memory: synchronised before anything is freed
     ~DeviceArena();
+    void serve(cudaStream_t st) { consumers.push_back(st); }
     int alloc(void **p, size_t bytes);
     void release();
 };
@@ -34,6 +36,12 @@ struct Session {
     // affinities (owned rows)
     float *P = nullptr;       // [rows][K]
     int32_t *ids = nullptr;   // [rows][K]
+    // Column-blocked copy of P for the attractive force (attractive_blocked.cu), built with the affinities when the
+    // neighbours of a row fall into few tiles of the cell order; otherwise the row-major kernel reads P / ids.
+    BlockedAttractive blocked;
+    DeviceArena blocked_arena;
+    int32_t *cell_order = nullptr;   // [N] point order by cell (from the points; null = natural order)
+    int build_blocked();             // (re)builds `blocked` from P / ids; drops captured iterations
     // embedding and optimiser state
     float2 *Y2 = nullptr;     // [N] AoS, replicated on every rank
     float2 *Fattr = nullptr;  // [N] (owned rows valid)
@@ -101,6 +109,7 @@ struct Session {
     int get_embedding_soa(float *Y_host);
     int iterate(int n_iters, float min_gradient_norm, float *elapsed_ms, int *iters_done);
     int one_iteration(bool want_norm);
+    int attractive(cudaStream_t st);   // Fattr of the owned rows from the current embedding
     int affinities_from_points(const float *X_host, int D, float perplexity, float eps);
 };
 
