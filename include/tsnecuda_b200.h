@@ -74,7 +74,7 @@ typedef struct b200tsne_options {
     float min_gradient_norm;
     int initialization_type;           /* 0 UNIFORM, 1 GAUSSIAN, 2 RESUME, 3 VECTOR (options.h:20-26) */
     const float *preinit_data;         /* SoA 2N floats when initialization_type is 2 or 3           */
-    int random_seed;
+    int random_seed;                   /* Options::random_seed (options.h:104); 0 = seed from the clock, as the reference's constructors do */
     int verbosity;
     int print_interval;
     int gpu_device;

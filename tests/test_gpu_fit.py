@@ -173,7 +173,7 @@ def test_library_drawn_initial_embedding_equals_the_reference(engine):
         pytest.skip("oracle/_ref/libtsnecuda_ref.so was not built (needs the reference tree)")
     X = mixture(700, 12, 4)
     for init_type in (1, 0):          # GAUSSIAN, UNIFORM
-        for seed in (0, 12345):
+        for seed in (7, 12345):     # (0 asks this library for a clock seed, as the reference's constructors do)
             Yr = ref.run_seeded(X, init_type, seed, iterations=0, num_neighbors=30, perplexity=10.0)
             Ym, _ = engine.fit(X, iterations=0, num_neighbors=30, perplexity=10.0, initialization_type=init_type,
                                random_seed=seed)

@@ -337,11 +337,16 @@ constexpr int kWalkWarps = 2;
 constexpr int kMaxK = 1024;
 struct WalkScratch {
     long long run[kMaxTiles];      // count pass: entries this range adds to the tile; fill pass: next free entry of the tile
-    int rowcnt[kMaxTiles];         // entries of the current row per tile
-    unsigned slot[kMaxK];          // per slot of the current row: tile << 16 | rank inside (row, tile); 0xffffffff = unused slot
+    unsigned rowcnt[kMaxTiles];    // low half: entries of the current row in the tile; high half: cells handed out in phase 2 of the fill
+    unsigned cellmask[kMaxTiles];  // fill pass: cells of the current (row, tile) group claimed in phase 1
+    unsigned slot[kMaxK];          // per slot of the current row, see kSlot*; 0xffffffff = unused slot
     unsigned short col[kMaxK];     // per slot: column inside the tile
     unsigned bitmap[2][32];        // tiles touched by the previous / the current row
 };
+// slot word: bits 16..25 tile, bit 30 first slot of its (row, tile) group, bit 29 cell claimed in phase 1,
+// low 16 bits: rank inside the group in slot order, later the cell
+constexpr unsigned kSlotLeader = 1u << 30, kSlotClaimed = 1u << 29, kSlotUnused = 0xffffffffu;
+__device__ __forceinline__ int slot_tile(unsigned info) { return (info >> 16) & 0x3ffu; }
 
 struct WalkArgs {
     const float *P_rows;           // [rows][K]
@@ -359,8 +364,8 @@ __device__ __forceinline__ void analyse_row(const WalkArgs &a, long long lr, Wal
     const long long r = (long long)a.own_perm[lr] - a.row_lo;
     for (int k0 = 0; k0 < a.K; k0 += 32) {
         const int sl = k0 + lane;
-        int j = (sl < a.K) ? a.ids_rows[r * a.K + sl] : -1;
-        const bool valid = (unsigned long long)(long long)j < (unsigned long long)a.N && j >= 0;
+        const int j = (sl < a.K) ? a.ids_rows[r * a.K + sl] : -1;
+        const bool valid = j >= 0 && (long long)j < a.N;
         int t = -1 - lane, c = 0;
         if (valid) {
             const int q = a.pos[j];
@@ -369,7 +374,7 @@ __device__ __forceinline__ void analyse_row(const WalkArgs &a, long long lr, Wal
         }
         const unsigned m = __match_any_sync(0xffffffffu, t);
         const int before = __popc(m & ((1u << lane) - 1u));
-        const int base = valid ? s.rowcnt[t] : 0;
+        const unsigned base = valid ? s.rowcnt[t] : 0u;
         __syncwarp();
         if (valid) {
             if (before == __popc(m) - 1) s.rowcnt[t] = base + __popc(m);
@@ -377,11 +382,27 @@ __device__ __forceinline__ void analyse_row(const WalkArgs &a, long long lr, Wal
         }
         __syncwarp();
         if (sl < a.K) {
-            s.slot[sl] = valid ? (((unsigned)t << 16) | (unsigned)(base + before)) : 0xffffffffu;
+            s.slot[sl] = valid ? (((unsigned)t << 16) | (base + before) | ((base + before) == 0 ? kSlotLeader : 0u)) : kSlotUnused;
             s.col[sl] = (unsigned short)c;
         }
     }
     __syncwarp();
+}
+
+// Entries of a group may stand in any order.  The kernel's k-th gather of a warp reads the k-th entry of all 32
+// lanes, 16 lanes per shared-memory pass, and a pass costs as many cycles as the most loaded pair of banks;
+// a float2 at column c lies in bank pair c mod 16.  So every cell (lane h of its half warp, entry k) of the
+// stream has a preferred bank pair (h + 4k) mod 16 - distinct for the 16 lanes of a pass - and a group
+// first gives its entries the cells that prefer their bank pairs (phase 1, at most one entry per cell), then
+// hands the remaining cells to the remaining entries in slot order (phase 2).  Groups of more than 32 entries
+// keep the slot order.
+__device__ __forceinline__ int preferred_cell(int bank_pair, int lane0, int n_lanes, int attempt)
+{
+    const int delta = (bank_pair - lane0) & 15;      // = l + 4k (mod 16) for cell (lane l of the group, entry k)
+    const int l = (delta & 3) + 4 * attempt;
+    if (l >= n_lanes) return -1;
+    const int k = ((delta - l) & 15) >> 2;
+    return 4 * l + k;
 }
 
 // FILL = false: add the row's groups to run[] (sizes) and count them.  FILL = true: write the row's entries.
@@ -392,21 +413,64 @@ __device__ __forceinline__ void emit_row(const WalkArgs &a, long long lr, WalkSc
 {
     const long long r = (long long)a.own_perm[lr] - a.row_lo;
     if (FILL) {
+        // phase 0: no cell of the row's groups is taken
         for (int k0 = 0; k0 < a.K; k0 += 32) {
             const int sl = k0 + lane;
-            const unsigned info = (sl < a.K) ? s.slot[sl] : 0xffffffffu;
-            if (info == 0xffffffffu) continue;
-            const int t = info >> 16, rank = info & 0xffffu;
+            const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
+            if (info != kSlotUnused && (info & kSlotLeader)) s.cellmask[slot_tile(info)] = 0u;
+        }
+        __syncwarp();
+        // phase 1: claim the preferred cell
+        for (int k0 = 0; k0 < a.K; k0 += 32) {
+            const int sl = k0 + lane;
+            unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
+            if (info == kSlotUnused) continue;
+            const int t = slot_tile(info);
+            const int cnt = (int)(s.rowcnt[t] & 0xffffu);
+            if (cnt > 32) continue;
+            const bool marker = !((prev[t >> 5] >> (t & 31)) & 1u);
+            const int lane0 = (int)(((s.run[t] >> 2) + (marker ? 1 : 0)) & 15);
+            const int n_lanes = (cnt + 3) >> 2;
+            for (int attempt = 0; attempt < 2; attempt++) {
+                const int x = preferred_cell(s.col[sl] & 15, lane0, n_lanes, attempt);
+                if (x < 0) break;
+                const unsigned old = atomicOr(&s.cellmask[t], 1u << x);
+                if (!((old >> x) & 1u)) {
+                    info = (info & 0xffff0000u) | kSlotClaimed | (unsigned)x;
+                    s.slot[sl] = info;
+                    break;
+                }
+            }
+        }
+        __syncwarp();
+        // phase 2: the other entries take the free cells in slot order; then every entry is written
+        for (int k0 = 0; k0 < a.K; k0 += 32) {
+            const int sl = k0 + lane;
+            const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
+            const bool valid = info != kSlotUnused;
+            const int t = valid ? slot_tile(info) : 0;
+            const int cnt = valid ? (int)(s.rowcnt[t] & 0xffffu) : 0;
+            const bool roams = valid && cnt <= 32 && !(info & kSlotClaimed);
+            const unsigned m = __match_any_sync(0xffffffffu, roams ? t : -1 - lane);
+            const int before = __popc(m & ((1u << lane) - 1u));
+            const unsigned word = roams ? s.rowcnt[t] : 0u;
+            __syncwarp();
+            if (roams && before == __popc(m) - 1) s.rowcnt[t] = word + ((unsigned)__popc(m) << 16);
+            __syncwarp();
+            if (!valid) continue;
+            int x = (int)(info & 0xffffu);                     // claimed cell, or the slot-order rank of a long group
+            if (roams) x = (int)__fns(~s.cellmask[t], 0u, (int)(word >> 16) + before + 1);
             const bool marker = !((prev[t >> 5] >> (t & 31)) & 1u);
             const long long gs = s.run[t];
-            const long long off = gs + (marker ? 4 : 0) + rank;
+            const long long off = gs + (marker ? 4 : 0) + x;
             ev[off] = a.P_rows[r * a.K + sl];
-            ec[off] = (uint16_t)(s.col[sl] | ((rank == 0 && !marker) ? 0x8000u : 0u));
-            if (rank == 0) {
+            ec[off] = (uint16_t)(s.col[sl] | ((x == 0 && !marker) ? 0x8000u : 0u));
+            if (info & kSlotLeader) {
+                const int size = ((cnt + 3) & ~3) + (marker ? 4 : 0);
                 if (marker) { ev[gs] = __int_as_float((int)lr); ec[gs] = 0xffffu; }
-                const int size = ((s.rowcnt[t] + 3) & ~3) + (marker ? 4 : 0);
-                for (long long m = (gs + kChunk - 1) / kChunk * kChunk; m < gs + size; m += kChunk)
-                    chunk_row0[m / kChunk] = (m == gs && !marker) ? (int)lr - 1 : (int)lr;
+                else if (cnt <= 32 && !(s.cellmask[t] & 1u) && cnt == __popc(s.cellmask[t])) ec[gs] = 0x8000u;   // cell 0 stays a padding entry
+                for (long long mm = (gs + kChunk - 1) / kChunk * kChunk; mm < gs + size; mm += kChunk)
+                    chunk_row0[mm / kChunk] = (mm == gs && !marker) ? (int)lr - 1 : (int)lr;
             }
         }
         __syncwarp();
@@ -414,12 +478,12 @@ __device__ __forceinline__ void emit_row(const WalkArgs &a, long long lr, WalkSc
     // group leaders close the row: advance the tile's cursor, clear the row's count
     for (int k0 = 0; k0 < a.K; k0 += 32) {
         const int sl = k0 + lane;
-        const unsigned info = (sl < a.K) ? s.slot[sl] : 0xffffffffu;
-        if (info == 0xffffffffu || (info & 0xffffu) != 0) continue;
-        const int t = info >> 16;
+        const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
+        if (info == kSlotUnused || !(info & kSlotLeader)) continue;
+        const int t = slot_tile(info);
         const bool marker = !((prev[t >> 5] >> (t & 31)) & 1u);
-        s.run[t] += ((s.rowcnt[t] + 3) & ~3) + (marker ? 4 : 0);
-        s.rowcnt[t] = 0;
+        s.run[t] += (((int)(s.rowcnt[t] & 0xffffu) + 3) & ~3) + (marker ? 4 : 0);
+        s.rowcnt[t] = 0u;
         n_groups++;
     }
     __syncwarp();
@@ -451,8 +515,8 @@ walk_kernel(WalkArgs a, unsigned *__restrict__ range_size, const unsigned *__res
         analyse_row(a, lr0 - 1, s, s.bitmap[0], lane);
         for (int k0 = 0; k0 < a.K; k0 += 32) {
             const int sl = k0 + lane;
-            const unsigned info = (sl < a.K) ? s.slot[sl] : 0xffffffffu;
-            if (info != 0xffffffffu && (info & 0xffffu) == 0) s.rowcnt[info >> 16] = 0;
+            const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
+            if (info != kSlotUnused && (info & kSlotLeader)) s.rowcnt[slot_tile(info)] = 0u;
         }
         __syncwarp();
         cur = 1;
@@ -488,10 +552,10 @@ sample_kernel(WalkArgs a, long long n_samples, unsigned long long *__restrict__ 
     unsigned groups = 0, entries = 0;
     for (int k0 = 0; k0 < a.K; k0 += 32) {
         const int sl = k0 + lane;
-        const unsigned info = (sl < a.K) ? s.slot[sl] : 0xffffffffu;
-        if (info == 0xffffffffu) continue;
+        const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
+        if (info == kSlotUnused) continue;
         entries++;
-        groups += (info & 0xffffu) == 0;
+        groups += (info & kSlotLeader) != 0;
     }
     groups = __reduce_add_sync(0xffffffffu, groups);
     entries = __reduce_add_sync(0xffffffffu, entries);
@@ -821,6 +885,12 @@ int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, floa
             sms = cached[dev];
         }
     }
+    // A block fills its SM (1,024 threads, all registers, 224 KB of shared memory), so the grid pipeline that runs
+    // beside this kernel on the other stream only gets the SMs this kernel leaves alone.  Measured at N = 10^6,
+    // K = 90 on 148 SMs: 148 blocks 3,680 iterations/s (attractive stage 196 us), 140: 3,854, 132: 3,896 (214 us),
+    // 116: 3,821.  Default: one SM in nine stays free; B200TSNE_ATTRACTIVE_BLOCKS overrides.
+    static const int want_blocks = getenv("B200TSNE_ATTRACTIVE_BLOCKS") ? atoi(getenv("B200TSNE_ATTRACTIVE_BLOCKS")) : 0;
+    sms = want_blocks > 0 ? std::min(sms, want_blocks) : sms - sms / 9;
     const int grid = std::max(1, std::min(sms, b.C));
     attractive_blocked_kernel<<<grid, kBlockedThreads, (size_t)b.T * sizeof(float2), st>>>(s, b.Yp, b.Yown, b.N, b.Fp);
     unpermute_kernel<<<(unsigned)((b.rows + 255) / 256), 256, 0, st>>>(b.Fp, b.own_pos, b.row_lo, b.rows, F2);
