@@ -90,6 +90,18 @@ void b200tsne_default_options(b200tsne_options *opt);
 int b200tsne_fit(const float *points, int64_t num_points, int num_dims, const b200tsne_options *opt,
                  float *result, float *trained_norm);
 
+/* The reference's live feed of the embedding without its socket.  The reference (built WITH_ZMQ) connects a
+ * REQ socket to its plotting server, sends the number of points as decimal text, and after every iteration
+ * sends the embedding as raw float32 (2N values, x block then y block), each time waiting for the server's
+ * reply; a send or reply that fails ends the feed, not the run (src/fit_tsne.cu:354-389, :546-561; server:
+ * visualization/vis_rt.py:8-38).  Here the same frames go to a callback: first the text frame, then one
+ * embedding frame after every `every`-th iteration (the reference: every = 1).  The callback returns 0 for
+ * "received" and anything else for "gone"; it is called on the calling thread and must not call back into the
+ * library.  A socket, a file or a plotting front end is the caller's side. */
+typedef int (*b200tsne_frame_fn)(void *user, const void *data, size_t bytes);
+int b200tsne_fit_with_frames(const float *points, int64_t num_points, int num_dims, const b200tsne_options *opt,
+                             float *result, float *trained_norm, b200tsne_frame_fn send, void *user, int every);
+
 /* ------------------------------------------------------------------------------------------- *
  * Stage entry points with host buffers (one call = upload, kernels, download).  These are what
  * the parity tests drive; `device` is the CUDA ordinal.
@@ -188,6 +200,13 @@ int b200tsne_session_affinities_from_points(b200tsne_session *s, const float *X,
 /* Set the full embedding (2N floats SoA); resets gains to 1 and momentum to 0 when reset != 0. */
 int b200tsne_session_set_embedding(b200tsne_session *s, const float *Y, int reset);
 int b200tsne_session_get_embedding(b200tsne_session *s, float *Y);
+/* Checkpoint and resume of the loop: the embedding (2N floats SoA, all points), the owned rows' momentum (the
+ * reference's old_forces) and gains (2 * rows floats SoA each; NULL = skip) and the iteration number, which
+ * selects momentum, exaggeration and the spread-order refresh.  A session restored with set_state continues
+ * as the saved one would have.  Replaces: TSNE_INIT::RESUME (src/include/options.h:24), which the reference
+ * declares for this purpose but implements as a copy of the points alone (src/fit_tsne.cu:205-217). */
+int b200tsne_session_get_state(b200tsne_session *s, float *Y, float *momentum, float *gains, int *step);
+int b200tsne_session_set_state(b200tsne_session *s, const float *Y, const float *momentum, const float *gains, int step);
 /* Download the owned rows of P / ids. */
 int b200tsne_session_get_affinities(b200tsne_session *s, float *P_rows, int32_t *ids_rows);
 /* Which attractive kernel the session's loop runs: 1 = column-blocked copy of P (built with the affinities),

@@ -39,11 +39,27 @@ namespace faiss { enum MetricType { METRIC_INNER_PRODUCT = 0, METRIC_L2 = 1, MET
 """
 
 
+def stage_python_wrapper(ref):
+    """Put the reference's own Python package (src/python/tsnecuda: __init__.py, TSNE.py) under
+    oracle/_ref/python/, unmodified, so that the drop-in test can import it next to this repository's
+    libtsnecuda.so on a machine that has no reference tree.  Build output like the .so: never committed."""
+    import shutil
+    pkg = os.path.join(ref, "src", "python", "tsnecuda")
+    if not os.path.isdir(pkg):
+        return None
+    dst = os.path.join(OUT, "python", "tsnecuda")
+    os.makedirs(dst, exist_ok=True)
+    for name in ("__init__.py", "TSNE.py"):
+        shutil.copyfile(os.path.join(pkg, name), os.path.join(dst, name))
+    return dst
+
+
 def build(force=False, reference_root=None):
     ref = reference_root or find_reference_root()
     src = os.path.join(ref, "src")
     if not os.path.isdir(src):
         return LIB if os.path.exists(LIB) else None
+    stage_python_wrapper(ref)
     own = [os.path.join(HERE, "knn_shim.cu"), os.path.join(HERE, "ref_harness.cu")]
     theirs = sorted(glob.glob(os.path.join(src, "kernels", "*.cu")) + glob.glob(os.path.join(src, "util", "*.cu")) +
                     glob.glob(os.path.join(src, "ext", "*.cu")) + [os.path.join(src, "fit_tsne.cu")])

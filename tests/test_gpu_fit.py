@@ -99,6 +99,46 @@ def test_chunked_run_equals_single_run_in_quality(engine, oracle_cpu, golden):
     assert abs(kl[0] - kl[1]) / kl[0] < 0.02
 
 
+def test_checkpoint_and_resume_continue_the_same_run(engine, oracle_cpu, golden):
+    """run(300) against run(100) + get_state / new session / set_state + run(200): the state that crosses is
+    (Y, momentum, gains, step).  One iteration after the restore is compared directly (same inputs, so the
+    same forces up to the spread's reduction order); the finished runs by their KL.  A restore that dropped
+    gains or momentum, or restarted the schedule at step 0, fails both."""
+    P, ids, Y0 = golden["P"], golden["ids"], golden["Y_a"]
+    N, K = P.shape
+
+    def session():
+        s = engine.Session(N, K)
+        s.set_affinities(P, ids)
+        s.set_schedule(200.0, 12.0, 150, 0.5, 0.8)
+        return s
+
+    with session() as s:
+        s.set_embedding(Y0)
+        s.run(100)
+        Y, mom, gains, step = s.get_state()
+        assert step == 100 and np.abs(mom).max() > 0 and gains.max() > 1.0
+        s.run(1)
+        Y_next = s.get_embedding()
+        s.run(199)
+        kl_through = oracle_cpu.kl_divergence(P, ids, s.get_embedding())
+    with session() as s:
+        s.set_state(Y, mom, gains, step)
+        assert s.stats()["step"] == 100
+        Y2, mom2, gains2, _ = s.get_state()
+        assert np.array_equal(Y2, Y) and np.array_equal(mom2, mom) and np.array_equal(gains2, gains)
+        s.run(1)
+        assert rel_l2(s.get_embedding(), Y_next) < 1e-5
+        s.run(199)
+        assert s.stats()["step"] == 300
+        kl_resumed = oracle_cpu.kl_divergence(P, ids, s.get_embedding())
+    with session() as s:                       # what a restore without the optimiser state gives: clearly different
+        s.set_embedding(Y)
+        s.run(1)
+        assert rel_l2(s.get_embedding(), Y_next) > 1e-3
+    assert abs(kl_resumed - kl_through) / kl_through < 0.035
+
+
 def test_min_gradient_norm_stops_early(engine, golden):
     P, ids, Y0 = golden["P"], golden["ids"], golden["Y_a"]
     with engine.Session(*P.shape) as s:
@@ -137,16 +177,20 @@ def test_drop_in_fit_transform(engine, oracle_cpu):
 
 
 def test_fit_vs_live_reference(engine, oracle_cpu):
+    """End to end against the reference's own CUDA build on the same X, neighbour list and Y0, at a size where
+    the run-to-run scatter of the two engines' unordered reductions is below the bars (20 000 points: measured
+    spread of KL 0.2 %, of 10-NN preservation 0.3 points, for either engine).  Bars: final KL within 1 % for
+    EVERY pair of runs, 10-NN preservation within 0.5 points between the medians and 0.75 for every pair."""
     from oracle import ref
     if not ref.available():
         pytest.skip("oracle/_ref/libtsnecuda_ref.so was not built (needs the reference tree)")
     from tsne_cuda_b200 import TSNE
-    X = mixture(4000, 50, 5)
-    K = 90
-    Y0 = (1e-4 * np.random.default_rng(2).standard_normal((2, 4000))).astype(np.float32)
+    n, K = 20000, 90
+    X = mixture(n, 50, 5)
+    Y0 = (1e-4 * np.random.default_rng(2).standard_normal((2, n))).astype(np.float32)
     ids, d2 = engine.knn(X, K)
     ids_o, P = oracle_cpu.affinities(X, K, 30.0, 1e-3)
-    # both engines reduce with unordered atomics and scatter from run to run: medians of three runs each
+    assert np.array_equal(ids, ids_o)
     kl_r, kl_m, n_r, n_m = [], [], [], []
     ref.set_knn(ids, d2)
     for _ in range(3):
@@ -159,9 +203,13 @@ def test_fit_vs_live_reference(engine, oracle_cpu):
         Ym = np.ascontiguousarray(Ym.T)
         kl_m.append(oracle_cpu.kl_divergence(P, ids_o, Ym))
         n_m.append(oracle_cpu.nn_preservation(ids_o, Ym, 10))
-    kl_r, kl_m, n_r, n_m = (float(np.median(v)) for v in (kl_r, kl_m, n_r, n_m))
-    assert abs(kl_m - kl_r) / kl_r < 0.01, (kl_m, kl_r)
-    assert abs(n_m - n_r) < 0.005 + 0.01, (n_m, n_r)
+    for a in kl_m:
+        for b in kl_r:
+            assert abs(a - b) / b < 0.01, (kl_m, kl_r)
+    assert abs(np.median(n_m) - np.median(n_r)) < 0.005, (n_m, n_r)
+    for a in n_m:
+        for b in n_r:
+            assert abs(a - b) < 0.0075, (n_m, n_r)
 
 
 def test_library_drawn_initial_embedding_equals_the_reference(engine):
@@ -201,6 +249,33 @@ def test_snapshots_dump_and_errors(engine, tmp_path, capfd):
     Y, Z = engine.fit(X, iterations=30, num_neighbors=30, perplexity=10.0, verbosity=1, print_interval=10)
     out = capfd.readouterr().out
     assert "_time_knn:" in out and "[Step 20] Avg. Gradient Norm:" in out and "total_time:" in out and Z > 0
+
+
+def test_frame_feed_has_the_reference_wire_format(engine):
+    """The live feed without a socket: a text frame with the number of points, then raw float32 frames of 2N values
+    (x block, y block) after every iteration, as the reference's REQ/REP publisher sends them
+    (src/fit_tsne.cu:354-389, :546-561; the server reads them with int(...) and fromstring(..., 'float32', 2N):
+    visualization/vis_rt.py:14-23).  The last frame is the returned embedding; a receiver that goes away ends
+    the feed and not the run."""
+    X = mixture(600, 10, 2)
+    frames = []
+    Y, Z = engine.fit_with_frames(X, lambda b: frames.append(b), every=1, iterations=12, num_neighbors=30, perplexity=10.0,
+                                  random_seed=3)
+    assert int(frames[0]) == 600
+    assert len(frames) == 1 + 12 and all(len(f) == 600 * 2 * 4 for f in frames[1:])
+    data = [np.frombuffer(f, np.float32).reshape(2, 600) for f in frames[1:]]
+    assert np.array_equal(data[-1], Y) and not np.array_equal(data[0], data[-1]) and np.isfinite(data[0]).all()
+    # every third iteration; the receiver leaves after two embedding frames
+    frames = []
+
+    def leave_early(b):
+        frames.append(b)
+        return len(frames) < 3
+
+    Y2, _ = engine.fit_with_frames(X, leave_early, every=3, iterations=12, num_neighbors=30, perplexity=10.0, random_seed=3)
+    assert len(frames) == 3 and np.isfinite(Y2).all()
+    # same seed, same run whatever the feed does (up to the spread's reduction order)
+    assert rel_l2(Y2, Y) < 1e-3
 
 
 def test_full_size_properties_one_million_points(engine, oracle_cpu):

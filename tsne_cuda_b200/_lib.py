@@ -44,6 +44,7 @@ SIGNATURES = {
     "pymodule_tsne": (None, None),  # bound by TSNE.py with the reference's own argtypes
     "b200tsne_default_options": (None, [C.POINTER(Options)]),
     "b200tsne_fit": (C.c_int, [_fp, _i64, C.c_int, C.POINTER(Options), _fp, _fp]),
+    "b200tsne_fit_with_frames": (C.c_int, [_fp, _i64, C.c_int, C.POINTER(Options), _fp, _fp, C.c_void_p, C.c_void_p, C.c_int]),
     "b200tsne_knn": (C.c_int, [_fp, _i64, C.c_int, C.c_int, _i64, _i64, _i64, _i64, _ip, _fp, C.c_int]),
     "b200tsne_knn_last_stats": (C.c_int, [C.POINTER(C.c_int), C.POINTER(C.c_int), _fp]),
     "b200tsne_knn_noalloc": (C.c_int, [C.c_void_p, _i64, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
@@ -62,6 +63,8 @@ SIGNATURES = {
     "b200tsne_session_set_embedding": (C.c_int, [C.c_void_p, _fp, C.c_int]),
     "b200tsne_session_get_embedding": (C.c_int, [C.c_void_p, _fp]),
     "b200tsne_session_get_affinities": (C.c_int, [C.c_void_p, _fp, _ip]),
+    "b200tsne_session_get_state": (C.c_int, [C.c_void_p, _fp, _fp, _fp, C.POINTER(C.c_int)]),
+    "b200tsne_session_set_state": (C.c_int, [C.c_void_p, _fp, _fp, _fp, C.c_int]),
     "b200tsne_session_set_schedule": (C.c_int, [C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_float, C.c_float]),
     "b200tsne_session_run": (C.c_int, [C.c_void_p, C.c_int, C.c_float, _fp, C.POINTER(C.c_int)]),
     "b200tsne_session_stats": (C.c_int, [C.c_void_p, _fp, _fp, C.POINTER(C.c_int)]),
@@ -214,6 +217,37 @@ def fit(X, **kw):
     return (Y[0] if blocks <= 1 else Y), Z.value
 
 
+FRAME_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_size_t)
+
+
+def fit_with_frames(X, on_frame, every=1, **kw):
+    """b200tsne_fit_with_frames: on_frame(bytes) is called with the text frame (number of points) and then with
+    one raw float32 frame (2N values) after every `every`-th iteration; it returns True/None to go on, False for
+    "gone".  Returns (Y (2,N) SoA, Z)."""
+    X = _c(X, np.float32)
+    N, D = X.shape
+    o = Options()
+    lib.b200tsne_default_options(C.byref(o))
+    keep = []
+    for k, v in kw.items():
+        if k == "preinit_data":
+            v = _c(v, np.float32)
+            keep.append(v)
+            o.preinit_data = _f(v)
+        else:
+            setattr(o, k, v)
+
+    def trampoline(user, data, nbytes):
+        ok = on_frame(C.string_at(data, nbytes))
+        return 0 if (ok is None or ok) else 1
+
+    cb = FRAME_FN(trampoline)
+    Y = np.zeros((2, N), np.float32)
+    Z = C.c_float()
+    check(lib.b200tsne_fit_with_frames(_f(X), N, D, C.byref(o), _f(Y), C.byref(Z), C.cast(cb, C.c_void_p), None, int(every)))
+    return Y, Z.value
+
+
 # ---- device-resident session -------------------------------------------------------------------
 class Session(object):
     """The gradient loop with everything resident in HBM (b200tsne_session_*)."""
@@ -265,6 +299,20 @@ class Session(object):
         Y = np.empty((2, self.N), np.float32)
         check(lib.b200tsne_session_get_embedding(self._h, _f(Y)))
         return Y
+
+    def get_state(self):
+        """(Y (2,N), momentum (2,rows), gains (2,rows), step): everything a later session needs to continue."""
+        r = self.row_hi - self.row_lo
+        Y = np.empty((2, self.N), np.float32)
+        mom = np.empty((2, r), np.float32)
+        gains = np.empty((2, r), np.float32)
+        step = C.c_int()
+        check(lib.b200tsne_session_get_state(self._h, _f(Y), _f(mom), _f(gains), C.byref(step)))
+        return Y, mom, gains, step.value
+
+    def set_state(self, Y, momentum, gains, step):
+        Y, momentum, gains = _c(Y, np.float32), _c(momentum, np.float32), _c(gains, np.float32)
+        check(lib.b200tsne_session_set_state(self._h, _f(Y), _f(momentum), _f(gains), int(step)))
 
     def set_schedule(self, learning_rate=200.0, early_exaggeration=12.0, force_magnify_iters=250,
                      pre_momentum=0.5, post_momentum=0.8):

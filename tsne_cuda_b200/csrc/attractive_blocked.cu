@@ -17,9 +17,12 @@
 //     its 32 row numbers with one ballot and a population count.
 //   * A block owns a contiguous 1/gridDim of the stream, loads the tile(s) it crosses, and its warps walk
 //     chunks: gather from shared memory, evaluate p / (1 + d^2) * (y_i - y_j), reduce the lanes of a row
-//     with shuffles, and add the row's partial force with one 8-byte reduction per (row, tile).
-//   * The loop is software-pipelined in registers (stream loads two chunks ahead, the row's own coordinate
-//     one chunk ahead): with 32 warps per SM and one block per SM nothing else hides the latency.
+//     with shuffles, and add the partial force with an 8-byte reduction.  The lanes of a group are cut into
+//     runs of at most four (never across a chunk) when the stream is built, and bit 15 of a lane's other
+//     three columns says "a run starts here", "add the next lane", "add the lane after": two shuffle steps
+//     without any control flow, one reduction per run.
+//   * With one block of 32 warps per SM the kernel lives on what the set-up precomputes (about 110 instructions per
+//     chunk of 128 entries) and on stream loads that run one chunk ahead in registers.
 //
 // Arithmetic per entry is that of the reference's ComputePijxQijKernelV3 (src/kernels/attr_forces.cu:129-184);
 // only the order of the additions differs (and varies from run to run in the last bits, as the sums of
@@ -337,16 +340,12 @@ constexpr int kWalkWarps = 2;
 constexpr int kMaxK = 1024;
 struct WalkScratch {
     long long run[kMaxTiles];      // count pass: entries this range adds to the tile; fill pass: next free entry of the tile
-    unsigned rowcnt[kMaxTiles];    // low half: entries of the current row in the tile; high half: cells handed out in phase 2 of the fill
-    unsigned cellmask[kMaxTiles];  // fill pass: cells of the current (row, tile) group claimed in phase 1
-    unsigned slot[kMaxK];          // per slot of the current row, see kSlot*; 0xffffffff = unused slot
+    int rowcnt[kMaxTiles];         // entries of the current row per tile
+    unsigned slot[kMaxK];          // per slot of the current row: tile << 16 | rank inside (row, tile) in slot order; 0xffffffff = unused slot
     unsigned short col[kMaxK];     // per slot: column inside the tile
     unsigned bitmap[2][32];        // tiles touched by the previous / the current row
 };
-// slot word: bits 16..25 tile, bit 30 first slot of its (row, tile) group, bit 29 cell claimed in phase 1,
-// low 16 bits: rank inside the group in slot order, later the cell
-constexpr unsigned kSlotLeader = 1u << 30, kSlotClaimed = 1u << 29, kSlotUnused = 0xffffffffu;
-__device__ __forceinline__ int slot_tile(unsigned info) { return (info >> 16) & 0x3ffu; }
+constexpr unsigned kSlotUnused = 0xffffffffu;
 
 struct WalkArgs {
     const float *P_rows;           // [rows][K]
@@ -374,7 +373,7 @@ __device__ __forceinline__ void analyse_row(const WalkArgs &a, long long lr, Wal
         }
         const unsigned m = __match_any_sync(0xffffffffu, t);
         const int before = __popc(m & ((1u << lane) - 1u));
-        const unsigned base = valid ? s.rowcnt[t] : 0u;
+        const int base = valid ? s.rowcnt[t] : 0;
         __syncwarp();
         if (valid) {
             if (before == __popc(m) - 1) s.rowcnt[t] = base + __popc(m);
@@ -382,28 +381,25 @@ __device__ __forceinline__ void analyse_row(const WalkArgs &a, long long lr, Wal
         }
         __syncwarp();
         if (sl < a.K) {
-            s.slot[sl] = valid ? (((unsigned)t << 16) | (base + before) | ((base + before) == 0 ? kSlotLeader : 0u)) : kSlotUnused;
+            s.slot[sl] = valid ? (((unsigned)t << 16) | (unsigned)(base + before)) : kSlotUnused;
             s.col[sl] = (unsigned short)c;
         }
     }
     __syncwarp();
 }
 
-// Entries of a group may stand in any order.  The kernel's k-th gather of a warp reads the k-th entry of all 32
-// lanes, 16 lanes per shared-memory pass, and a pass costs as many cycles as the most loaded pair of banks;
-// a float2 at column c lies in bank pair c mod 16.  So every cell (lane h of its half warp, entry k) of the
-// stream has a preferred bank pair (h + 4k) mod 16 - distinct for the 16 lanes of a pass - and a group
-// first gives its entries the cells that prefer their bank pairs (phase 1, at most one entry per cell), then
-// hands the remaining cells to the remaining entries in slot order (phase 2).  Groups of more than 32 entries
-// keep the slot order.
-__device__ __forceinline__ int preferred_cell(int bank_pair, int lane0, int n_lanes, int attempt)
-{
-    const int delta = (bank_pair - lane0) & 15;      // = l + 4k (mod 16) for cell (lane l of the group, entry k)
-    const int l = (delta & 3) + 4 * attempt;
-    if (l >= n_lanes) return -1;
-    const int k = ((delta - l) & 15) >> 2;
-    return 4 * l + k;
-}
+// Geometry of a group in the stream.  Its lanes (a marker lane first, if any, then ceil(cnt / 4) lanes of entries)
+// are cut into runs of at most four lanes that never cross a chunk; the kernel reduces a run with two shuffle
+// steps and its first lane adds the sum to the row's force.
+struct GroupGeom {
+    long long lane0;     // absolute lane (= entry offset / 4) of the group's first lane
+    int n_lanes;
+    __device__ bool start(int i) const { return (i & 3) == 0 || ((lane0 + i) & 31) == 0; }
+    __device__ bool take1(int i) const { return i + 1 < n_lanes && !start(i + 1); }
+    __device__ bool take2(int i) const { return i + 2 < n_lanes && !start(i + 1) && !start(i + 2); }
+    // bit 15 of entry k of lane i (k = 0 is the row bit, set by the caller)
+    __device__ unsigned flag(int i, int k) const { return ((k == 1 && start(i)) || (k == 2 && take1(i)) || (k == 3 && take2(i))) ? 0x8000u : 0u; }
+};
 
 // FILL = false: add the row's groups to run[] (sizes) and count them.  FILL = true: write the row's entries.
 template <bool FILL>
@@ -413,64 +409,33 @@ __device__ __forceinline__ void emit_row(const WalkArgs &a, long long lr, WalkSc
 {
     const long long r = (long long)a.own_perm[lr] - a.row_lo;
     if (FILL) {
-        // phase 0: no cell of the row's groups is taken
         for (int k0 = 0; k0 < a.K; k0 += 32) {
             const int sl = k0 + lane;
             const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
-            if (info != kSlotUnused && (info & kSlotLeader)) s.cellmask[slot_tile(info)] = 0u;
-        }
-        __syncwarp();
-        // phase 1: claim the preferred cell
-        for (int k0 = 0; k0 < a.K; k0 += 32) {
-            const int sl = k0 + lane;
-            unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
             if (info == kSlotUnused) continue;
-            const int t = slot_tile(info);
-            const int cnt = (int)(s.rowcnt[t] & 0xffffu);
-            if (cnt > 32) continue;
-            const bool marker = !((prev[t >> 5] >> (t & 31)) & 1u);
-            const int lane0 = (int)(((s.run[t] >> 2) + (marker ? 1 : 0)) & 15);
-            const int n_lanes = (cnt + 3) >> 2;
-            for (int attempt = 0; attempt < 2; attempt++) {
-                const int x = preferred_cell(s.col[sl] & 15, lane0, n_lanes, attempt);
-                if (x < 0) break;
-                const unsigned old = atomicOr(&s.cellmask[t], 1u << x);
-                if (!((old >> x) & 1u)) {
-                    info = (info & 0xffff0000u) | kSlotClaimed | (unsigned)x;
-                    s.slot[sl] = info;
-                    break;
-                }
-            }
-        }
-        __syncwarp();
-        // phase 2: the other entries take the free cells in slot order; then every entry is written
-        for (int k0 = 0; k0 < a.K; k0 += 32) {
-            const int sl = k0 + lane;
-            const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
-            const bool valid = info != kSlotUnused;
-            const int t = valid ? slot_tile(info) : 0;
-            const int cnt = valid ? (int)(s.rowcnt[t] & 0xffffu) : 0;
-            const bool roams = valid && cnt <= 32 && !(info & kSlotClaimed);
-            const unsigned m = __match_any_sync(0xffffffffu, roams ? t : -1 - lane);
-            const int before = __popc(m & ((1u << lane) - 1u));
-            const unsigned word = roams ? s.rowcnt[t] : 0u;
-            __syncwarp();
-            if (roams && before == __popc(m) - 1) s.rowcnt[t] = word + ((unsigned)__popc(m) << 16);
-            __syncwarp();
-            if (!valid) continue;
-            int x = (int)(info & 0xffffu);                     // claimed cell, or the slot-order rank of a long group
-            if (roams) x = (int)__fns(~s.cellmask[t], 0u, (int)(word >> 16) + before + 1);
-            const bool marker = !((prev[t >> 5] >> (t & 31)) & 1u);
+            const int t = info >> 16, x = info & 0xffffu;
+            const int cnt = s.rowcnt[t];
+            const int marker = ((prev[t >> 5] >> (t & 31)) & 1u) ? 0 : 1;
             const long long gs = s.run[t];
-            const long long off = gs + (marker ? 4 : 0) + x;
+            GroupGeom g;
+            g.lane0 = gs >> 2;
+            g.n_lanes = marker + ((cnt + 3) >> 2);
+            const int i = marker + (x >> 2), k = x & 3;
+            const long long off = gs + 4 * marker + x;
             ev[off] = a.P_rows[r * a.K + sl];
-            ec[off] = (uint16_t)(s.col[sl] | ((x == 0 && !marker) ? 0x8000u : 0u));
-            if (info & kSlotLeader) {
-                const int size = ((cnt + 3) & ~3) + (marker ? 4 : 0);
-                if (marker) { ev[gs] = __int_as_float((int)lr); ec[gs] = 0xffffu; }
-                else if (cnt <= 32 && !(s.cellmask[t] & 1u) && cnt == __popc(s.cellmask[t])) ec[gs] = 0x8000u;   // cell 0 stays a padding entry
+            ec[off] = (uint16_t)(s.col[sl] | (k == 0 ? ((x == 0 && !marker) ? 0x8000u : 0u) : g.flag(i, k)));
+            if (x == 0) {   // the group's first slot also writes what no slot owns
+                if (marker) {
+                    ev[gs] = __int_as_float((int)lr);
+                    ec[gs] = 0xffffu;
+                    for (int kk = 1; kk < 4; kk++) ec[gs + kk] = (uint16_t)g.flag(0, kk);
+                    atomicOr(reinterpret_cast<unsigned *>(chunk_row0) + gs / kChunk, 0x80000000u);   // "this chunk holds a marker"
+                }
+                const int last = g.n_lanes - 1;                    // padding entries of the last lane carry its flags
+                for (int kk = max(1, cnt & 3 ? cnt & 3 : 4); kk < 4; kk++) ec[gs + 4 * last + kk] = (uint16_t)g.flag(last, kk);
+                const int size = 4 * g.n_lanes;
                 for (long long mm = (gs + kChunk - 1) / kChunk * kChunk; mm < gs + size; mm += kChunk)
-                    chunk_row0[mm / kChunk] = (mm == gs && !marker) ? (int)lr - 1 : (int)lr;
+                    atomicOr(reinterpret_cast<unsigned *>(chunk_row0) + mm / kChunk, (unsigned)((mm == gs && !marker) ? (int)lr - 1 : (int)lr));
             }
         }
         __syncwarp();
@@ -479,11 +444,11 @@ __device__ __forceinline__ void emit_row(const WalkArgs &a, long long lr, WalkSc
     for (int k0 = 0; k0 < a.K; k0 += 32) {
         const int sl = k0 + lane;
         const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
-        if (info == kSlotUnused || !(info & kSlotLeader)) continue;
-        const int t = slot_tile(info);
-        const bool marker = !((prev[t >> 5] >> (t & 31)) & 1u);
-        s.run[t] += (((int)(s.rowcnt[t] & 0xffffu) + 3) & ~3) + (marker ? 4 : 0);
-        s.rowcnt[t] = 0u;
+        if (info == kSlotUnused || (info & 0xffffu) != 0) continue;
+        const int t = info >> 16;
+        const int marker = ((prev[t >> 5] >> (t & 31)) & 1u) ? 0 : 1;
+        s.run[t] += ((s.rowcnt[t] + 3) & ~3) + 4 * marker;
+        s.rowcnt[t] = 0;
         n_groups++;
     }
     __syncwarp();
@@ -516,7 +481,7 @@ walk_kernel(WalkArgs a, unsigned *__restrict__ range_size, const unsigned *__res
         for (int k0 = 0; k0 < a.K; k0 += 32) {
             const int sl = k0 + lane;
             const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
-            if (info != kSlotUnused && (info & kSlotLeader)) s.rowcnt[slot_tile(info)] = 0u;
+            if (info != kSlotUnused && (info & 0xffffu) == 0) s.rowcnt[info >> 16] = 0;
         }
         __syncwarp();
         cur = 1;
@@ -555,7 +520,7 @@ sample_kernel(WalkArgs a, long long n_samples, unsigned long long *__restrict__ 
         const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
         if (info == kSlotUnused) continue;
         entries++;
-        groups += (info & kSlotLeader) != 0;
+        groups += (info & 0xffffu) == 0;
     }
     groups = __reduce_add_sync(0xffffffffu, groups);
     entries = __reduce_add_sync(0xffffffffu, entries);
@@ -641,68 +606,82 @@ unpermute_kernel(const float2 *__restrict__ Fp, const int32_t *__restrict__ own_
     if (r < rows) F2[row_lo + r] = Fp[own_pos[r]];
 }
 
-struct ChunkRegs {
-    float4 p;
-    uint2 c;
-    int row0;
-};
-__device__ __forceinline__ ChunkRegs load_chunk(const BlockedStream &b, int cc, int lane)
-{
-    ChunkRegs r;
-    r.p = __ldcs(reinterpret_cast<const float4 *>(b.ev) + (size_t)cc * 32 + lane);
-    r.c = __ldcs(reinterpret_cast<const uint2 *>(b.ec) + (size_t)cc * 32 + lane);
-    r.row0 = __ldg(b.chunk_row0 + cc);
-    return r;
-}
-
 __device__ __forceinline__ void add_entry(float2 yi, float2 yj, float p, float &ox, float &oy)
 {
     const float dx = yi.x - yj.x, dy = yi.y - yj.y;
-    const float pq = __fdividef(p, 1.0f + dx * dx + dy * dy);
+    const float pq = __fdividef(p, fmaf(dy, dy, fmaf(dx, dx, 1.0f)));
     ox = fmaf(pq, dx, ox);
     oy = fmaf(pq, dy, oy);
 }
-
-__device__ __forceinline__ void process_chunk(const ChunkRegs &R, const float2 *__restrict__ tile, const float2 *__restrict__ Yown,
-                                              float2 *__restrict__ Fp, int lane)
+__device__ __forceinline__ float2 tile_at(const float2 *tile, unsigned byte_offset)
 {
-    const unsigned e0 = R.c.x & 0xffffu, e1 = R.c.x >> 16, e2 = R.c.y & 0xffffu, e3 = R.c.y >> 16;
-    const bool head = e0 >> 15;
-    const bool marker = e0 == 0xffffu;
+    return *reinterpret_cast<const float2 *>(reinterpret_cast<const char *>(tile) + byte_offset);
+}
+
+// A chunk in a warp's registers: the stream loads are issued one round before the chunk is processed; then the
+// lane's row is found (it takes the place of row0), the row's own coordinate fetched, and the forces evaluated.
+// Measured alternatives, all slower on B200 at N = 10^6, K = 90 (attractive stage of the iteration, 148 blocks):
+// as below 190 us; two register sets in turn instead of the copy 212 us; stream loads two rounds ahead 218 us;
+// rows and own coordinates a round ahead as well (three sets) 247 us; an additional L2 prefetch six rounds ahead
+// changes nothing; 768 threads with 79 registers 241 us.
+struct ChunkSet {
+    float4 p;
+    uint2 c;
+    int r;        // after stage A: the chunk's row0 word; after stage B: this lane's row
+    float2 yi;
+};
+// The stream is read once: its loads do not take lines of the (small, beside 224 KB of shared memory) L1.
+__device__ __forceinline__ void stage_load(ChunkSet &s, const BlockedStream &b, int cc, int lane)
+{
+    const float4 *pv = reinterpret_cast<const float4 *>(b.ev) + (size_t)cc * 32 + lane;
+    const uint2 *pc = reinterpret_cast<const uint2 *>(b.ec) + (size_t)cc * 32 + lane;
+    asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(s.p.x), "=f"(s.p.y), "=f"(s.p.z), "=f"(s.p.w) : "l"(pv));
+    asm volatile("ld.global.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(s.c.x), "=r"(s.c.y) : "l"(pc));
+    s.r = __ldg(b.chunk_row0 + cc);
+}
+
+__device__ __forceinline__ void stage_rows(ChunkSet &w, const float2 *__restrict__ Yown, int lane)
+{
+    const bool head = w.c.x & 0x8000u;
     const unsigned hm = __ballot_sync(0xffffffffu, head);
-    int r;
-    if (!__any_sync(0xffffffffu, marker)) {
-        r = R.row0 + __popc(hm & (0xffffffffu >> (31 - lane)));
+    if (w.r >= 0) {
+        w.r += __popc(hm & (0xffffffffu >> (31 - lane)));
     } else {
-        // rows as a scan over (absolute row set by a marker, heads since)
-        int s = marker ? __float_as_int(R.p.x) : INT_MIN, n = (head && !marker) ? 1 : 0;
+        // a marker lane (first word 0xffff) sets the row to the number its first value holds; rows are then a
+        // scan over (row set by a marker, heads since)
+        const bool marker = (w.c.x & 0xffffu) == 0xffffu;
+        int s = marker ? __float_as_int(w.p.x) : INT_MIN, n = (head && !marker) ? 1 : 0;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             const int sa = __shfl_up_sync(0xffffffffu, s, d), na = __shfl_up_sync(0xffffffffu, n, d);
             if (lane >= d && s == INT_MIN) { s = sa; n += na; }
         }
-        r = (s == INT_MIN ? R.row0 : s) + n;
+        w.r = (s == INT_MIN ? (w.r & 0x7fffffff) : s) + n;
+        if (marker) { w.p.x = 0.0f; w.c.x &= 0xffff0000u; }   // from here on an entry of value 0 at column 0
     }
-    const float2 yi = __ldg(Yown + r);
-    const float2 yj0 = tile[marker ? 0u : (e0 & 0x7fffu)], yj1 = tile[e1], yj2 = tile[e2], yj3 = tile[e3];
+    w.yi = __ldg(Yown + w.r);
+}
+
+__device__ __forceinline__ void stage_forces(const ChunkSet &w, const float2 *__restrict__ tile, float2 *__restrict__ Fp)
+{
+    // byte offsets of the four columns in the tile
+    const float2 yj0 = tile_at(tile, (w.c.x << 3) & 0x3fff8u), yj1 = tile_at(tile, (w.c.x >> 13) & 0x3fff8u);
+    const float2 yj2 = tile_at(tile, (w.c.y << 3) & 0x3fff8u), yj3 = tile_at(tile, (w.c.y >> 13) & 0x3fff8u);
     float ox = 0.0f, oy = 0.0f;
-    add_entry(yi, yj0, marker ? 0.0f : R.p.x, ox, oy);
-    add_entry(yi, yj1, R.p.y, ox, oy);
-    add_entry(yi, yj2, R.p.z, ox, oy);
-    add_entry(yi, yj3, R.p.w, ox, oy);
-    // lanes of one row are neighbours: a run starts at lane 0 and at every head
-    const unsigned starts = hm | 1u;
-    const unsigned above = (lane == 31) ? 0u : (starts & (0xffffffffu << (lane + 1)));
-    const int run_end = above ? (__ffs(above) - 2) : 31;
-    const bool is_start = (starts >> lane) & 1u;
-    const int maxlen = __reduce_max_sync(0xffffffffu, is_start ? run_end - lane : 0);
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        if (d > maxlen) break;
-        const float tx = __shfl_down_sync(0xffffffffu, ox, d), ty = __shfl_down_sync(0xffffffffu, oy, d);
-        if (lane + d <= run_end) { ox += tx; oy += ty; }
+    add_entry(w.yi, yj0, w.p.x, ox, oy);
+    add_entry(w.yi, yj1, w.p.y, ox, oy);
+    add_entry(w.yi, yj2, w.p.z, ox, oy);
+    add_entry(w.yi, yj3, w.p.w, ox, oy);
+    // runs of at most four lanes: two steps, the flags say which lanes add
+    {
+        const float tx = __shfl_down_sync(0xffffffffu, ox, 1), ty = __shfl_down_sync(0xffffffffu, oy, 1);
+        if (w.c.y & 0x8000u) { ox += tx; oy += ty; }
     }
-    if (is_start) atomicAdd(Fp + r, make_float2(ox, oy));
+    {
+        const float tx = __shfl_down_sync(0xffffffffu, ox, 2), ty = __shfl_down_sync(0xffffffffu, oy, 2);
+        if (w.c.y & 0x80000000u) { ox += tx; oy += ty; }
+    }
+    if (w.c.x & 0x80000000u) atomicAdd(Fp + w.r, make_float2(ox, oy));
 }
 
 __global__ void __launch_bounds__(kBlockedThreads, 1)
@@ -724,7 +703,9 @@ attractive_blocked_kernel(BlockedStream b, const float2 *__restrict__ Yp, const 
         t = lo;
     }
     int c = c_lo, cc = c_lo + warp;
-    ChunkRegs next = load_chunk(b, min(cc, b.C - 1), lane);
+    const int last = b.C - 1;
+    ChunkSet next;   // the stream of the chunk this warp processes in the next round
+    stage_load(next, b, min(cc, last), lane);
     while (c < c_hi) {
         while (b.tile_chunk0[t + 1] <= c) t++;
         const int c_end = min(c_hi, b.tile_chunk0[t + 1]);
@@ -740,9 +721,10 @@ attractive_blocked_kernel(BlockedStream b, const float2 *__restrict__ Yp, const 
         }
         __syncthreads();
         for (; cc < c_end; cc += nwarps) {
-            const ChunkRegs cur = next;
-            next = load_chunk(b, min(cc + nwarps, b.C - 1), lane);
-            process_chunk(cur, tile, Yown, Fp, lane);
+            ChunkSet cur = next;
+            stage_load(next, b, min(cc + nwarps, last), lane);
+            stage_rows(cur, Yown, lane);
+            stage_forces(cur, tile, Fp);
         }
         c = c_end;
     }

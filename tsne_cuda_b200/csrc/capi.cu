@@ -373,6 +373,29 @@ int b200tsne_session_get_embedding(b200tsne_session *h, float *Y)
     return h->s.get_embedding_soa(Y);
 }
 
+int b200tsne_session_get_state(b200tsne_session *h, float *Y, float *momentum, float *gains, int *step)
+{
+    if (!h) { set_error("session_get_state: null session"); return B200TSNE_ERR_INVALID; }
+    if (Y) B200_TRY(h->s.get_embedding_soa(Y));
+    B200_TRY(h->s.get_optimizer_soa(momentum, gains));
+    if (step) *step = h->s.step;
+    return 0;
+}
+
+int b200tsne_session_set_state(b200tsne_session *h, const float *Y, const float *momentum, const float *gains, int step)
+{
+    if (!h || !Y || step < 0) { set_error("session_set_state: invalid arguments"); return B200TSNE_ERR_INVALID; }
+    Session &s = h->s;
+    if (s.comm && s.comm->world > 1 && ((step ^ s.step) & 1)) {
+        // the exchange buffers alternate with the iteration's parity, alike on all ranks
+        set_error("session_set_state: in a sharded session the step must keep the parity of the current step");
+        return B200TSNE_ERR_UNSUPPORTED;
+    }
+    s.step = step;                       // set_embedding prepares the min/max slot of this step
+    B200_TRY(s.set_embedding_soa(Y, false));
+    return s.set_optimizer_soa(momentum, gains);
+}
+
 int b200tsne_session_set_schedule(b200tsne_session *h, float learning_rate, float early_exaggeration,
                                   int force_magnify_iters, float pre_momentum, float post_momentum)
 {

@@ -40,6 +40,15 @@ GpuOptions::GpuOptions(int device_) : device(device_)
 }
 
 namespace {
+// Where the embedding goes while the loop runs (the reference's live visualisation feed, src/fit_tsne.cu:354-389 and
+// :546-561, without the socket): set for the calling thread by b200tsne_fit_with_frames around one run.
+struct FrameSink {
+    int (*send)(void *user, const void *data, size_t bytes) = nullptr;
+    void *user = nullptr;
+    int every = 1;
+};
+thread_local FrameSink g_frames;
+
 struct PhaseTimer {
     std::chrono::high_resolution_clock::time_point t0 = std::chrono::high_resolution_clock::now();
     double lap()
@@ -142,9 +151,22 @@ int run(Options &opt, GpuOptions &gpu_opt)
         host_ys.resize((size_t)N * 2);
         dump_file << N << " " << 2 << std::endl;
     }
-    if (opt.get_use_interactive())
+    // The reference's feed: first the number of points as decimal text, then after every iteration the raw
+    // embedding (2N floats, x block then y block); a send that fails ends the feed, not the run.
+    FrameSink frames = g_frames;
+    std::vector<float> frame_buf;
+    if (frames.send) {
+        const std::string hello = std::to_string(N);
+        if (frames.send(frames.user, hello.data(), hello.size()) != 0) {
+            std::cout << "No Visualization Terminal, continuing..." << std::endl;
+            frames.send = nullptr;
+        } else {
+            frame_buf.resize((size_t)N * 2);
+        }
+    } else if (opt.get_use_interactive()) {
         std::cout << "This version is not built with ZMQ for interative viz. Rebuild with WITH_ZMQ=TRUE for viz."
                   << std::endl;
+    }
     if (verbose) std::cout << "done." << std::endl;
     t_fft = timer.lap();
 
@@ -159,9 +181,10 @@ int run(Options &opt, GpuOptions &gpu_opt)
     const bool want_print = opt.verbosity >= 1;
     const bool want_dump = opt.get_dump_points();
     const bool want_snap = opt.return_style == RETURN_STYLE::SNAPSHOT && opt.return_data != nullptr;
+    const int frame_iv = std::max(1, frames.every);
     auto host_work_after = [&](long long st) {
         return (want_print && st % print_iv == 0) || (want_dump && st % dump_iv == 0) ||
-               (want_snap && st % snap_interval == 0);
+               (want_snap && st % snap_interval == 0) || (frames.send && st % frame_iv == 0);
     };
     auto next_multiple = [](long long st, long long iv) { return (st / iv + 1) * iv; };
     float loop_ms = 0.0f;
@@ -176,6 +199,7 @@ int run(Options &opt, GpuOptions &gpu_opt)
             if (want_print) stop = std::min(stop, next_multiple(step, print_iv));
             if (want_dump) stop = std::min(stop, next_multiple(step, dump_iv));
             if (want_snap) stop = std::min(stop, next_multiple(step, snap_interval));
+            if (frames.send) stop = std::min(stop, next_multiple(step, frame_iv));
         }
         int done = 0;
         float ms = 0.0f;
@@ -192,6 +216,13 @@ int run(Options &opt, GpuOptions &gpu_opt)
         // the reference prints the 2-norm of the update vector under this label (fit_tsne.cu:539-542)
         if (want_print && first % print_iv == 0)
             std::cout << "[Step " << first << "] Avg. Gradient Norm: " << s.last_unorm << std::endl;
+        if (frames.send && first % frame_iv == 0) {
+            B200_TRY(s.get_embedding_soa(frame_buf.data()));
+            if (frames.send(frames.user, frame_buf.data(), sizeof(float) * frame_buf.size()) != 0) {
+                std::cout << "Server Disconnected, Not sending anymore for this session." << std::endl;
+                frames.send = nullptr;
+            }
+        }
         if (want_dump && first % dump_iv == 0) {
             B200_TRY(s.get_embedding_soa(host_ys.data()));
             for (int i = 0; i < N; i++) dump_file << host_ys[i] << " " << host_ys[i + N] << std::endl;
@@ -318,6 +349,18 @@ int b200tsne_fit(const float *points, int64_t num_points, int num_dims, const b2
     }
     const int rc = tsnecuda::run(opt, gpu_opt);
     if (trained_norm) *trained_norm = opt.trained_norm;
+    return rc;
+}
+
+int b200tsne_fit_with_frames(const float *points, int64_t num_points, int num_dims, const b200tsne_options *o, float *result,
+                             float *trained_norm, b200tsne_frame_fn send, void *user, int every)
+{
+    if (!send || every <= 0) { b200::set_error("b200tsne_fit_with_frames: invalid arguments"); return B200TSNE_ERR_INVALID; }
+    tsnecuda::g_frames.send = send;
+    tsnecuda::g_frames.user = user;
+    tsnecuda::g_frames.every = every;
+    const int rc = b200tsne_fit(points, num_points, num_dims, o, result, trained_norm);
+    tsnecuda::g_frames = tsnecuda::FrameSink();
     return rc;
 }
 

@@ -47,8 +47,10 @@ __device__ __forceinline__ unsigned long long peer_global_ns()
 // waits until rank r's slot of the local array has reached it; gives up after 2 s.  With `state` the ranks also
 // exchange the min/max of the rows they have just updated (IterState slot mm_slot) and leave the global
 // min/max there, which replaces a pass over the whole embedding.
+// part: 0 = publish and wait in one launch; 1 = publish only; 2 = wait only (for the epoch the last publish used),
+// so that a stream can put work of its own between telling the others and waiting for them.
 __global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int *epochs, IterState *state, int mm_slot, int *err,
-                                    int *err_host, unsigned long long timeout_ns)
+                                    int *err_host, unsigned long long timeout_ns, int part)
 {
     const int lane = threadIdx.x;
     // An earlier meeting of this exchange gave up, here or on a peer (which then set the abort word in every
@@ -61,12 +63,12 @@ __global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int *epoch
     // the meeting's number: a device counter per kind that every rank advances alike (a launch parameter
     // would be frozen into a captured graph)
     unsigned int value = 0;
-    if (lane == 0) value = ++epochs[kind];
+    if (lane == 0) value = (part == 2) ? epochs[kind] : ++epochs[kind];
     value = __shfl_sync(0xffffffffu, value, 0);
     unsigned int my_min = 0, my_max = 0;
-    if (state) { my_min = state->min_enc[mm_slot]; my_max = state->max_enc[mm_slot]; }
+    if (state && part != 2) { my_min = state->min_enc[mm_slot]; my_max = state->max_enc[mm_slot]; }
     __threadfence_system();   // everything this stream wrote before (kernel boundary) is ordered before the flag
-    if (lane < tab.world) {
+    if (lane < tab.world && part != 2) {
         unsigned int *base = tab.flags[lane];
         if (state) {
             base[kMinMaxOffset + 2 * tab.rank] = my_min;
@@ -76,7 +78,7 @@ __global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int *epoch
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(value) : "memory");
     }
     unsigned int mn = 0xffffffffu, mx = 0u;
-    if (dead) return;
+    if (dead || part == 1) return;
     if (lane < tab.world) {
         const unsigned int *mine = tab.flags[tab.rank];
         const unsigned int *f = mine + kind * kMaxPeers + lane;
@@ -304,10 +306,10 @@ void peer_exchange_destroy(PeerExchange *px, Comm *comm, cudaStream_t st)
     delete px;
 }
 
-int launch_peer_barrier(PeerExchange *px, int kind, IterState *state, int mm_slot, cudaStream_t st)
+int launch_peer_barrier(PeerExchange *px, int kind, IterState *state, int mm_slot, cudaStream_t st, int part)
 {
     peer_barrier_kernel<<<1, 32, 0, st>>>(px->tab, kind, reinterpret_cast<unsigned int *>(px->err) + 2, state, mm_slot, px->err,
-                                          px->err_host_dev, px->timeout_ns);
+                                          px->err_host_dev, px->timeout_ns, part);
     B200_CUDA(cudaGetLastError());
     return 0;
 }
@@ -341,10 +343,10 @@ int peer_wait_selftest(int timeout_ms, float *waited_ms, cudaStream_t st)
     tab.flags[1] = flags + words;
     const unsigned long long ns = (unsigned long long)timeout_ms * 1000000ull;
     B200_CUDA(cudaEventRecord(a, st));
-    peer_barrier_kernel<<<1, 32, 0, st>>>(tab, kFlagSpread, reinterpret_cast<unsigned int *>(err) + 2, nullptr, 0, err, err_host_dev, ns);
+    peer_barrier_kernel<<<1, 32, 0, st>>>(tab, kFlagSpread, reinterpret_cast<unsigned int *>(err) + 2, nullptr, 0, err, err_host_dev, ns, 0);
     B200_CUDA(cudaGetLastError());
     // a second meeting on the failed exchange must return at once (it sees the error word on entry)
-    peer_barrier_kernel<<<1, 32, 0, st>>>(tab, kFlagUpdate, reinterpret_cast<unsigned int *>(err) + 2, nullptr, 0, err, err_host_dev, ns);
+    peer_barrier_kernel<<<1, 32, 0, st>>>(tab, kFlagUpdate, reinterpret_cast<unsigned int *>(err) + 2, nullptr, 0, err, err_host_dev, ns, 0);
     B200_CUDA(cudaGetLastError());
     B200_CUDA(cudaEventRecord(b, st));
     B200_CUDA(cudaStreamSynchronize(st));

@@ -71,7 +71,9 @@ void peer_exchange_destroy(PeerExchange *px, Comm *comm, cudaStream_t st);
 
 // All ranks meet: publish the next epoch of `kind` everywhere, wait (bounded) until every rank has.  With `state`, the
 // ranks' min/max encodings in IterState slot mm_slot are combined across the ranks on the way.
-int launch_peer_barrier(PeerExchange *px, int kind, IterState *state, int mm_slot, cudaStream_t st);
+// part: kMeetAll = one launch; kMeetPublish then kMeetWait = two launches with the stream's own work in between.
+enum MeetPart { kMeetAll = 0, kMeetPublish = 1, kMeetWait = 2 };
+int launch_peer_barrier(PeerExchange *px, int kind, IterState *state, int mm_slot, cudaStream_t st, int part = kMeetAll);
 // Exercises the bounded wait on one GPU without a peer: a two-rank table whose second rank is local memory
 // that nothing writes.  The meeting must give up after timeout_ms, set both error words and leave the device
 // usable; returns -5 when it did, 0 when the wait (wrongly) succeeded.

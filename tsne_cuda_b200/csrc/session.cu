@@ -202,6 +202,42 @@ int Session::get_embedding_soa(float *Y_host)
     return 0;
 }
 
+int Session::get_optimizer_soa(float *momentum_host, float *gains_host)
+{
+    B200_CUDA(cudaSetDevice(device));
+    const int64_t r = rows();
+    if (r == 0) return 0;
+    if (momentum_host) {
+        B200_TRY(launch_aos_to_soa(u, soa_tmp, r, stream));
+        B200_CUDA(cudaMemcpyAsync(momentum_host, soa_tmp, sizeof(float) * 2 * r, cudaMemcpyDeviceToHost, stream));
+        B200_CUDA(cudaStreamSynchronize(stream));
+    }
+    if (gains_host) {
+        B200_TRY(launch_aos_to_soa(gains, soa_tmp, r, stream));
+        B200_CUDA(cudaMemcpyAsync(gains_host, soa_tmp, sizeof(float) * 2 * r, cudaMemcpyDeviceToHost, stream));
+        B200_CUDA(cudaStreamSynchronize(stream));
+    }
+    return 0;
+}
+
+int Session::set_optimizer_soa(const float *momentum_host, const float *gains_host)
+{
+    B200_CUDA(cudaSetDevice(device));
+    const int64_t r = rows();
+    if (r == 0) return 0;
+    if (momentum_host) {
+        B200_CUDA(cudaMemcpyAsync(soa_tmp, momentum_host, sizeof(float) * 2 * r, cudaMemcpyHostToDevice, stream));
+        B200_TRY(launch_soa_to_aos(soa_tmp, u, r, stream));
+        B200_CUDA(cudaStreamSynchronize(stream));
+    }
+    if (gains_host) {
+        B200_CUDA(cudaMemcpyAsync(soa_tmp, gains_host, sizeof(float) * 2 * r, cudaMemcpyHostToDevice, stream));
+        B200_TRY(launch_soa_to_aos(soa_tmp, gains, r, stream));
+        B200_CUDA(cudaStreamSynchronize(stream));
+    }
+    return 0;
+}
+
 namespace {
 // Times the stages of one iteration when stage timers are on (serialised on one stream).
 struct StageClock {
@@ -256,9 +292,12 @@ int Session::one_iteration(bool want_norm)
     }
 
     // The embedding reshuffles quickly while it is being exaggerated and slowly afterwards: sort every
-    // iteration early, every order_refresh iterations later.
+    // iteration early, every order_refresh iterations later.  With the peer-memory exchange the sort for
+    // iteration t + 1 runs at the end of iteration t, between telling the other ranks "updated" and waiting
+    // for them (see below), so it is off the path here.
     const bool settling = step < force_magnify_iters + 50;
-    if (order_refresh > 0 && step % (settling ? order_refresh_early : order_refresh) == 0) {
+    const int refresh_every = settling ? order_refresh_early : order_refresh;
+    if (!p2p && order_refresh > 0 && step % refresh_every == 0) {
         clk.begin(stream);
         B200_TRY(launch_order_refresh(Y2, row_lo, row_hi, order, order_alt, order_keys, box_hist, state, slot, stream));
         std::swap(order, order_alt);
@@ -313,8 +352,21 @@ int Session::one_iteration(bool want_norm)
     clk.end(stream, kStUpdate, 1);
     if (p2p) {
         clk.begin(stream);
-        // the update kernel left this rank's min/max in slot^1; the meeting makes them global
-        B200_TRY(launch_peer_barrier(px, kFlagUpdate, state, slot ^ 1, stream));
+        // the update kernel left this rank's min/max in slot^1; the meeting makes them global.  Between its two
+        // halves this rank sorts its own new rows for the next spread: their boxes are taken from this
+        // iteration's bounding box (the next one is only known after the meeting), which is good enough for an
+        // order that only has to be roughly by box (spread_kernel recomputes every point's box).
+        B200_TRY(launch_peer_barrier(px, kFlagUpdate, state, slot ^ 1, stream, kMeetPublish));
+        clk.end(stream, kStExchange, 1);
+        if (order_refresh > 0 && (step + 1) % refresh_every == 0) {
+            clk.begin(stream);
+            B200_TRY(launch_order_refresh(px->y_local(px->parity ^ 1), row_lo, row_hi, order, order_alt, order_keys, box_hist, state,
+                                          slot, stream));
+            std::swap(order, order_alt);
+            clk.end(stream, kStOrder, 3);
+        }
+        clk.begin(stream);
+        B200_TRY(launch_peer_barrier(px, kFlagUpdate, state, slot ^ 1, stream, kMeetWait));
         px->parity ^= 1;
         Y2 = px->y_local(px->parity);
         w = px->w_local(px->parity);

@@ -107,6 +107,9 @@ struct Session {
     void destroy();
     int set_embedding_soa(const float *Y_host, bool reset);
     int get_embedding_soa(float *Y_host);
+    // optimiser state of the owned rows (momentum = the reference's old_forces, gains), SoA [2][rows] on the host
+    int get_optimizer_soa(float *momentum_host, float *gains_host);
+    int set_optimizer_soa(const float *momentum_host, const float *gains_host);
     int iterate(int n_iters, float min_gradient_norm, float *elapsed_ms, int *iters_done);
     int one_iteration(bool want_norm);
     int attractive(cudaStream_t st);   // Fattr of the owned rows from the current embedding
