@@ -191,7 +191,7 @@ def run_ours(args):
     return out if rank == 0 else None
 
 
-TRAFFIC_RATIO_BLOCKED = 0.90   # DRAM bytes / algorithmic bytes of the blocked kernel, from the committed capture
+TRAFFIC_RATIO_BLOCKED = 245.5 / 294.4   # dram__bytes_read + dram__bytes_write over algorithmic bytes, profiles/attractive_blocked_kernel_n400k.md
 
 
 def sharded_parity(s, X, K, lo, hi, rank, world):

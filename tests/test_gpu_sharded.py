@@ -22,8 +22,10 @@ def _free_port():
 def _rank(rank, world, port, X, Y0, K, knn_shard, exchange, out):
     import torch
     import torch.distributed as dist
+    # "p2p-slices": peer memory with the slice-owner form of the grid sum, which is the default from four ranks on
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
-                      B200TSNE_KNN_SHARD=knn_shard, B200TSNE_EXCHANGE=exchange)
+                      B200TSNE_KNN_SHARD=knn_shard, B200TSNE_EXCHANGE="nccl" if exchange == "nccl" else "p2p",
+                      B200TSNE_GRID_SUM="slices" if exchange == "p2p-slices" else "all")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world)
     from tsne_cuda_b200 import distributed
@@ -48,7 +50,7 @@ def _rank(rank, world, port, X, Y0, K, knn_shard, exchange, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("knn_shard,exchange", [("queries", "p2p"), ("queries", "nccl"), ("database", "p2p")])
+@pytest.mark.parametrize("knn_shard,exchange", [("queries", "p2p"), ("queries", "nccl"), ("database", "p2p"), ("queries", "p2p-slices")])
 def test_two_ranks_match_one(engine, oracle_cpu, knn_shard, exchange):
     torch = pytest.importorskip("torch")
     if torch.cuda.device_count() < 2:
@@ -68,7 +70,7 @@ def test_two_ranks_match_one(engine, oracle_cpu, knn_shard, exchange):
     for p in procs:
         p.join(timeout=60)
     assert [r[1] for r in res] == ["ok", "ok"], [r[1] for r in res]
-    assert [r[6] for r in res] == [2 if exchange == "p2p" else 1] * 2   # the exchange under test is the one that ran
+    assert [r[6] for r in res] == [1 if exchange == "nccl" else 2] * 2   # the exchange under test is the one that ran
     with engine.Session(N, K) as s:
         s.affinities_from_points(X, 20.0, 1e-4)
         P1, ids1 = s.get_affinities()

@@ -606,6 +606,31 @@ unpermute_kernel(const float2 *__restrict__ Fp, const int32_t *__restrict__ own_
     if (r < rows) F2[row_lo + r] = Fp[own_pos[r]];
 }
 
+// A chunk in a warp's registers: the stream loads are issued one round before the chunk is processed; then the
+// lane's row is found (it takes the place of row0), the row's own coordinate fetched, and the forces evaluated.
+// The kernel is bound by the L1/shared-memory data path (about two thirds busy: per chunk 4 gathers of 5 to 6
+// bank-conflict cycles each, 7 cycles of stream loads, the coordinate load, 4 shuffles, the reduction) and by
+// latency at one block of 32 warps per SM; more loads in flight make it slower, not faster.  Measured on B200
+// at N = 10^6, K = 90 (attractive stage of the iteration, 148 blocks): as below 190 us; without
+// L1::no_allocate on the stream 191 us; two register sets in turn instead of the copy 212 us; stream loads two
+// rounds ahead 218 us; rows and own coordinates a round ahead as well (three sets) 247 us; the row coordinates
+// of a chunk fetched a round ahead as one coalesced load and handed to the lanes by shuffle 244 us; an L2
+// prefetch six rounds ahead changes nothing; 768 threads with 79 registers 241 us.
+struct ChunkSet {
+    float4 p;      // values of the lane's four entries
+    uint2 c;       // their 16-bit words: column (15 bits) | flag (bit 15): entry 0 "next row", 1 "run starts", 2, 3 "add lane + 1 / + 2"
+    int r;         // the chunk's row0 word (sign bit: the chunk holds a marker lane), then this lane's row
+};
+// The stream is read once: its loads do not take lines of the (small, beside 224 KB of shared memory) L1.
+__device__ __forceinline__ void stage_load(ChunkSet &s, const BlockedStream &b, int cc, int lane)
+{
+    const float4 *pv = reinterpret_cast<const float4 *>(b.ev) + (size_t)cc * 32 + lane;
+    const uint2 *pc = reinterpret_cast<const uint2 *>(b.ec) + (size_t)cc * 32 + lane;
+    asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(s.p.x), "=f"(s.p.y), "=f"(s.p.z), "=f"(s.p.w) : "l"(pv));
+    asm volatile("ld.global.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(s.c.x), "=r"(s.c.y) : "l"(pc));
+    s.r = __ldg(b.chunk_row0 + cc);
+}
+
 __device__ __forceinline__ void add_entry(float2 yi, float2 yj, float p, float &ox, float &oy)
 {
     const float dx = yi.x - yj.x, dy = yi.y - yj.y;
@@ -618,34 +643,13 @@ __device__ __forceinline__ float2 tile_at(const float2 *tile, unsigned byte_offs
     return *reinterpret_cast<const float2 *>(reinterpret_cast<const char *>(tile) + byte_offset);
 }
 
-// A chunk in a warp's registers: the stream loads are issued one round before the chunk is processed; then the
-// lane's row is found (it takes the place of row0), the row's own coordinate fetched, and the forces evaluated.
-// Measured alternatives, all slower on B200 at N = 10^6, K = 90 (attractive stage of the iteration, 148 blocks):
-// as below 190 us; two register sets in turn instead of the copy 212 us; stream loads two rounds ahead 218 us;
-// rows and own coordinates a round ahead as well (three sets) 247 us; an additional L2 prefetch six rounds ahead
-// changes nothing; 768 threads with 79 registers 241 us.
-struct ChunkSet {
-    float4 p;
-    uint2 c;
-    int r;        // after stage A: the chunk's row0 word; after stage B: this lane's row
-    float2 yi;
-};
-// The stream is read once: its loads do not take lines of the (small, beside 224 KB of shared memory) L1.
-__device__ __forceinline__ void stage_load(ChunkSet &s, const BlockedStream &b, int cc, int lane)
-{
-    const float4 *pv = reinterpret_cast<const float4 *>(b.ev) + (size_t)cc * 32 + lane;
-    const uint2 *pc = reinterpret_cast<const uint2 *>(b.ec) + (size_t)cc * 32 + lane;
-    asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(s.p.x), "=f"(s.p.y), "=f"(s.p.z), "=f"(s.p.w) : "l"(pv));
-    asm volatile("ld.global.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(s.c.x), "=r"(s.c.y) : "l"(pc));
-    s.r = __ldg(b.chunk_row0 + cc);
-}
-
-__device__ __forceinline__ void stage_rows(ChunkSet &w, const float2 *__restrict__ Yown, int lane)
+__device__ __forceinline__ void process_chunk(ChunkSet &w, const float2 *__restrict__ tile, const float2 *__restrict__ Yown,
+                                              float2 *__restrict__ Fp, int lane)
 {
     const bool head = w.c.x & 0x8000u;
     const unsigned hm = __ballot_sync(0xffffffffu, head);
     if (w.r >= 0) {
-        w.r += __popc(hm & (0xffffffffu >> (31 - lane)));
+        w.r += __popc(hm & (0xffffffffu >> (31 - lane)));   // heads up to and including this lane
     } else {
         // a marker lane (first word 0xffff) sets the row to the number its first value holds; rows are then a
         // scan over (row set by a marker, heads since)
@@ -659,19 +663,15 @@ __device__ __forceinline__ void stage_rows(ChunkSet &w, const float2 *__restrict
         w.r = (s == INT_MIN ? (w.r & 0x7fffffff) : s) + n;
         if (marker) { w.p.x = 0.0f; w.c.x &= 0xffff0000u; }   // from here on an entry of value 0 at column 0
     }
-    w.yi = __ldg(Yown + w.r);
-}
-
-__device__ __forceinline__ void stage_forces(const ChunkSet &w, const float2 *__restrict__ tile, float2 *__restrict__ Fp)
-{
+    const float2 yi = __ldg(Yown + w.r);
     // byte offsets of the four columns in the tile
     const float2 yj0 = tile_at(tile, (w.c.x << 3) & 0x3fff8u), yj1 = tile_at(tile, (w.c.x >> 13) & 0x3fff8u);
     const float2 yj2 = tile_at(tile, (w.c.y << 3) & 0x3fff8u), yj3 = tile_at(tile, (w.c.y >> 13) & 0x3fff8u);
     float ox = 0.0f, oy = 0.0f;
-    add_entry(w.yi, yj0, w.p.x, ox, oy);
-    add_entry(w.yi, yj1, w.p.y, ox, oy);
-    add_entry(w.yi, yj2, w.p.z, ox, oy);
-    add_entry(w.yi, yj3, w.p.w, ox, oy);
+    add_entry(yi, yj0, w.p.x, ox, oy);
+    add_entry(yi, yj1, w.p.y, ox, oy);
+    add_entry(yi, yj2, w.p.z, ox, oy);
+    add_entry(yi, yj3, w.p.w, ox, oy);
     // runs of at most four lanes: two steps, the flags say which lanes add
     {
         const float tx = __shfl_down_sync(0xffffffffu, ox, 1), ty = __shfl_down_sync(0xffffffffu, oy, 1);
@@ -723,8 +723,7 @@ attractive_blocked_kernel(BlockedStream b, const float2 *__restrict__ Yp, const 
         for (; cc < c_end; cc += nwarps) {
             ChunkSet cur = next;
             stage_load(next, b, min(cc + nwarps, last), lane);
-            stage_rows(cur, Yown, lane);
-            stage_forces(cur, tile, Fp);
+            process_chunk(cur, tile, Yown, Fp, lane);
         }
         c = c_end;
     }

@@ -17,18 +17,21 @@ size_t round_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
 
 // Flag words of a rank: [kind][writer rank] epochs, then [writer rank][2] the writers' min/max encodings, then one
 // abort word that a rank whose wait expired sets in every rank's block.
-constexpr int kMinMaxOffset = 2 * kMaxPeers;
-constexpr int kAbortOffset = 4 * kMaxPeers;
-constexpr int kFlagWords = 4 * kMaxPeers + 16;
+constexpr int kMinMaxOffset = kFlagKinds * kMaxPeers;
+constexpr int kAbortOffset = (kFlagKinds + 2) * kMaxPeers;
+constexpr int kFlagWords = (kFlagKinds + 2) * kMaxPeers + 16;
+constexpr int kErrWords = 8;
 
 struct Layout {
-    size_t w[2], y[2], flags, total;
+    size_t w[2], ws, y[2], flags, total;
 };
 Layout block_layout(int64_t npad)
 {
     Layout l;
     size_t o = 0;
     for (int b = 0; b < 2; b++) { l.w[b] = o; o += round_up(sizeof(float4) * (size_t)kG * kG); }
+    l.ws = o;
+    o += round_up(sizeof(float4) * (size_t)kG * kG);
     for (int b = 0; b < 2; b++) { l.y[b] = o; o += round_up(sizeof(float2) * (size_t)npad); }
     l.flags = o;
     o += round_up(sizeof(unsigned int) * kFlagWords);   // epochs [2][ranks], min/max [ranks][2], abort word
@@ -47,10 +50,8 @@ __device__ __forceinline__ unsigned long long peer_global_ns()
 // waits until rank r's slot of the local array has reached it; gives up after 2 s.  With `state` the ranks also
 // exchange the min/max of the rows they have just updated (IterState slot mm_slot) and leave the global
 // min/max there, which replaces a pass over the whole embedding.
-// part: 0 = publish and wait in one launch; 1 = publish only; 2 = wait only (for the epoch the last publish used),
-// so that a stream can put work of its own between telling the others and waiting for them.
 __global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int *epochs, IterState *state, int mm_slot, int *err,
-                                    int *err_host, unsigned long long timeout_ns, int part)
+                                    int *err_host, unsigned long long timeout_ns)
 {
     const int lane = threadIdx.x;
     // An earlier meeting of this exchange gave up, here or on a peer (which then set the abort word in every
@@ -63,12 +64,12 @@ __global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int *epoch
     // the meeting's number: a device counter per kind that every rank advances alike (a launch parameter
     // would be frozen into a captured graph)
     unsigned int value = 0;
-    if (lane == 0) value = (part == 2) ? epochs[kind] : ++epochs[kind];
+    if (lane == 0) value = ++epochs[kind];
     value = __shfl_sync(0xffffffffu, value, 0);
     unsigned int my_min = 0, my_max = 0;
-    if (state && part != 2) { my_min = state->min_enc[mm_slot]; my_max = state->max_enc[mm_slot]; }
+    if (state) { my_min = state->min_enc[mm_slot]; my_max = state->max_enc[mm_slot]; }
     __threadfence_system();   // everything this stream wrote before (kernel boundary) is ordered before the flag
-    if (lane < tab.world && part != 2) {
+    if (lane < tab.world) {
         unsigned int *base = tab.flags[lane];
         if (state) {
             base[kMinMaxOffset + 2 * tab.rank] = my_min;
@@ -78,7 +79,7 @@ __global__ void peer_barrier_kernel(PeerTable tab, int kind, unsigned int *epoch
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(value) : "memory");
     }
     unsigned int mn = 0xffffffffu, mx = 0u;
-    if (dead || part == 1) return;
+    if (dead) return;
     if (lane < tab.world) {
         const unsigned int *mine = tab.flags[tab.rank];
         const unsigned int *f = mine + kind * kMaxPeers + lane;
@@ -141,6 +142,89 @@ peer_grid_reduce_kernel(GridSources src, float4 *__restrict__ w_sum)
             if (s < src.world) { acc.x += v[s].x; acc.y += v[s].y; acc.z += v[s].z; acc.w += v[s].w; }
         w_sum[i] = acc;
     }
+}
+
+// Waits until the `kind` flags of all ranks in this rank's flag array have reached `value`; one thread per rank.
+// Returns false (and sets the error words and every rank's abort word) when the limit runs out or a peer has aborted.
+__device__ __forceinline__ bool wait_flags(const PeerTable &tab, int kind, unsigned int value, int who, int *err, int *err_host,
+                                           unsigned long long timeout_ns)
+{
+    const unsigned int *mine = tab.flags[tab.rank];
+    const unsigned int *f = mine + kind * kMaxPeers + who;
+    const unsigned long long t0 = peer_global_ns();
+    int spins = 0;
+    for (;;) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+        if ((int)(v - value) >= 0) return true;
+        if ((++spins & 255) == 0) {
+            const bool aborted = *reinterpret_cast<const volatile unsigned int *>(mine + kAbortOffset) != 0;
+            if (aborted || peer_global_ns() - t0 > timeout_ns) {
+                atomicExch(err, 1);
+                *reinterpret_cast<volatile int *>(err_host) = 1;
+                for (int r = 0; r < tab.world; r++) *reinterpret_cast<volatile unsigned int *>(tab.flags[r] + kAbortOffset) = 1u;
+                return false;
+            }
+        }
+    }
+}
+
+// Grid sum and "all spreads done" meeting in one launch (see peer.h).  Every block publishes nothing but waits for
+// the spread flags itself (block 0 publishes this rank's); the block that finishes its share of the slice last
+// publishes "slice stored", waits for the other ranks' slices and advances the epoch counters.
+constexpr int kAllreduceBlocks = 48;
+__global__ void __launch_bounds__(256)
+peer_grid_allreduce_kernel(PeerTable tab, int buf, unsigned int *epochs, int *block_counter, int *err, int *err_host,
+                           unsigned long long timeout_ns)
+{
+    __shared__ int s_ok, s_last;
+    const unsigned int v_spread = epochs[kFlagSpread] + 1, v_slice = epochs[kFlagSlice] + 1;   // alike in all blocks: written only by the last one
+    bool dead = *reinterpret_cast<volatile int *>(err) != 0 ||
+                *reinterpret_cast<volatile unsigned int *>(tab.flags[tab.rank] + kAbortOffset) != 0;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (blockIdx.x == 0 && threadIdx.x < tab.world) {
+        __threadfence_system();   // this rank's spread (earlier in the stream) before its flag
+        unsigned int *f = tab.flags[threadIdx.x] + kFlagSpread * kMaxPeers + tab.rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(v_spread) : "memory");
+    }
+    if (!dead && threadIdx.x < tab.world) {
+        if (!wait_flags(tab, kFlagSpread, v_spread, threadIdx.x, err, err_host, timeout_ns)) s_ok = 0;
+    }
+    __syncthreads();
+    if (!dead && s_ok) {
+        const int n = kG * kG, slice = (n + tab.world - 1) / tab.world;
+        const int lo = tab.rank * slice, hi = min(n, lo + slice);
+        for (int i = lo + blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += gridDim.x * blockDim.x) {
+            float4 v[kMaxPeers];
+#pragma unroll
+            for (int s = 0; s < kMaxPeers; s++)
+                if (s < tab.world) v[s] = tab.w[buf][s][i];   // all loads first: the peer round trips overlap
+            float4 acc = v[0];
+#pragma unroll
+            for (int s = 1; s < kMaxPeers; s++)
+                if (s < tab.world) { acc.x += v[s].x; acc.y += v[s].y; acc.z += v[s].z; acc.w += v[s].w; }
+#pragma unroll
+            for (int s = 0; s < kMaxPeers; s++)
+                if (s < tab.world) tab.ws[s][i] = acc;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(block_counter, 1) == (int)gridDim.x - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence_system();   // the other blocks' stores (each fenced before its count) before this rank's flag
+    if (threadIdx.x == 0) *block_counter = 0;
+    if (threadIdx.x < tab.world) {
+        unsigned int *f = tab.flags[threadIdx.x] + kFlagSlice * kMaxPeers + tab.rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(v_slice) : "memory");
+        dead = dead || *reinterpret_cast<volatile int *>(err) != 0;
+        if (!dead) wait_flags(tab, kFlagSlice, v_slice, threadIdx.x, err, err_host, timeout_ns);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) { epochs[kFlagSpread] = v_spread; epochs[kFlagSlice] = v_slice; }
+    __threadfence_system();
 }
 
 // sum_i Z_i with Z_i = (1 + |y_i|^2) phi_count(y_i) - 2 (x_i phi_x(y_i) + y_i phi_y(y_i)) + phi_r2(y_i) and every
@@ -215,7 +299,7 @@ int peer_exchange_acquire(PeerExchange **out, Comm *comm, int64_t npad, cudaStre
         if (ms > 0) px->timeout_ns = (unsigned long long)ms * 1000000ull;
     }
     B200_CUDA(cudaMalloc(&px->local, lay.total));
-    B200_CUDA(cudaMalloc((void **)&px->err, sizeof(int) * 4));
+    B200_CUDA(cudaMalloc((void **)&px->err, sizeof(int) * kErrWords));
     {
         int *h = nullptr;
         B200_CUDA(cudaHostAlloc((void **)&h, sizeof(int), cudaHostAllocMapped));
@@ -224,7 +308,7 @@ int peer_exchange_acquire(PeerExchange **out, Comm *comm, int64_t npad, cudaStre
         B200_CUDA(cudaHostGetDevicePointer((void **)&px->err_host_dev, h, 0));
     }
     B200_CUDA(cudaMemsetAsync(px->local, 0, lay.total, st));
-    B200_CUDA(cudaMemsetAsync(px->err, 0, sizeof(int) * 4, st));
+    B200_CUDA(cudaMemsetAsync(px->err, 0, sizeof(int) * kErrWords, st));
 
     // handles of all ranks, gathered through the communicator
     cudaIpcMemHandle_t mine;
@@ -269,6 +353,7 @@ int peer_exchange_acquire(PeerExchange **out, Comm *comm, int64_t npad, cudaStre
             px->tab.w[b][r] = base ? reinterpret_cast<float4 *>(base + lay.w[b]) : nullptr;
             px->tab.y[b][r] = base ? reinterpret_cast<float2 *>(base + lay.y[b]) : nullptr;
         }
+        px->tab.ws[r] = base ? reinterpret_cast<float4 *>(base + lay.ws) : nullptr;
         px->tab.flags[r] = base ? reinterpret_cast<unsigned int *>(base + lay.flags) : nullptr;
     }
     fail.armed = false;
@@ -306,10 +391,10 @@ void peer_exchange_destroy(PeerExchange *px, Comm *comm, cudaStream_t st)
     delete px;
 }
 
-int launch_peer_barrier(PeerExchange *px, int kind, IterState *state, int mm_slot, cudaStream_t st, int part)
+int launch_peer_barrier(PeerExchange *px, int kind, IterState *state, int mm_slot, cudaStream_t st)
 {
     peer_barrier_kernel<<<1, 32, 0, st>>>(px->tab, kind, reinterpret_cast<unsigned int *>(px->err) + 2, state, mm_slot, px->err,
-                                          px->err_host_dev, px->timeout_ns, part);
+                                          px->err_host_dev, px->timeout_ns);
     B200_CUDA(cudaGetLastError());
     return 0;
 }
@@ -327,12 +412,12 @@ int peer_wait_selftest(int timeout_ms, float *waited_ms, cudaStream_t st)
     } guard{flags, err, err_host, a, b};
     const size_t words = kFlagWords;
     B200_CUDA(cudaMalloc((void **)&flags, sizeof(unsigned int) * words * 2));
-    B200_CUDA(cudaMalloc((void **)&err, sizeof(int) * 4));
+    B200_CUDA(cudaMalloc((void **)&err, sizeof(int) * kErrWords));
     B200_CUDA(cudaHostAlloc((void **)&err_host, sizeof(int), cudaHostAllocMapped));
     *err_host = 0;
     B200_CUDA(cudaHostGetDevicePointer((void **)&err_host_dev, err_host, 0));
     B200_CUDA(cudaMemsetAsync(flags, 0, sizeof(unsigned int) * words * 2, st));
-    B200_CUDA(cudaMemsetAsync(err, 0, sizeof(int) * 4, st));
+    B200_CUDA(cudaMemsetAsync(err, 0, sizeof(int) * kErrWords, st));
     B200_CUDA(cudaEventCreate(&a));
     B200_CUDA(cudaEventCreate(&b));
     PeerTable tab;
@@ -343,10 +428,10 @@ int peer_wait_selftest(int timeout_ms, float *waited_ms, cudaStream_t st)
     tab.flags[1] = flags + words;
     const unsigned long long ns = (unsigned long long)timeout_ms * 1000000ull;
     B200_CUDA(cudaEventRecord(a, st));
-    peer_barrier_kernel<<<1, 32, 0, st>>>(tab, kFlagSpread, reinterpret_cast<unsigned int *>(err) + 2, nullptr, 0, err, err_host_dev, ns, 0);
+    peer_barrier_kernel<<<1, 32, 0, st>>>(tab, kFlagSpread, reinterpret_cast<unsigned int *>(err) + 2, nullptr, 0, err, err_host_dev, ns);
     B200_CUDA(cudaGetLastError());
     // a second meeting on the failed exchange must return at once (it sees the error word on entry)
-    peer_barrier_kernel<<<1, 32, 0, st>>>(tab, kFlagUpdate, reinterpret_cast<unsigned int *>(err) + 2, nullptr, 0, err, err_host_dev, ns, 0);
+    peer_barrier_kernel<<<1, 32, 0, st>>>(tab, kFlagUpdate, reinterpret_cast<unsigned int *>(err) + 2, nullptr, 0, err, err_host_dev, ns);
     B200_CUDA(cudaGetLastError());
     B200_CUDA(cudaEventRecord(b, st));
     B200_CUDA(cudaStreamSynchronize(st));
@@ -365,6 +450,14 @@ int launch_peer_grid_reduce(PeerExchange *px, int buf, float4 *w_sum, cudaStream
     src.world = px->tab.world;
     for (int r = 0; r < kMaxPeers; r++) src.p[r] = px->tab.w[buf][r];
     peer_grid_reduce_kernel<<<148 * 2, 256, 0, st>>>(src, w_sum);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_peer_grid_allreduce(PeerExchange *px, int buf, cudaStream_t st)
+{
+    unsigned int *epochs = reinterpret_cast<unsigned int *>(px->err) + 2;
+    peer_grid_allreduce_kernel<<<kAllreduceBlocks, 256, 0, st>>>(px->tab, buf, epochs, px->err + 5, px->err, px->err_host_dev, px->timeout_ns);
     B200_CUDA(cudaGetLastError());
     return 0;
 }

@@ -34,12 +34,14 @@ namespace b200 {
 struct Comm;
 
 constexpr int kMaxPeers = 16;
-enum PeerFlag { kFlagSpread = 0, kFlagUpdate = 1 };
+enum PeerFlag { kFlagSpread = 0, kFlagUpdate = 1, kFlagSlice = 2 };
+constexpr int kFlagKinds = 3;
 
 // pointer table handed to kernels by value
 struct PeerTable {
     int world, rank;
     float4 *w[2][kMaxPeers];     // [buffer][rank] partial grids
+    float4 *ws[kMaxPeers];       // [rank] summed grid of that rank (written by the owners of its slices)
     float2 *y[2][kMaxPeers];     // [buffer][rank] embedding copies
     unsigned int *flags[kMaxPeers];   // [rank] flag words: [kind * kMaxPeers + writer rank], then min/max per writer
 };
@@ -48,7 +50,7 @@ struct PeerExchange {
     PeerTable tab;
     void *local = nullptr;       // this rank's block
     void *mapped[kMaxPeers];     // peers' blocks as mapped here (null for this rank)
-    int *err = nullptr;          // device words: [0] a bounded wait expired, [1] scratch of the closing meeting, [2], [3] epoch counters per kind
+    int *err = nullptr;          // device words: [0] a bounded wait expired, [1] scratch of the closing meeting, [2..4] epoch counters per kind, [5] block counter of the grid sum
     volatile int *err_host = nullptr;   // mapped host word the kernel sets on expiry (read by the host without a sync)
     int *err_host_dev = nullptr;        // the same word as the device addresses it
     unsigned long long timeout_ns = 2000000000ull;   // limit of one meeting
@@ -57,6 +59,7 @@ struct PeerExchange {
     int64_t npad = 0;
 
     float4 *w_local(int b) { return tab.w[b][tab.rank]; }
+    float4 *ws_local() { return tab.ws[tab.rank]; }
     float2 *y_local(int b) { return tab.y[b][tab.rank]; }
 };
 
@@ -71,15 +74,17 @@ void peer_exchange_destroy(PeerExchange *px, Comm *comm, cudaStream_t st);
 
 // All ranks meet: publish the next epoch of `kind` everywhere, wait (bounded) until every rank has.  With `state`, the
 // ranks' min/max encodings in IterState slot mm_slot are combined across the ranks on the way.
-// part: kMeetAll = one launch; kMeetPublish then kMeetWait = two launches with the stream's own work in between.
-enum MeetPart { kMeetAll = 0, kMeetPublish = 1, kMeetWait = 2 };
-int launch_peer_barrier(PeerExchange *px, int kind, IterState *state, int mm_slot, cudaStream_t st, int part = kMeetAll);
+int launch_peer_barrier(PeerExchange *px, int kind, IterState *state, int mm_slot, cudaStream_t st);
 // Exercises the bounded wait on one GPU without a peer: a two-rank table whose second rank is local memory
 // that nothing writes.  The meeting must give up after timeout_ms, set both error words and leave the device
 // usable; returns -5 when it did, 0 when the wait (wrongly) succeeded.
 int peer_wait_selftest(int timeout_ms, float *waited_ms, cudaStream_t st);
 // w_sum[node] = sum over ranks (in rank order) of their partial grid `buf`
 int launch_peer_grid_reduce(PeerExchange *px, int buf, float4 *w_sum, cudaStream_t st);
+// The same sum in one launch that also is the "all spreads done" meeting, with 1/world of the traffic per rank:
+// every rank sums the nodes of its own slice from all ranks' partial grids and stores the sums into every
+// rank's summed grid (ws), then the ranks meet once more ("all slices stored").  The result is in px->ws_local().
+int launch_peer_grid_allreduce(PeerExchange *px, int buf, cudaStream_t st);
 // state->zsum[slot] += sum over nodes of the bilinear form of charges w_sum and potentials ytilde
 int launch_grid_z(const float4 *w_sum, const float4 *ytilde, IterState *state, int slot, cudaStream_t st);
 

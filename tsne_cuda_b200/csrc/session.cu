@@ -292,12 +292,13 @@ int Session::one_iteration(bool want_norm)
     }
 
     // The embedding reshuffles quickly while it is being exaggerated and slowly afterwards: sort every
-    // iteration early, every order_refresh iterations later.  With the peer-memory exchange the sort for
-    // iteration t + 1 runs at the end of iteration t, between telling the other ranks "updated" and waiting
-    // for them (see below), so it is off the path here.
+    // iteration early, every order_refresh iterations later.  (Sorting the rows for iteration t + 1 at the end of
+    // iteration t, while waiting for the other ranks, was measured on two GPUs: the next bounding box is only
+    // known after that meeting, and boxes taken from the previous one - the embedding grows by more than a box
+    // width per exaggerated iteration - break the runs of equal boxes: spread 61 us instead of 15.)
     const bool settling = step < force_magnify_iters + 50;
     const int refresh_every = settling ? order_refresh_early : order_refresh;
-    if (!p2p && order_refresh > 0 && step % refresh_every == 0) {
+    if (order_refresh > 0 && step % refresh_every == 0) {
         clk.begin(stream);
         B200_TRY(launch_order_refresh(Y2, row_lo, row_hi, order, order_alt, order_keys, box_hist, state, slot, stream));
         std::swap(order, order_alt);
@@ -308,9 +309,14 @@ int Session::one_iteration(bool want_norm)
     clk.end(stream, kStSpread, 1);
     if (p2p) {
         clk.begin(stream);
-        B200_TRY(launch_peer_barrier(px, kFlagSpread, nullptr, 0, stream));
-        B200_TRY(launch_peer_grid_reduce(px, px->parity, w_sum, stream));
-        clk.end(stream, kStExchange, 2);
+        if (grid_two_shot) {
+            B200_TRY(launch_peer_grid_allreduce(px, px->parity, stream));
+            clk.end(stream, kStExchange, 1);
+        } else {
+            B200_TRY(launch_peer_barrier(px, kFlagSpread, nullptr, 0, stream));
+            B200_TRY(launch_peer_grid_reduce(px, px->parity, w_sum, stream));
+            clk.end(stream, kStExchange, 2);
+        }
     } else if (multi) {
         clk.begin(stream);
         B200_TRY(comm->all_reduce_sum_f32(reinterpret_cast<float *>(w), (size_t)kG * kG * 4, stream));
@@ -352,21 +358,8 @@ int Session::one_iteration(bool want_norm)
     clk.end(stream, kStUpdate, 1);
     if (p2p) {
         clk.begin(stream);
-        // the update kernel left this rank's min/max in slot^1; the meeting makes them global.  Between its two
-        // halves this rank sorts its own new rows for the next spread: their boxes are taken from this
-        // iteration's bounding box (the next one is only known after the meeting), which is good enough for an
-        // order that only has to be roughly by box (spread_kernel recomputes every point's box).
-        B200_TRY(launch_peer_barrier(px, kFlagUpdate, state, slot ^ 1, stream, kMeetPublish));
-        clk.end(stream, kStExchange, 1);
-        if (order_refresh > 0 && (step + 1) % refresh_every == 0) {
-            clk.begin(stream);
-            B200_TRY(launch_order_refresh(px->y_local(px->parity ^ 1), row_lo, row_hi, order, order_alt, order_keys, box_hist, state,
-                                          slot, stream));
-            std::swap(order, order_alt);
-            clk.end(stream, kStOrder, 3);
-        }
-        clk.begin(stream);
-        B200_TRY(launch_peer_barrier(px, kFlagUpdate, state, slot ^ 1, stream, kMeetWait));
+        // the update kernel left this rank's min/max in slot^1; the meeting makes them global
+        B200_TRY(launch_peer_barrier(px, kFlagUpdate, state, slot ^ 1, stream));
         px->parity ^= 1;
         Y2 = px->y_local(px->parity);
         w = px->w_local(px->parity);
@@ -538,7 +531,15 @@ int Session::attach_peer_exchange()
     B200_CUDA(cudaSetDevice(device));
     B200_TRY(peer_exchange_acquire(&px, comm, N + 16, stream));
     if (!px) return 0;
-    B200_TRY(arena.alloc((void **)&w_sum, sizeof(float4) * kG * kG));
+    // The grid sum: every rank reads all partial grids ((W - 1) x 2.4 MB over NVLink per rank), or the slice owners
+    // form (2 x 2.4 MB x (W - 1) / W and one more flag round trip).  B200TSNE_GRID_SUM = "all" / "slices"; default:
+    // slices from four ranks on.
+    {
+        const char *g = getenv("B200TSNE_GRID_SUM");
+        grid_two_shot = g ? strcmp(g, "slices") == 0 : comm->world >= 4;
+    }
+    if (grid_two_shot) w_sum = px->ws_local();
+    else B200_TRY(arena.alloc((void **)&w_sum, sizeof(float4) * kG * kG));
     B200_CUDA(cudaMemcpyAsync(px->y_local(px->parity), Y2_own, sizeof(float2) * (size_t)N, cudaMemcpyDeviceToDevice, stream));
     B200_CUDA(cudaStreamSynchronize(stream));
     Y2 = px->y_local(px->parity);

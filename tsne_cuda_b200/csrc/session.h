@@ -82,6 +82,7 @@ struct Session {
     float2 *Y2_own = nullptr;   // the session's own allocations, used whenever px is null
     float4 *w_own = nullptr;
     float4 *w_sum = nullptr;
+    bool grid_two_shot = false;   // peer-memory exchange: the grid sum as slice owners (peer.h), chosen at attach
     int attach_peer_exchange();   // collective, after comm is set
 
     // Captured iterations (single GPU or peer-memory exchange, no stage timers, no update norm): at small N the loop is bound by the
