@@ -181,7 +181,7 @@ def run_ours(args):
 
     if rank == 0 and not multi and not args.no_e2e:
         out["e2e"] = e2e_ours(X, hp, Y0, args)
-    elif multi:
+    elif multi and not args.no_e2e:
         out["e2e"] = e2e_sharded(X, hp, Y0, args, rank, local_rank, world)
     if rank == 0 and not multi and not args.no_cpu:
         out["cpu_baseline"] = cpu_baseline(X, hp, Y0, args)

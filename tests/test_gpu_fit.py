@@ -251,6 +251,27 @@ def test_snapshots_dump_and_errors(engine, tmp_path, capfd):
     assert "_time_knn:" in out and "[Step 20] Avg. Gradient Norm:" in out and "total_time:" in out and Z > 0
 
 
+def test_snapshots_are_the_states_the_oracle_reaches(engine, oracle_cpu):
+    """SNAPSHOT return: block s is the embedding after iteration s * interval has run, the last block the final
+    embedding (src/fit_tsne.cu:573-579, :615-618; interval = iterations / (num_snapshots - 1)).  Compared with the
+    CPU oracle's loop stopped at the same iteration counts, from the same points, neighbours and injected Y0."""
+    n, K, iters, snaps = 2000, 30, 8, 5
+    X = mixture(n, 12, 6)
+    Y0 = (1e-4 * np.random.default_rng(3).standard_normal((2, n))).astype(np.float32)
+    Y, _ = engine.fit(X, iterations=iters, num_neighbors=K, perplexity=10.0, perplexity_search_epsilon=1e-4, learning_rate=200.0,
+                      initialization_type=3, preinit_data=Y0, return_style=1, num_snapshots=snaps)
+    assert Y.shape == (snaps, 2, n)
+    with engine.Session(n, K) as s:          # the affinities the fit computed (same code, deterministic)
+        s.affinities_from_points(X, 10.0, 1e-4)
+        P, ids = s.get_affinities()
+    assert np.array_equal(ids, oracle_cpu.knn(X, K)[0])
+    interval = iters // (snaps - 1)
+    done = [s * interval + 1 for s in range(snaps - 1)] + [iters]       # iterations behind each block
+    for block, n_it in zip(Y, done):
+        Yc, _, _, _ = oracle_cpu.iterate(P, ids, Y0, n_it, 200.0)
+        assert rel_l2(block, Yc) < 1e-3, n_it
+
+
 def test_frame_feed_has_the_reference_wire_format(engine):
     """The live feed without a socket: a text frame with the number of points, then raw float32 frames of 2N values
     (x block, y block) after every iteration, as the reference's REQ/REP publisher sends them

@@ -336,16 +336,23 @@ own_scatter_kernel(const int32_t *__restrict__ perm, long long N, long long row_
 }
 
 // ---- walking the rows of a range: per-warp scratch ----
-constexpr int kWalkWarps = 2;
+constexpr int kWalkWarps = 1;
 constexpr int kMaxK = 1024;
 struct WalkScratch {
     long long run[kMaxTiles];      // count pass: entries this range adds to the tile; fill pass: next free entry of the tile
     int rowcnt[kMaxTiles];         // entries of the current row per tile
-    unsigned slot[kMaxK];          // per slot of the current row: tile << 16 | rank inside (row, tile) in slot order; 0xffffffff = unused slot
+    unsigned slot[kMaxK];          // per slot of the current row, see kSlot*; 0xffffffff = unused slot
     unsigned short col[kMaxK];     // per slot: column inside the tile
     unsigned bitmap[2][32];        // tiles touched by the previous / the current row
+    // fill pass, per tile: bank pairs already taken in the half-warp window (16 lanes) that holds the tile's cursor
+    // and in the window after it: bit 16 k + b = "the k-th gather of that window reads bank pair b"
+    unsigned long long win[kMaxTiles][2];
+    int win_id[kMaxTiles];         // absolute lane / 16 of win[.][0]
 };
-constexpr unsigned kSlotUnused = 0xffffffffu;
+// slot word: bits 16..25 tile, bit 30 first slot of its (row, tile) group; low 16 bits: rank inside the group in
+// slot order, later the cell (4 x lane of the group + entry) the slot's entry is written to
+constexpr unsigned kSlotUnused = 0xffffffffu, kSlotLeader = 1u << 30;
+__device__ __forceinline__ int slot_tile(unsigned info) { return (info >> 16) & 0x3ffu; }
 
 struct WalkArgs {
     const float *P_rows;           // [rows][K]
@@ -355,6 +362,7 @@ struct WalkArgs {
     long long N, row_lo, rows;
     int K, T, ntiles, range_rows;
     long long n_ranges;
+    int greedy;                    // place a group's entries by bank pair (place_group) instead of in slot order
 };
 
 // slot table, per-tile counts and the tile bitmap of one row
@@ -381,7 +389,7 @@ __device__ __forceinline__ void analyse_row(const WalkArgs &a, long long lr, Wal
         }
         __syncwarp();
         if (sl < a.K) {
-            s.slot[sl] = valid ? (((unsigned)t << 16) | (unsigned)(base + before)) : kSlotUnused;
+            s.slot[sl] = valid ? (((unsigned)t << 16) | (unsigned)(base + before) | ((base + before) == 0 ? kSlotLeader : 0u)) : kSlotUnused;
             s.col[sl] = (unsigned short)c;
         }
     }
@@ -401,6 +409,48 @@ struct GroupGeom {
     __device__ unsigned flag(int i, int k) const { return ((k == 1 && start(i)) || (k == 2 && take1(i)) || (k == 3 && take2(i))) ? 0x8000u : 0u; }
 };
 
+// Where the entries of a group go when the caller asks for placement by bank pair (off by default, see
+// blocked_attractive_build).  A group's entries may stand in any order.  The kernel's k-th gather of a warp
+// reads the k-th entry of all 32 lanes, 16 lanes per shared-memory pass, and a pass costs as many cycles as its
+// most loaded pair of banks (a float2 at column c lies in bank pair c mod 16): random columns cost 5.6 cycles
+// per gather where 2 would do.  The stream of a tile is written front to back by one warp, so the builder keeps,
+// per tile, the bank pairs already taken in each of the four passes of the current half-warp window, and gives
+// every entry the first free cell of its group whose pass does not have the entry's bank pair yet (else the
+// first free cell).  Groups of more than 32 entries keep the slot order.  Returns the cells taken (bit per cell).
+__device__ __forceinline__ unsigned place_group(WalkScratch &s, int K, int t, int cnt, long long first_lane)
+{
+    const int n_lanes = (cnt + 3) >> 2;
+    const int w0 = (int)(first_lane >> 4);
+    if (s.win_id[t] != w0) {       // the cursor moved on: the window after the old one becomes the current one, or both start empty
+        s.win[t][0] = (s.win_id[t] + 1 == w0) ? s.win[t][1] : 0ull;
+        s.win[t][1] = 0ull;
+        s.win_id[t] = w0;
+    }
+    unsigned long long m0 = s.win[t][0], m1 = s.win[t][1];
+    unsigned used = 0u;
+    for (int sl = 0; sl < K; sl++) {
+        const unsigned info = s.slot[sl];
+        if (info == kSlotUnused || slot_tile(info) != t) continue;
+        const int b = s.col[sl] & 15;
+        int cell = -1;
+        for (int l = 0; l < n_lanes && cell < 0; l++) {
+            const unsigned long long m = (((first_lane + l) >> 4) == w0) ? m0 : m1;
+            for (int k = 0; k < 4; k++) {
+                const int c = 4 * l + k;
+                if (!((used >> c) & 1u) && !((m >> (16 * k + b)) & 1ull)) { cell = c; break; }
+            }
+        }
+        if (cell < 0) cell = __ffs(~used) - 1;
+        used |= 1u << cell;
+        const unsigned long long bit = 1ull << (16 * (cell & 3) + b);
+        if (((first_lane + (cell >> 2)) >> 4) == w0) m0 |= bit; else m1 |= bit;
+        s.slot[sl] = (info & 0xffff0000u) | (unsigned)cell;
+    }
+    s.win[t][0] = m0;
+    s.win[t][1] = m1;
+    return used;
+}
+
 // FILL = false: add the row's groups to run[] (sizes) and count them.  FILL = true: write the row's entries.
 template <bool FILL>
 __device__ __forceinline__ void emit_row(const WalkArgs &a, long long lr, WalkScratch &s, const unsigned *prev, int lane,
@@ -409,11 +459,44 @@ __device__ __forceinline__ void emit_row(const WalkArgs &a, long long lr, WalkSc
 {
     const long long r = (long long)a.own_perm[lr] - a.row_lo;
     if (FILL) {
+        // every group's first slot places the group's entries and writes what no entry owns
+        for (int k0 = 0; k0 < a.K; k0 += 32) {
+            const int sl = k0 + lane;
+            const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
+            if (info == kSlotUnused || !(info & kSlotLeader)) continue;
+            const int t = slot_tile(info);
+            const int cnt = s.rowcnt[t];
+            const int marker = ((prev[t >> 5] >> (t & 31)) & 1u) ? 0 : 1;
+            const long long gs = s.run[t];
+            GroupGeom g;
+            g.lane0 = gs >> 2;
+            g.n_lanes = marker + ((cnt + 3) >> 2);
+            unsigned used = (cnt >= 32) ? 0xffffffffu : ((1u << cnt) - 1u);      // slot order: the first cnt cells
+            if (cnt <= 32 && a.greedy) used = place_group(s, a.K, t, cnt, g.lane0 + marker);
+            if (marker) {
+                ev[gs] = __int_as_float((int)lr);
+                ec[gs] = 0xffffu;
+                for (int kk = 1; kk < 4; kk++) ec[gs + kk] = (uint16_t)g.flag(0, kk);
+                atomicOr(reinterpret_cast<unsigned *>(chunk_row0) + gs / kChunk, 0x80000000u);   // "this chunk holds a marker"
+            }
+            // cells without an entry (value 0, column 0) still carry their lane's flags
+            const int n_cells = 4 * ((cnt + 3) >> 2);
+            const bool placed = cnt <= 32 && a.greedy;
+            for (int c = (placed ? 0 : cnt); c < n_cells; c++) {
+                if (placed && ((used >> c) & 1u)) continue;
+                const int i = marker + (c >> 2), k = c & 3;
+                ec[gs + 4 * marker + c] = (uint16_t)(k == 0 ? ((c == 0 && !marker) ? 0x8000u : 0u) : g.flag(i, k));
+            }
+            const int size = 4 * g.n_lanes;
+            for (long long mm = (gs + kChunk - 1) / kChunk * kChunk; mm < gs + size; mm += kChunk)
+                atomicOr(reinterpret_cast<unsigned *>(chunk_row0) + mm / kChunk, (unsigned)((mm == gs && !marker) ? (int)lr - 1 : (int)lr));
+        }
+        __syncwarp();
         for (int k0 = 0; k0 < a.K; k0 += 32) {
             const int sl = k0 + lane;
             const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
             if (info == kSlotUnused) continue;
-            const int t = info >> 16, x = info & 0xffffu;
+            const int t = slot_tile(info), x = info & 0xffffu;
             const int cnt = s.rowcnt[t];
             const int marker = ((prev[t >> 5] >> (t & 31)) & 1u) ? 0 : 1;
             const long long gs = s.run[t];
@@ -424,19 +507,6 @@ __device__ __forceinline__ void emit_row(const WalkArgs &a, long long lr, WalkSc
             const long long off = gs + 4 * marker + x;
             ev[off] = a.P_rows[r * a.K + sl];
             ec[off] = (uint16_t)(s.col[sl] | (k == 0 ? ((x == 0 && !marker) ? 0x8000u : 0u) : g.flag(i, k)));
-            if (x == 0) {   // the group's first slot also writes what no slot owns
-                if (marker) {
-                    ev[gs] = __int_as_float((int)lr);
-                    ec[gs] = 0xffffu;
-                    for (int kk = 1; kk < 4; kk++) ec[gs + kk] = (uint16_t)g.flag(0, kk);
-                    atomicOr(reinterpret_cast<unsigned *>(chunk_row0) + gs / kChunk, 0x80000000u);   // "this chunk holds a marker"
-                }
-                const int last = g.n_lanes - 1;                    // padding entries of the last lane carry its flags
-                for (int kk = max(1, cnt & 3 ? cnt & 3 : 4); kk < 4; kk++) ec[gs + 4 * last + kk] = (uint16_t)g.flag(last, kk);
-                const int size = 4 * g.n_lanes;
-                for (long long mm = (gs + kChunk - 1) / kChunk * kChunk; mm < gs + size; mm += kChunk)
-                    atomicOr(reinterpret_cast<unsigned *>(chunk_row0) + mm / kChunk, (unsigned)((mm == gs && !marker) ? (int)lr - 1 : (int)lr));
-            }
         }
         __syncwarp();
     }
@@ -444,8 +514,8 @@ __device__ __forceinline__ void emit_row(const WalkArgs &a, long long lr, WalkSc
     for (int k0 = 0; k0 < a.K; k0 += 32) {
         const int sl = k0 + lane;
         const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
-        if (info == kSlotUnused || (info & 0xffffu) != 0) continue;
-        const int t = info >> 16;
+        if (info == kSlotUnused || !(info & kSlotLeader)) continue;
+        const int t = slot_tile(info);
         const int marker = ((prev[t >> 5] >> (t & 31)) & 1u) ? 0 : 1;
         s.run[t] += ((s.rowcnt[t] + 3) & ~3) + 4 * marker;
         s.rowcnt[t] = 0;
@@ -469,6 +539,8 @@ walk_kernel(WalkArgs a, unsigned *__restrict__ range_size, const unsigned *__res
     for (int t = lane; t < a.ntiles; t += 32) {
         s.rowcnt[t] = 0;
         s.run[t] = FILL ? tile_start[t] + (long long)range_off[(size_t)t * a.n_ranges + range] : 0;
+        s.win_id[t] = -2;
+        s.win[t][0] = s.win[t][1] = 0ull;
     }
     s.bitmap[0][lane] = 0u;
     s.bitmap[1][lane] = 0u;
@@ -481,7 +553,7 @@ walk_kernel(WalkArgs a, unsigned *__restrict__ range_size, const unsigned *__res
         for (int k0 = 0; k0 < a.K; k0 += 32) {
             const int sl = k0 + lane;
             const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
-            if (info != kSlotUnused && (info & 0xffffu) == 0) s.rowcnt[info >> 16] = 0;
+            if (info != kSlotUnused && (info & kSlotLeader)) s.rowcnt[slot_tile(info)] = 0;
         }
         __syncwarp();
         cur = 1;
@@ -520,7 +592,7 @@ sample_kernel(WalkArgs a, long long n_samples, unsigned long long *__restrict__ 
         const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
         if (info == kSlotUnused) continue;
         entries++;
-        groups += (info & 0xffffu) == 0;
+        groups += (info & kSlotLeader) != 0;
     }
     groups = __reduce_add_sync(0xffffffffu, groups);
     entries = __reduce_add_sync(0xffffffffu, entries);
@@ -779,6 +851,10 @@ int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const flo
     WalkArgs a;
     a.P_rows = P_rows; a.ids_rows = ids_rows; a.pos = pos; a.own_perm = own_perm;
     a.N = N; a.row_lo = row_lo; a.rows = rows; a.K = K; a.T = T; a.ntiles = ntiles;
+    // Measured at N = 10^6, K = 90: placing by bank pair takes the kernel from 190 to 185 us per iteration and the
+    // set-up from 15 to 74 ms (one lane per group walks the group's entries): it pays from 12,000 iterations on, so
+    // it is off unless B200TSNE_ATTRACTIVE_PLACE=1 asks for it.
+    a.greedy = getenv("B200TSNE_ATTRACTIVE_PLACE") ? atoi(getenv("B200TSNE_ATTRACTIVE_PLACE")) : 0;
     a.range_rows = 64;
     while ((rows + a.range_rows - 1) / a.range_rows * ntiles > (1ll << 24)) a.range_rows *= 2;
     a.n_ranges = (rows + a.range_rows - 1) / a.range_rows;
