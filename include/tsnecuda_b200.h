@@ -166,6 +166,17 @@ int b200tsne_attractive(const float *P, const int32_t *ids, const float *Y, int6
 int b200tsne_attractive_blocked(const float *P, const int32_t *ids, const float *Y, int64_t N, int K, int64_t row_lo,
                                 int64_t row_hi, const float *X, int D, float *F, float *entries_per_group, int device);
 
+/* Attractive force under a TRULY symmetric P = (p + p^T) / 2N (opt-in; not what the reference computes).  The
+ * reference's fixed-width symmetrisation stores P_ij only where j is one of i's neighbours, so where j has i as a
+ * neighbour but not the other way round, row i never sees that edge (src/util/math_utils.cu:269-291).  Here every such
+ * edge also gets its mirror image, kept beside the fixed-width P as a variable-width list per row, and the force
+ * sums both.  p: conditional probabilities [N][K] as b200tsne_perplexity returns them; X ([N][D], may be NULL) orders
+ * the points for the blocked kernel.  Outputs besides F (2N floats SoA; all may be NULL): the fixed-width part
+ * P_fixed [N][K], the number of extra entries, their sum (fixed-width sum + extra sum = 1), and whether the blocked
+ * kernel ran.  No counterpart in the reference (a "next" row of the scope table: true symmetric P as an opt-in). */
+int b200tsne_attractive_symmetric(const float *p, const int32_t *ids, const float *Y, int64_t N, int K, const float *X, int D, float *F,
+                                  float *P_fixed, int64_t *extra_entries, float *extra_sum, int *blocked, int device);
+
 /* One FIt-SNE repulsive evaluation on a fixed Y: min/max, charges, spread, FFT convolution with
  * the squared-Cauchy kernel, gather, Z.  Frep: 2N floats SoA; Z = sum_i Z_i - N.
  * w_out / ytilde_out ([390][390][4]) may be NULL.
@@ -209,6 +220,10 @@ int b200tsne_session_get_state(b200tsne_session *s, float *Y, float *momentum, f
 int b200tsne_session_set_state(b200tsne_session *s, const float *Y, const float *momentum, const float *gains, int step);
 /* Download the owned rows of P / ids. */
 int b200tsne_session_get_affinities(b200tsne_session *s, float *P_rows, int32_t *ids_rows);
+/* Opt-in before b200tsne_session_affinities_from_points: build P truly symmetric (see b200tsne_attractive_symmetric).
+ * The environment variable B200TSNE_SYMMETRIC_P=1 does the same for every run, pymodule_tsne included.
+ * b200tsne_session_get_affinities still returns the fixed-width part. */
+int b200tsne_session_set_symmetric(b200tsne_session *s, int on);
 /* Which attractive kernel the session's loop runs: 1 = column-blocked copy of P (built with the affinities),
  * 0 = row-major P / ids.  entries_per_group (may be NULL): see b200tsne_attractive_blocked. */
 int b200tsne_session_attractive_mode(b200tsne_session *s, float *entries_per_group);

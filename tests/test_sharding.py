@@ -68,6 +68,28 @@ def _worker(rank, world, port, q):
         w = torch.from_numpy(cpu.spread(Y, mn, mx, lo, hi))
         dist.all_reduce(w)
         assert rel_l2(w.numpy(), cpu.spread(Y, mn, mx)) < 1e-5
+        # the same sum by slice owners (the peer-memory form from four ranks on): every rank sums its slice of the
+        # nodes over all ranks' partial grids in rank order and hands the slice to everybody; all ranks then hold
+        # bit-identical grids, and the normalisation follows from the summed grid without an exchange
+        part = cpu.spread(Y, mn, mx, lo, hi).reshape(-1, 4)
+        parts_w = [torch.zeros(part.shape, dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(parts_w, torch.from_numpy(part))
+        n_nodes = part.shape[0]
+        slice_len = (n_nodes + world - 1) // world
+        s_lo, s_hi = min(n_nodes, rank * slice_len), min(n_nodes, (rank + 1) * slice_len)
+        mine_w = np.zeros((slice_len, 4), np.float32)
+        acc = parts_w[0].numpy()[s_lo:s_hi].copy()
+        for r in range(1, world):
+            acc += parts_w[r].numpy()[s_lo:s_hi]
+        mine_w[:s_hi - s_lo] = acc
+        slices = [torch.zeros((slice_len, 4), dtype=torch.float32) for _ in range(world)]
+        dist.all_gather(slices, torch.from_numpy(mine_w))
+        w_slices = np.concatenate([t.numpy() for t in slices])[:n_nodes]
+        by_rank_order = parts_w[0].numpy().copy()
+        for r in range(1, world):
+            by_rank_order += parts_w[r].numpy()
+        assert np.array_equal(w_slices, by_rank_order)
+        assert rel_l2(w_slices, w.numpy().reshape(-1, 4)) < 1e-6
         yt = cpu.convolve(w.numpy(), mn, mx)
         Fr, zs, _ = cpu.gather(Y, mn, mx, yt, lo, hi)
         z = torch.tensor([zs], dtype=torch.float64)

@@ -53,6 +53,9 @@ SIGNATURES = {
     "b200tsne_symmetrize": (C.c_int, [_fp, _ip, _i64, C.c_int, _fp, C.c_int]),
     "b200tsne_attractive": (C.c_int, [_fp, _ip, _fp, _i64, C.c_int, _i64, _i64, _fp, C.c_int]),
     "b200tsne_attractive_blocked": (C.c_int, [_fp, _ip, _fp, _i64, C.c_int, _i64, _i64, _fp, C.c_int, _fp, _fp, C.c_int]),
+    "b200tsne_attractive_symmetric": (C.c_int, [_fp, _ip, _fp, _i64, C.c_int, _fp, C.c_int, _fp, _fp, C.POINTER(_i64), _fp,
+                                                 C.POINTER(C.c_int), C.c_int]),
+    "b200tsne_session_set_symmetric": (C.c_int, [C.c_void_p, C.c_int]),
     "b200tsne_session_attractive_mode": (C.c_int, [C.c_void_p, _fp]),
     "b200tsne_repulsive": (C.c_int, [_fp, _i64, _fp, _fp, _fp, _fp, C.c_int]),
     "b200tsne_apply_forces": (C.c_int, [_fp, _fp, _fp, _fp, _fp, C.c_float, C.c_float, C.c_float, C.c_float, _i64, C.c_int]),
@@ -173,6 +176,25 @@ def attractive_blocked(P, ids, Y, X=None, row_lo=0, row_hi=None, device=0):
         D = X.shape[1]
     check(lib.b200tsne_attractive_blocked(_f(P), _i(ids), _f(Y), N, K, row_lo, row_hi, _f(X), D, _f(F), C.byref(epg), device))
     return F, epg.value
+
+
+def attractive_symmetric(p, ids, Y, X=None, device=0):
+    """Force under the truly symmetric P = (p + p^T) / 2N.  Returns (F (2,N), P_fixed (N,K), number of extra entries,
+    their sum, 1 if the blocked kernel ran)."""
+    p = _c(p, np.float32)
+    ids = _c(ids, np.int32)
+    Y = _c(Y, np.float32)
+    N, K = p.shape
+    F = np.zeros((2, N), np.float32)
+    P = np.zeros((N, K), np.float32)
+    n_extra, s_extra, blocked = _i64(), C.c_float(), C.c_int()
+    D = 0
+    if X is not None:
+        X = _c(X, np.float32)
+        D = X.shape[1]
+    check(lib.b200tsne_attractive_symmetric(_f(p), _i(ids), _f(Y), N, K, _f(X), D, _f(F), _f(P), C.byref(n_extra), C.byref(s_extra),
+                                            C.byref(blocked), device))
+    return F, P, n_extra.value, s_extra.value, blocked.value
 
 
 def repulsive(Y, want_grids=False, device=0):
@@ -346,6 +368,10 @@ class Session(object):
     def exchange_mode(self):
         """0 single GPU, 1 NCCL collectives, 2 peer memory (see include/tsnecuda_b200.h)."""
         return lib.b200tsne_session_exchange_mode(self._h)
+
+    def set_symmetric(self, on=True):
+        """Before affinities_from_points: P truly symmetric, (p + p^T) / 2N, instead of the reference's fixed-width form."""
+        check(lib.b200tsne_session_set_symmetric(self._h, 1 if on else 0))
 
     def attractive_mode(self):
         """(1 if the loop uses the column-blocked copy of P else 0, sampled entries per row and tile)."""

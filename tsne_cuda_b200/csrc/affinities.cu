@@ -125,8 +125,87 @@ symmetrize_kernel(const float *__restrict__ p, const int32_t *__restrict__ ids, 
     }
 }
 
+// The entries the fixed-width P leaves out.  The fixed-width symmetrisation stores P_ij only where j is a neighbour
+// of i; where j has i as a neighbour but not the other way round, the reference drops P_ji's mirror image
+// (src/util/math_utils.cu:269-291).  A truly symmetric P = (p + p^T) / 2N has it: for every edge i -> j whose
+// reverse is missing, row j gets the extra entry (column i, p_j|i / 2N).
+// One warp per source row i (all N rows); PASS 0 counts the extra entries of the owned target rows, PASS 1 writes them
+// (order inside a row: as the atomics fall, which only reorders a row's sum).
+template <int PASS>
+__global__ void __launch_bounds__(kSymWarps * 32)
+reverse_only_kernel(const float *__restrict__ p, const int32_t *__restrict__ ids, long long N, int K, long long row_lo, long long row_hi,
+                    int *__restrict__ count, const int *__restrict__ ptr, int *__restrict__ cursor, int32_t *__restrict__ ext_ids,
+                    float *__restrict__ ext_val)
+{
+    const int lane = threadIdx.x & 31;
+    const long long i = (long long)blockIdx.x * kSymWarps + (threadIdx.x >> 5);
+    if (i >= N) return;
+    const double inv = 2.0 * (double)N;
+    for (int s0 = 0; s0 < K; s0 += 32) {
+        const int s_mine = s0 + lane;
+        int j_mine = -1;
+        float p_mine = 0.0f;
+        if (s_mine < K) {
+            j_mine = ids[i * K + s_mine];
+            p_mine = p[i * K + s_mine];
+        }
+        const int cnt = min(32, K - s0);
+        for (int t = 0; t < cnt; t++) {
+            const int j = __shfl_sync(0xffffffffu, j_mine, t);
+            if (j < row_lo || j >= row_hi || j == i) continue;          // not an owned target, or the point itself
+            const int32_t *rj = ids + (long long)j * K;
+            bool found = false;
+            for (int u = lane; u < K; u += 32) found |= rj[u] == (int32_t)i;
+            if (__any_sync(0xffffffffu, found)) continue;               // mutual: the fixed-width entry has both halves
+            if (lane == t) {
+                const long long r = j - row_lo;
+                if (PASS == 0) {
+                    atomicAdd(&count[r], 1);
+                } else {
+                    const int at = ptr[r] + atomicAdd(&cursor[r], 1);
+                    ext_ids[at] = (int32_t)i;
+                    ext_val[at] = (float)((double)p_mine / inv);
+                }
+            }
+        }
+    }
+}
+
 inline unsigned nblk(long long n, int t) { return (unsigned)((n + t - 1) / t); }
 }  // namespace
+
+// ptr: [rows + 1] ints (device), filled here; returns the number of extra entries in *count_host (synchronises st).
+int launch_reverse_only_count(const float *p_all, const int32_t *ids_all, int64_t N, int K, int64_t row_lo, int64_t row_hi, int *ptr,
+                              int64_t *count_host, cudaStream_t st)
+{
+    const long long rows = row_hi - row_lo;
+    *count_host = 0;
+    if (rows <= 0) return 0;
+    B200_CUDA(cudaMemsetAsync(ptr, 0, sizeof(int) * (rows + 1), st));
+    reverse_only_kernel<0><<<nblk(N, kSymWarps), kSymWarps * 32, 0, st>>>(p_all, ids_all, N, K, row_lo, row_hi, ptr, nullptr, nullptr, nullptr,
+                                                                          nullptr);
+    B200_CUDA(cudaGetLastError());
+    B200_TRY(launch_exclusive_scan_i32(ptr, rows + 1, st));
+    int total = 0;
+    B200_CUDA(cudaMemcpyAsync(&total, ptr + rows, sizeof(int), cudaMemcpyDeviceToHost, st));
+    B200_CUDA(cudaStreamSynchronize(st));
+    if (total < 0) { set_error("symmetric P: more than 2^31 reverse-only entries"); return -4; }
+    *count_host = total;
+    return 0;
+}
+
+// cursor: [rows] ints of scratch (device)
+int launch_reverse_only_fill(const float *p_all, const int32_t *ids_all, int64_t N, int K, int64_t row_lo, int64_t row_hi, const int *ptr,
+                             int *cursor, int32_t *ext_ids, float *ext_val, cudaStream_t st)
+{
+    const long long rows = row_hi - row_lo;
+    if (rows <= 0) return 0;
+    B200_CUDA(cudaMemsetAsync(cursor, 0, sizeof(int) * rows, st));
+    reverse_only_kernel<1><<<nblk(N, kSymWarps), kSymWarps * 32, 0, st>>>(p_all, ids_all, N, K, row_lo, row_hi, nullptr, ptr, cursor, ext_ids,
+                                                                          ext_val);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
 
 int launch_absmax(const float *v, int64_t n, unsigned int *max_enc, cudaStream_t st)
 {

@@ -101,7 +101,47 @@ attractive_long_rows_kernel(const float *__restrict__ P, const int32_t *__restri
     }
     if (lane == 0) F2[i] = make_float2(ax, ay);
 }
+// the rows' extra entries (variable width): one warp per row, added to what the fixed-width kernel wrote
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+attractive_extra_kernel(const int *__restrict__ ptr, const int32_t *__restrict__ ext_ids, const float *__restrict__ ext_val,
+                        const float2 *__restrict__ Y2, long long N, long long row_lo, long long n_rows, float2 *__restrict__ F2)
+{
+    const int lane = threadIdx.x & 31;
+    const long long r = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const long long i = row_lo + r;
+    const int lo = ptr[r], hi = ptr[r + 1];
+    if (lo == hi) return;
+    const float2 yi = __ldg(Y2 + i);
+    float ax = 0.0f, ay = 0.0f;
+    for (int e = lo + lane; e < hi; e += 32) {
+        const int j = __ldcs(ext_ids + e);
+        if ((unsigned long long)j < (unsigned long long)N) accumulate(yi, __ldg(Y2 + j), __ldcs(ext_val + e), ax, ay);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ax += __shfl_xor_sync(0xffffffffu, ax, o);
+        ay += __shfl_xor_sync(0xffffffffu, ay, o);
+    }
+    if (lane == 0) {
+        float2 f = F2[i];
+        f.x += ax;
+        f.y += ay;
+        F2[i] = f;
+    }
+}
 }  // namespace
+
+int launch_attractive_extra(const int *ptr, const int32_t *ext_ids, const float *ext_val, const float2 *Y2, int64_t N, int64_t row_lo,
+                            int64_t row_hi, float2 *F2, cudaStream_t st)
+{
+    const long long n_rows = row_hi - row_lo;
+    if (n_rows <= 0) return 0;
+    const unsigned blocks = (unsigned)((n_rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    attractive_extra_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(ptr, ext_ids, ext_val, Y2, N, row_lo, n_rows, F2);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
 
 int launch_attractive(const float *P_rows, const int32_t *ids_rows, const float2 *Y2, int64_t N, int K, int64_t row_lo,
                       int64_t row_hi, float2 *F2, cudaStream_t st)

@@ -354,24 +354,51 @@ struct WalkScratch {
 constexpr unsigned kSlotUnused = 0xffffffffu, kSlotLeader = 1u << 30;
 __device__ __forceinline__ int slot_tile(unsigned info) { return (info >> 16) & 0x3ffu; }
 
+// The rows come from one of two sources.  Fixed width (seg_row null): segment g is the row at local permuted
+// position g, its K slots at val / ids + (own_perm[g] - row_lo) * K.  Variable width: segment g is seg_len[g] <= kMaxK
+// slots at val / ids + seg_base[g] of row seg_row[g] (local permuted position; ascending; a long row is several
+// consecutive segments, rows without slots have none).
 struct WalkArgs {
-    const float *P_rows;           // [rows][K]
-    const int32_t *ids_rows;
+    const float *val;
+    const int32_t *ids;
+    const int32_t *seg_row;
+    const long long *seg_base;
+    const int *seg_len;
     const int32_t *pos;            // [N] point -> permuted position
     const int32_t *own_perm;       // [rows] local permuted position -> point
-    long long N, row_lo, rows;
-    int K, T, ntiles, range_rows;
+    long long N, row_lo, n_seg;
+    int K, T, ntiles, range_rows;  // range_rows: segments per range
     long long n_ranges;
     int greedy;                    // place a group's entries by bank pair (place_group) instead of in slot order
 };
+struct Segment {
+    long long lr, base;
+    int len;
+    bool force;                    // every group of the segment needs a marker: its row is not the previous segment's row + 1
+};
+__device__ __forceinline__ Segment get_segment(const WalkArgs &a, long long g)
+{
+    Segment sg;
+    if (!a.seg_row) {
+        sg.lr = g;
+        sg.base = ((long long)a.own_perm[g] - a.row_lo) * a.K;
+        sg.len = a.K;
+        sg.force = false;
+    } else {
+        sg.lr = a.seg_row[g];
+        sg.base = a.seg_base[g];
+        sg.len = a.seg_len[g];
+        sg.force = g == 0 || a.seg_row[g - 1] != sg.lr - 1;
+    }
+    return sg;
+}
 
 // slot table, per-tile counts and the tile bitmap of one row
-__device__ __forceinline__ void analyse_row(const WalkArgs &a, long long lr, WalkScratch &s, unsigned *bitmap, int lane)
+__device__ __forceinline__ void analyse_row(const WalkArgs &a, const Segment &sg, WalkScratch &s, unsigned *bitmap, int lane)
 {
-    const long long r = (long long)a.own_perm[lr] - a.row_lo;
-    for (int k0 = 0; k0 < a.K; k0 += 32) {
+    for (int k0 = 0; k0 < sg.len; k0 += 32) {
         const int sl = k0 + lane;
-        const int j = (sl < a.K) ? a.ids_rows[r * a.K + sl] : -1;
+        const int j = (sl < sg.len) ? a.ids[sg.base + sl] : -1;
         const bool valid = j >= 0 && (long long)j < a.N;
         int t = -1 - lane, c = 0;
         if (valid) {
@@ -388,7 +415,7 @@ __device__ __forceinline__ void analyse_row(const WalkArgs &a, long long lr, Wal
             if (before == 0 && base == 0) atomicOr(&bitmap[t >> 5], 1u << (t & 31));
         }
         __syncwarp();
-        if (sl < a.K) {
+        if (sl < sg.len) {
             s.slot[sl] = valid ? (((unsigned)t << 16) | (unsigned)(base + before) | ((base + before) == 0 ? kSlotLeader : 0u)) : kSlotUnused;
             s.col[sl] = (unsigned short)c;
         }
@@ -453,26 +480,27 @@ __device__ __forceinline__ unsigned place_group(WalkScratch &s, int K, int t, in
 
 // FILL = false: add the row's groups to run[] (sizes) and count them.  FILL = true: write the row's entries.
 template <bool FILL>
-__device__ __forceinline__ void emit_row(const WalkArgs &a, long long lr, WalkScratch &s, const unsigned *prev, int lane,
+__device__ __forceinline__ void emit_row(const WalkArgs &a, const Segment &sg, WalkScratch &s, const unsigned *prev, int lane,
                                          float *__restrict__ ev, uint16_t *__restrict__ ec, int *__restrict__ chunk_row0,
                                          unsigned long long &n_groups)
 {
-    const long long r = (long long)a.own_perm[lr] - a.row_lo;
+    const long long lr = sg.lr;
+    const int K = sg.len;
     if (FILL) {
         // every group's first slot places the group's entries and writes what no entry owns
-        for (int k0 = 0; k0 < a.K; k0 += 32) {
+        for (int k0 = 0; k0 < K; k0 += 32) {
             const int sl = k0 + lane;
-            const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
+            const unsigned info = (sl < K) ? s.slot[sl] : kSlotUnused;
             if (info == kSlotUnused || !(info & kSlotLeader)) continue;
             const int t = slot_tile(info);
             const int cnt = s.rowcnt[t];
-            const int marker = ((prev[t >> 5] >> (t & 31)) & 1u) ? 0 : 1;
+            const int marker = (!sg.force && ((prev[t >> 5] >> (t & 31)) & 1u)) ? 0 : 1;
             const long long gs = s.run[t];
             GroupGeom g;
             g.lane0 = gs >> 2;
             g.n_lanes = marker + ((cnt + 3) >> 2);
             unsigned used = (cnt >= 32) ? 0xffffffffu : ((1u << cnt) - 1u);      // slot order: the first cnt cells
-            if (cnt <= 32 && a.greedy) used = place_group(s, a.K, t, cnt, g.lane0 + marker);
+            if (cnt <= 32 && a.greedy) used = place_group(s, K, t, cnt, g.lane0 + marker);
             if (marker) {
                 ev[gs] = __int_as_float((int)lr);
                 ec[gs] = 0xffffu;
@@ -492,31 +520,31 @@ __device__ __forceinline__ void emit_row(const WalkArgs &a, long long lr, WalkSc
                 atomicOr(reinterpret_cast<unsigned *>(chunk_row0) + mm / kChunk, (unsigned)((mm == gs && !marker) ? (int)lr - 1 : (int)lr));
         }
         __syncwarp();
-        for (int k0 = 0; k0 < a.K; k0 += 32) {
+        for (int k0 = 0; k0 < K; k0 += 32) {
             const int sl = k0 + lane;
-            const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
+            const unsigned info = (sl < K) ? s.slot[sl] : kSlotUnused;
             if (info == kSlotUnused) continue;
             const int t = slot_tile(info), x = info & 0xffffu;
             const int cnt = s.rowcnt[t];
-            const int marker = ((prev[t >> 5] >> (t & 31)) & 1u) ? 0 : 1;
+            const int marker = (!sg.force && ((prev[t >> 5] >> (t & 31)) & 1u)) ? 0 : 1;
             const long long gs = s.run[t];
             GroupGeom g;
             g.lane0 = gs >> 2;
             g.n_lanes = marker + ((cnt + 3) >> 2);
             const int i = marker + (x >> 2), k = x & 3;
             const long long off = gs + 4 * marker + x;
-            ev[off] = a.P_rows[r * a.K + sl];
+            ev[off] = a.val[sg.base + sl];
             ec[off] = (uint16_t)(s.col[sl] | (k == 0 ? ((x == 0 && !marker) ? 0x8000u : 0u) : g.flag(i, k)));
         }
         __syncwarp();
     }
     // group leaders close the row: advance the tile's cursor, clear the row's count
-    for (int k0 = 0; k0 < a.K; k0 += 32) {
+    for (int k0 = 0; k0 < K; k0 += 32) {
         const int sl = k0 + lane;
-        const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
+        const unsigned info = (sl < K) ? s.slot[sl] : kSlotUnused;
         if (info == kSlotUnused || !(info & kSlotLeader)) continue;
         const int t = slot_tile(info);
-        const int marker = ((prev[t >> 5] >> (t & 31)) & 1u) ? 0 : 1;
+        const int marker = (!sg.force && ((prev[t >> 5] >> (t & 31)) & 1u)) ? 0 : 1;
         s.run[t] += ((s.rowcnt[t] + 3) & ~3) + 4 * marker;
         s.rowcnt[t] = 0;
         n_groups++;
@@ -545,24 +573,26 @@ walk_kernel(WalkArgs a, unsigned *__restrict__ range_size, const unsigned *__res
     s.bitmap[0][lane] = 0u;
     s.bitmap[1][lane] = 0u;
     __syncwarp();
-    const long long lr0 = range * a.range_rows, lr1 = min(a.rows, lr0 + (long long)a.range_rows);
+    const long long g0 = range * a.range_rows, g1 = min(a.n_seg, g0 + (long long)a.range_rows);
     unsigned long long n_groups = 0;
     int cur = 0;
-    if (lr0 > 0) {   // the tiles of the row before the range decide the first row's markers
-        analyse_row(a, lr0 - 1, s, s.bitmap[0], lane);
-        for (int k0 = 0; k0 < a.K; k0 += 32) {
+    if (g0 > 0) {   // the tiles of the segment before the range decide the first segment's markers
+        const Segment before = get_segment(a, g0 - 1);
+        analyse_row(a, before, s, s.bitmap[0], lane);
+        for (int k0 = 0; k0 < before.len; k0 += 32) {
             const int sl = k0 + lane;
-            const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
+            const unsigned info = (sl < before.len) ? s.slot[sl] : kSlotUnused;
             if (info != kSlotUnused && (info & kSlotLeader)) s.rowcnt[slot_tile(info)] = 0;
         }
         __syncwarp();
         cur = 1;
     }
-    for (long long lr = lr0; lr < lr1; lr++) {
+    for (long long g = g0; g < g1; g++) {
+        const Segment sg = get_segment(a, g);
         s.bitmap[cur][lane] = 0u;
         __syncwarp();
-        analyse_row(a, lr, s, s.bitmap[cur], lane);
-        emit_row<FILL>(a, lr, s, s.bitmap[cur ^ 1], lane, ev, ec, chunk_row0, n_groups);
+        analyse_row(a, sg, s, s.bitmap[cur], lane);
+        emit_row<FILL>(a, sg, s, s.bitmap[cur ^ 1], lane, ev, ec, chunk_row0, n_groups);
         cur ^= 1;
     }
     if (!FILL) {
@@ -584,12 +614,12 @@ sample_kernel(WalkArgs a, long long n_samples, unsigned long long *__restrict__ 
     for (int t = lane; t < a.ntiles; t += 32) s.rowcnt[t] = 0;
     s.bitmap[0][lane] = 0u;
     __syncwarp();
-    const long long lr = k * (a.rows / n_samples);
-    analyse_row(a, lr, s, s.bitmap[0], lane);
+    const Segment sg = get_segment(a, k * (a.n_seg / n_samples));
+    analyse_row(a, sg, s, s.bitmap[0], lane);
     unsigned groups = 0, entries = 0;
-    for (int k0 = 0; k0 < a.K; k0 += 32) {
+    for (int k0 = 0; k0 < sg.len; k0 += 32) {
         const int sl = k0 + lane;
-        const unsigned info = (sl < a.K) ? s.slot[sl] : kSlotUnused;
+        const unsigned info = (sl < sg.len) ? s.slot[sl] : kSlotUnused;
         if (info == kSlotUnused) continue;
         entries++;
         groups += (info & kSlotLeader) != 0;
@@ -805,12 +835,116 @@ attractive_blocked_kernel(BlockedStream b, const float2 *__restrict__ Yp, const 
 
 void BlockedAttractive::clear() { *this = BlockedAttractive(); }
 
-// Builds the blocked copy of the owned rows' fixed-width P.  perm (device, [N]; null = identity) is the order
-// of the points; persistent buffers come from `arena`.  On return b->ready says whether the copy was built;
-// it is not when the sampled rows average fewer than kMinEntriesPerGroup entries per (row, tile), when there
-// are too many tiles, or when K exceeds 1,024 - none of which is an error.
+int launch_exclusive_scan_i32(int *data, int64_t n, cudaStream_t st)
+{
+    if (n <= 0) return 0;
+    scan_inplace_kernel<<<1, 1024, 0, st>>>(data, (long long)n);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+namespace {
+// segments of a variable-width source: row at local permuted position lr has ptr[r + 1] - ptr[r] slots (r = own_perm[lr] - row_lo)
+__global__ void seg_count_kernel(const int *__restrict__ ptr, const int32_t *__restrict__ own_perm, long long row_lo, long long rows,
+                                 int *__restrict__ nseg)
+{
+    const long long lr = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (lr >= rows) return;
+    const long long r = own_perm[lr] - row_lo;
+    nseg[lr] = (ptr[r + 1] - ptr[r] + kMaxK - 1) / kMaxK;
+}
+__global__ void seg_fill_kernel(const int *__restrict__ ptr, const int32_t *__restrict__ own_perm, long long row_lo, long long rows,
+                                const int *__restrict__ seg_off, int32_t *__restrict__ seg_row, long long *__restrict__ seg_base,
+                                int *__restrict__ seg_len)
+{
+    const long long lr = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (lr >= rows) return;
+    const long long r = own_perm[lr] - row_lo;
+    const int lo = ptr[r], hi = ptr[r + 1];
+    int g = seg_off[lr];
+    for (int o = lo; o < hi; o += kMaxK, g++) {
+        seg_row[g] = (int32_t)lr;
+        seg_base[g] = o;
+        seg_len[g] = min(kMaxK, hi - o);
+    }
+}
+
+struct StreamOut {
+    float *ev = nullptr;
+    uint16_t *ec = nullptr;
+    int *chunk_row0 = nullptr, *tile_chunk0 = nullptr;
+    int C = 0;
+    int64_t E = 0, groups = 0;
+    float entries_per_group = 0.0f;
+    bool built = false;
+};
+
+// One stream from the source described in `a` (val / ids / segments, pos, own_perm, N, row_lo, K, T, ntiles filled in).
+// min_entries_per_group <= 0: build whatever the sample says.
+int build_stream(StreamOut *out, DeviceArena &arena, DeviceArena &tmp, WalkArgs a, float min_entries_per_group, cudaStream_t st)
+{
+    *out = StreamOut();
+    if (a.n_seg <= 0) return 0;
+    const int ntiles = a.ntiles;
+    // Measured at N = 10^6, K = 90: placing by bank pair takes the kernel from 190 to 185 us per iteration and the
+    // set-up from 15 to 74 ms (one lane per group walks the group's entries): it pays from 12,000 iterations on, so
+    // it is off unless B200TSNE_ATTRACTIVE_PLACE=1 asks for it.
+    a.greedy = getenv("B200TSNE_ATTRACTIVE_PLACE") ? atoi(getenv("B200TSNE_ATTRACTIVE_PLACE")) : 0;
+    a.range_rows = 64;
+    while ((a.n_seg + a.range_rows - 1) / a.range_rows * ntiles > (1ll << 24)) a.range_rows *= 2;
+    a.n_ranges = (a.n_seg + a.range_rows - 1) / a.range_rows;
+
+    unsigned long long *totals = nullptr, h_tot[5] = {0, 0, 0, 0, 0};
+    B200_TRY(tmp.alloc((void **)&totals, sizeof(h_tot)));
+    B200_CUDA(cudaMemsetAsync(totals, 0, sizeof(h_tot), st));
+    const long long n_samples = std::min<long long>(a.n_seg, 4096);
+    sample_kernel<<<(unsigned)((n_samples + kWalkWarps - 1) / kWalkWarps), kWalkWarps * 32, 0, st>>>(a, n_samples, totals);
+    B200_CUDA(cudaGetLastError());
+    B200_CUDA(cudaMemcpyAsync(h_tot, totals, sizeof(h_tot), cudaMemcpyDeviceToHost, st));
+    B200_CUDA(cudaStreamSynchronize(st));
+    out->entries_per_group = h_tot[1] ? (float)((double)h_tot[2] / (double)h_tot[1]) : 0.0f;
+    if (h_tot[1] == 0 || out->entries_per_group < min_entries_per_group) return 0;
+
+    unsigned *range_size = nullptr;
+    unsigned long long *tile_total = nullptr;
+    long long *tile_start = nullptr;
+    B200_TRY(tmp.alloc((void **)&range_size, sizeof(unsigned) * (size_t)ntiles * a.n_ranges));
+    B200_TRY(tmp.alloc((void **)&tile_total, sizeof(unsigned long long) * ntiles));
+    B200_TRY(tmp.alloc((void **)&tile_start, sizeof(long long) * (ntiles + 1)));
+    B200_TRY(arena.alloc((void **)&out->tile_chunk0, sizeof(int) * (ntiles + 1)));
+    const unsigned walk_blocks = (unsigned)((a.n_ranges + kWalkWarps - 1) / kWalkWarps);
+    walk_kernel<false><<<walk_blocks, kWalkWarps * 32, 0, st>>>(a, range_size, nullptr, nullptr, nullptr, nullptr, nullptr, totals);
+    tile_scan_kernel<<<ntiles, 1024, 0, st>>>(range_size, a.n_ranges, tile_total);
+    tile_layout_kernel<<<1, 1, 0, st>>>(tile_total, ntiles, tile_start, out->tile_chunk0, totals);
+    B200_CUDA(cudaGetLastError());
+    B200_CUDA(cudaMemcpyAsync(h_tot, totals, sizeof(h_tot), cudaMemcpyDeviceToHost, st));
+    B200_CUDA(cudaStreamSynchronize(st));
+    const long long E = (long long)h_tot[3];
+    if (E <= 0 || h_tot[4] || E / kChunk >= INT_MAX) return 0;
+    B200_TRY(arena.alloc((void **)&out->ev, sizeof(float) * E));
+    B200_TRY(arena.alloc((void **)&out->ec, sizeof(uint16_t) * E));
+    B200_TRY(arena.alloc((void **)&out->chunk_row0, sizeof(int) * (E / kChunk)));
+    B200_CUDA(cudaMemsetAsync(out->ev, 0, sizeof(float) * E, st));
+    B200_CUDA(cudaMemsetAsync(out->ec, 0, sizeof(uint16_t) * E, st));
+    B200_CUDA(cudaMemsetAsync(out->chunk_row0, 0, sizeof(int) * (E / kChunk), st));
+    walk_kernel<true><<<walk_blocks, kWalkWarps * 32, 0, st>>>(a, nullptr, range_size, tile_start, out->ev, out->ec, out->chunk_row0, totals);
+    B200_CUDA(cudaGetLastError());
+    B200_CUDA(cudaStreamSynchronize(st));   // the temporaries of the caller may go away
+    out->C = (int)(E / kChunk);
+    out->E = E;
+    out->groups = (int64_t)h_tot[0];
+    out->built = true;
+    return 0;
+}
+}  // namespace
+
+// Builds the blocked copy of the owned rows' fixed-width P and, with `extra`, a second stream from a variable-width
+// list of further entries of the same rows (the reverse-only edges of a truly symmetric P).  perm (device, [N];
+// null = identity) is the order of the points; persistent buffers come from `arena`.  On return b->ready says
+// whether the copy was built; it is not when the sampled rows average fewer than kMinEntriesPerGroup entries per
+// (row, tile), when there are too many tiles, or when K exceeds 1,024 - none of which is an error.
 int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const float *P_rows, const int32_t *ids_rows, int64_t N, int K,
-                             int64_t row_lo, int64_t row_hi, const int32_t *perm_in, cudaStream_t st)
+                             int64_t row_lo, int64_t row_hi, const int32_t *perm_in, const ExtraEntries *extra, cudaStream_t st)
 {
     b->clear();
     const int64_t rows = row_hi - row_lo;
@@ -849,62 +983,45 @@ int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const flo
     B200_CUDA(cudaGetLastError());
 
     WalkArgs a;
-    a.P_rows = P_rows; a.ids_rows = ids_rows; a.pos = pos; a.own_perm = own_perm;
-    a.N = N; a.row_lo = row_lo; a.rows = rows; a.K = K; a.T = T; a.ntiles = ntiles;
-    // Measured at N = 10^6, K = 90: placing by bank pair takes the kernel from 190 to 185 us per iteration and the
-    // set-up from 15 to 74 ms (one lane per group walks the group's entries): it pays from 12,000 iterations on, so
-    // it is off unless B200TSNE_ATTRACTIVE_PLACE=1 asks for it.
-    a.greedy = getenv("B200TSNE_ATTRACTIVE_PLACE") ? atoi(getenv("B200TSNE_ATTRACTIVE_PLACE")) : 0;
-    a.range_rows = 64;
-    while ((rows + a.range_rows - 1) / a.range_rows * ntiles > (1ll << 24)) a.range_rows *= 2;
-    a.n_ranges = (rows + a.range_rows - 1) / a.range_rows;
+    memset(&a, 0, sizeof(a));
+    a.val = P_rows; a.ids = ids_rows; a.pos = pos; a.own_perm = own_perm;
+    a.N = N; a.row_lo = row_lo; a.n_seg = rows; a.K = K; a.T = T; a.ntiles = ntiles;
+    StreamOut main_stream, extra_stream;
+    B200_TRY(build_stream(&main_stream, arena, tmp, a, forced ? 0.0f : kMinEntriesPerGroup, st));
+    b->entries_per_group = main_stream.entries_per_group;
+    if (!main_stream.built) return 0;
 
-    unsigned long long *totals = nullptr, h_tot[5] = {0, 0, 0, 0, 0};
-    B200_TRY(tmp.alloc((void **)&totals, sizeof(h_tot)));
-    B200_CUDA(cudaMemsetAsync(totals, 0, sizeof(h_tot), st));
-    const long long n_samples = std::min<long long>(rows, 4096);
-    sample_kernel<<<(unsigned)((n_samples + kWalkWarps - 1) / kWalkWarps), kWalkWarps * 32, 0, st>>>(a, n_samples, totals);
-    B200_CUDA(cudaGetLastError());
-    B200_CUDA(cudaMemcpyAsync(h_tot, totals, sizeof(h_tot), cudaMemcpyDeviceToHost, st));
-    B200_CUDA(cudaStreamSynchronize(st));
-    b->entries_per_group = h_tot[1] ? (float)((double)h_tot[2] / (double)h_tot[1]) : 0.0f;
-    if (h_tot[1] == 0 || (!forced && b->entries_per_group < kMinEntriesPerGroup)) return 0;
+    if (extra && extra->count > 0) {
+        // segments of at most kMaxK slots, in the order of the rows' local permuted positions
+        int *seg_off = nullptr, *seg_len = nullptr, h_last[2] = {0, 0};
+        int32_t *seg_row = nullptr;
+        long long *seg_base = nullptr;
+        const unsigned gR = (unsigned)((rows + 255) / 256);
+        B200_TRY(tmp.alloc((void **)&seg_off, sizeof(int) * (rows + 1)));
+        B200_CUDA(cudaMemsetAsync(seg_off, 0, sizeof(int) * (rows + 1), st));
+        seg_count_kernel<<<gR, 256, 0, st>>>(extra->ptr, own_perm, row_lo, rows, seg_off);
+        B200_TRY(launch_exclusive_scan_i32(seg_off, rows + 1, st));
+        B200_CUDA(cudaMemcpyAsync(h_last, seg_off + rows, sizeof(int), cudaMemcpyDeviceToHost, st));
+        B200_CUDA(cudaStreamSynchronize(st));
+        const long long n_seg = h_last[0];
+        B200_TRY(tmp.alloc((void **)&seg_row, sizeof(int32_t) * std::max<long long>(n_seg, 1)));
+        B200_TRY(tmp.alloc((void **)&seg_base, sizeof(long long) * std::max<long long>(n_seg, 1)));
+        B200_TRY(tmp.alloc((void **)&seg_len, sizeof(int) * std::max<long long>(n_seg, 1)));
+        seg_fill_kernel<<<gR, 256, 0, st>>>(extra->ptr, own_perm, row_lo, rows, seg_off, seg_row, seg_base, seg_len);
+        B200_CUDA(cudaGetLastError());
+        WalkArgs e = a;
+        e.val = extra->val; e.ids = extra->ids;
+        e.seg_row = seg_row; e.seg_base = seg_base; e.seg_len = seg_len; e.n_seg = n_seg;
+        B200_TRY(build_stream(&extra_stream, arena, tmp, e, 0.0f, st));
+        if (!extra_stream.built) { set_error("attractive: the stream of the reverse-only entries could not be built"); return -4; }
+    }
 
-    unsigned *range_size = nullptr;
-    unsigned long long *tile_total = nullptr;
-    long long *tile_start = nullptr;
-    int *tile_chunk0 = nullptr;
-    B200_TRY(tmp.alloc((void **)&range_size, sizeof(unsigned) * (size_t)ntiles * a.n_ranges));
-    B200_TRY(tmp.alloc((void **)&tile_total, sizeof(unsigned long long) * ntiles));
-    B200_TRY(tmp.alloc((void **)&tile_start, sizeof(long long) * (ntiles + 1)));
-    B200_TRY(arena.alloc((void **)&tile_chunk0, sizeof(int) * (ntiles + 1)));
-    const unsigned walk_blocks = (unsigned)((a.n_ranges + kWalkWarps - 1) / kWalkWarps);
-    walk_kernel<false><<<walk_blocks, kWalkWarps * 32, 0, st>>>(a, range_size, nullptr, nullptr, nullptr, nullptr, nullptr, totals);
-    tile_scan_kernel<<<ntiles, 1024, 0, st>>>(range_size, a.n_ranges, tile_total);
-    tile_layout_kernel<<<1, 1, 0, st>>>(tile_total, ntiles, tile_start, tile_chunk0, totals);
-    B200_CUDA(cudaGetLastError());
-    B200_CUDA(cudaMemcpyAsync(h_tot, totals, sizeof(h_tot), cudaMemcpyDeviceToHost, st));
-    B200_CUDA(cudaStreamSynchronize(st));
-    const long long E = (long long)h_tot[3];
-    if (E <= 0 || h_tot[4] || E / kChunk >= INT_MAX) return 0;
-
-    float *ev = nullptr;
-    uint16_t *ec = nullptr;
-    int *chunk_row0 = nullptr;
     float2 *Yp = nullptr, *Yown = nullptr, *Fp = nullptr;
-    B200_TRY(arena.alloc((void **)&ev, sizeof(float) * E));
-    B200_TRY(arena.alloc((void **)&ec, sizeof(uint16_t) * E));
-    B200_TRY(arena.alloc((void **)&chunk_row0, sizeof(int) * (E / kChunk)));
     B200_TRY(arena.alloc((void **)&Yp, sizeof(float2) * (size_t)ntiles * T));
     if (rows == N) Yown = Yp;
     else B200_TRY(arena.alloc((void **)&Yown, sizeof(float2) * rows));
     B200_TRY(arena.alloc((void **)&Fp, sizeof(float2) * rows));
-    B200_CUDA(cudaMemsetAsync(ev, 0, sizeof(float) * E, st));
-    B200_CUDA(cudaMemsetAsync(ec, 0, sizeof(uint16_t) * E, st));
-    B200_CUDA(cudaMemsetAsync(chunk_row0, 0, sizeof(int) * (E / kChunk), st));
     B200_CUDA(cudaMemsetAsync(Yp, 0, sizeof(float2) * (size_t)ntiles * T, st));
-    walk_kernel<true><<<walk_blocks, kWalkWarps * 32, 0, st>>>(a, nullptr, range_size, tile_start, ev, ec, chunk_row0, totals);
-    B200_CUDA(cudaGetLastError());
     static bool attr_set[64] = {false};
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
@@ -914,21 +1031,32 @@ int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const flo
     }
     B200_CUDA(cudaStreamSynchronize(st));   // the temporaries go away with `tmp`
 
-    b->ev = ev; b->ec = ec; b->chunk_row0 = chunk_row0; b->tile_chunk0 = tile_chunk0;
+    b->ev = main_stream.ev; b->ec = main_stream.ec; b->chunk_row0 = main_stream.chunk_row0; b->tile_chunk0 = main_stream.tile_chunk0;
+    b->C = main_stream.C; b->E = main_stream.E; b->groups = main_stream.groups;
+    b->extra_ev = extra_stream.ev; b->extra_ec = extra_stream.ec; b->extra_chunk_row0 = extra_stream.chunk_row0;
+    b->extra_tile_chunk0 = extra_stream.tile_chunk0; b->extra_C = extra_stream.C; b->extra_E = extra_stream.E;
     b->perm = perm; b->own_perm = own_perm; b->own_pos = own_pos;
     b->Yp = Yp; b->Yown = Yown; b->Fp = Fp;
-    b->ntiles = ntiles; b->T = T; b->C = (int)(E / kChunk); b->E = E; b->groups = (int64_t)h_tot[0];
+    b->ntiles = ntiles; b->T = T;
     b->N = N; b->row_lo = row_lo; b->rows = rows;
     b->ready = true;
     return 0;
 }
 
 // F2[row_lo + r] = attractive force of the owned rows on the embedding Y2 (three launches)
-int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st)
+int blocked_refresh_embedding(const BlockedAttractive &b, const float2 *Y2, cudaStream_t st)
 {
-    if (!b.ready) { set_error("attractive: the blocked copy of P was not built"); return -1; }
+    if (!b.ready) return 0;
     const unsigned gN = (unsigned)((std::max(b.N, b.rows) + 255) / 256);
     permute_kernel<<<gN, 256, 0, st>>>(Y2, b.perm, b.N, b.Yp, b.own_perm, b.rows, b.Yown, b.Fp);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st, bool convert)
+{
+    if (!b.ready) { set_error("attractive: the blocked copy of P was not built"); return -1; }
+    if (convert) B200_TRY(blocked_refresh_embedding(b, Y2, st));
     BlockedStream s;
     s.ev = b.ev; s.ec = b.ec; s.chunk_row0 = b.chunk_row0; s.tile_chunk0 = b.tile_chunk0;
     s.ntiles = b.ntiles; s.T = b.T; s.C = b.C;
@@ -950,7 +1078,13 @@ int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, floa
     sms = want_blocks > 0 ? std::min(sms, want_blocks) : sms - sms / 9;
     const int grid = std::max(1, std::min(sms, b.C));
     attractive_blocked_kernel<<<grid, kBlockedThreads, (size_t)b.T * sizeof(float2), st>>>(s, b.Yp, b.Yown, b.N, b.Fp);
-    unpermute_kernel<<<(unsigned)((b.rows + 255) / 256), 256, 0, st>>>(b.Fp, b.own_pos, b.row_lo, b.rows, F2);
+    if (b.extra_C > 0) {   // the reverse-only entries of a truly symmetric P add to the same forces
+        BlockedStream x = s;
+        x.ev = b.extra_ev; x.ec = b.extra_ec; x.chunk_row0 = b.extra_chunk_row0; x.tile_chunk0 = b.extra_tile_chunk0; x.C = b.extra_C;
+        attractive_blocked_kernel<<<std::max(1, std::min(sms, b.extra_C)), kBlockedThreads, (size_t)b.T * sizeof(float2), st>>>(x, b.Yp, b.Yown, b.N,
+                                                                                                                          b.Fp);
+    }
+    if (convert) unpermute_kernel<<<(unsigned)((b.rows + 255) / 256), 256, 0, st>>>(b.Fp, b.own_pos, b.row_lo, b.rows, F2);
     B200_CUDA(cudaGetLastError());
     return 0;
 }

@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <new>
 #include <string>
+#include <vector>
 
 #include "../../include/tsnecuda_b200.h"
 #include "comm.h"
@@ -198,7 +199,7 @@ int b200tsne_attractive_blocked(const float *P, const int32_t *ids, const float 
     B200_CUDA(cudaMemsetAsync(dF2, 0, sizeof(float2) * N, sg.st));
     B200_TRY(launch_soa_to_aos(dY, dY2, N, sg.st));
     BlockedAttractive blk;
-    B200_TRY(blocked_attractive_build(&blk, a, dP, di, N, K, row_lo, row_hi, perm, sg.st));
+    B200_TRY(blocked_attractive_build(&blk, a, dP, di, N, K, row_lo, row_hi, perm, nullptr, sg.st));
     if (entries_per_group) *entries_per_group = blk.entries_per_group;
     if (!blk.ready) {
         set_error("b200tsne_attractive_blocked: the blocked copy was not built for this graph (entries per row and tile: " +
@@ -209,6 +210,77 @@ int b200tsne_attractive_blocked(const float *P, const int32_t *ids, const float 
     B200_TRY(launch_aos_to_soa(dF2, dF, N, sg.st));
     B200_TRY(down(F, dF, (size_t)2 * N, sg.st));
     B200_CUDA(cudaStreamSynchronize(sg.st));
+    return 0;
+}
+
+int b200tsne_attractive_symmetric(const float *p, const int32_t *ids, const float *Y, int64_t N, int K, const float *X, int D, float *F,
+                                  float *P_fixed, int64_t *extra_entries, float *extra_sum, int *blocked, int device)
+{
+    if (!p || !ids || !Y || !F || N <= 0 || K <= 0 || (X && D <= 0)) {
+        set_error("b200tsne_attractive_symmetric: invalid arguments");
+        return B200TSNE_ERR_INVALID;
+    }
+    B200_TRY(check_device(device));
+    StreamGuard sg;
+    B200_TRY(sg.create());
+    DeviceArena a;
+    a.serve(sg.st);
+    float *dp = nullptr, *dP = nullptr, *dY = nullptr, *dF = nullptr, *dX = nullptr, *ext_val = nullptr;
+    float2 *dY2 = nullptr, *dF2 = nullptr;
+    int32_t *di = nullptr, *perm = nullptr, *ext_ids = nullptr;
+    int *ptr = nullptr, *cursor = nullptr;
+    const size_t nk = (size_t)N * K;
+    B200_TRY(up(a, &dp, p, nk, sg.st));
+    B200_TRY(up(a, &di, ids, nk, sg.st));
+    B200_TRY(up(a, &dY, Y, (size_t)2 * N, sg.st));
+    B200_TRY(a.alloc((void **)&dP, sizeof(float) * nk));
+    B200_TRY(a.alloc((void **)&dY2, sizeof(float2) * N));
+    B200_TRY(a.alloc((void **)&dF2, sizeof(float2) * N));
+    B200_TRY(a.alloc((void **)&dF, sizeof(float) * 2 * N));
+    B200_TRY(a.alloc((void **)&ptr, sizeof(int) * (N + 1)));
+    B200_TRY(a.alloc((void **)&cursor, sizeof(int) * N));
+    B200_TRY(launch_symmetrize(dp, di, N, K, 0, N, dP, sg.st));
+    ExtraEntries extra;
+    B200_TRY(launch_reverse_only_count(dp, di, N, K, 0, N, ptr, &extra.count, sg.st));
+    B200_TRY(a.alloc((void **)&ext_ids, sizeof(int32_t) * std::max<int64_t>(extra.count, 1)));
+    B200_TRY(a.alloc((void **)&ext_val, sizeof(float) * std::max<int64_t>(extra.count, 1)));
+    B200_TRY(launch_reverse_only_fill(dp, di, N, K, 0, N, ptr, cursor, ext_ids, ext_val, sg.st));
+    extra.ptr = ptr; extra.ids = ext_ids; extra.val = ext_val;
+    if (X) {
+        B200_TRY(up(a, &dX, X, (size_t)N * D, sg.st));
+        B200_TRY(a.alloc((void **)&perm, sizeof(int32_t) * N));
+        B200_TRY(order_points_by_cell(dX, N, D, perm, sg.st));
+    }
+    B200_CUDA(cudaMemsetAsync(dF2, 0, sizeof(float2) * N, sg.st));
+    B200_TRY(launch_soa_to_aos(dY, dY2, N, sg.st));
+    BlockedAttractive blk;
+    B200_TRY(blocked_attractive_build(&blk, a, dP, di, N, K, 0, N, perm, extra.count > 0 ? &extra : nullptr, sg.st));
+    if (blocked) *blocked = blk.ready ? 1 : 0;
+    if (blk.ready) {
+        B200_TRY(launch_attractive_blocked(blk, dY2, dF2, sg.st));
+    } else {
+        B200_TRY(launch_attractive(dP, di, dY2, N, K, 0, N, dF2, sg.st));
+        if (extra.count > 0) B200_TRY(launch_attractive_extra(ptr, ext_ids, ext_val, dY2, N, 0, N, dF2, sg.st));
+    }
+    B200_TRY(launch_aos_to_soa(dF2, dF, N, sg.st));
+    B200_TRY(down(F, dF, (size_t)2 * N, sg.st));
+    if (P_fixed) B200_TRY(down(P_fixed, dP, nk, sg.st));
+    B200_CUDA(cudaStreamSynchronize(sg.st));
+    if (extra_entries) *extra_entries = extra.count;
+    if (extra_sum) {
+        std::vector<float> v((size_t)extra.count);
+        if (extra.count) B200_CUDA(cudaMemcpy(v.data(), ext_val, sizeof(float) * extra.count, cudaMemcpyDeviceToHost));
+        double t = 0.0;
+        for (float x : v) t += x;
+        *extra_sum = (float)t;
+    }
+    return 0;
+}
+
+int b200tsne_session_set_symmetric(b200tsne_session *h, int on)
+{
+    if (!h) { set_error("session_set_symmetric: null session"); return B200TSNE_ERR_INVALID; }
+    h->s.symmetric_p = on != 0;
     return 0;
 }
 

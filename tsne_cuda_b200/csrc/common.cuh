@@ -105,19 +105,39 @@ int launch_knn_finalize(int32_t *ids, float *d2, int64_t n, cudaStream_t st);
 int launch_absmax(const float *v, int64_t n, unsigned int *max_enc, cudaStream_t st);  // max_enc: enc_float accumulator, pre-set to enc(0)
 int launch_perplexity(const float *d2, int64_t n_rows, int K, float perplexity, float eps, const unsigned int *max_enc,
                       float *p, float *betas, cudaStream_t st);
+int launch_reverse_only_count(const float *p_all, const int32_t *ids_all, int64_t N, int K, int64_t row_lo, int64_t row_hi, int *ptr,
+                              int64_t *count_host, cudaStream_t st);
+int launch_reverse_only_fill(const float *p_all, const int32_t *ids_all, int64_t N, int K, int64_t row_lo, int64_t row_hi, const int *ptr,
+                             int *cursor, int32_t *ext_ids, float *ext_val, cudaStream_t st);
 int launch_symmetrize(const float *p_all, const int32_t *ids_all, int64_t N, int K, int64_t row_lo, int64_t row_hi,
                       float *P_rows, cudaStream_t st);
 
 // attractive.cu   (Y2: AoS float2 [N]; F2: AoS float2, rows [row_lo,row_hi) written at their global index)
 int launch_attractive(const float *P_rows, const int32_t *ids_rows, const float2 *Y2, int64_t N, int K, int64_t row_lo,
                       int64_t row_hi, float2 *F2, cudaStream_t st);
+// F2[row] += force of the rows' extra entries (variable-width list, see ExtraEntries below)
+int launch_attractive_extra(const int *ptr, const int32_t *ext_ids, const float *ext_val, const float2 *Y2, int64_t N, int64_t row_lo,
+                            int64_t row_hi, float2 *F2, cudaStream_t st);
 
 // attractive_blocked.cu: column-blocked copy of P whose gathers come from shared memory (see that file)
 struct DeviceArena;
+// Further stored entries of the owned rows in variable-width form: row r (0-based among the owned rows) has the
+// entries ptr[r] .. ptr[r + 1].  Used for the reverse-only edges that make P truly symmetric (affinities.cu).
+struct ExtraEntries {
+    const int *ptr = nullptr;        // [rows + 1]
+    const int32_t *ids = nullptr;    // columns (point numbers)
+    const float *val = nullptr;
+    int64_t count = 0;
+};
 struct BlockedAttractive {
     const float *ev = nullptr;
     const uint16_t *ec = nullptr;
     const int *chunk_row0 = nullptr, *tile_chunk0 = nullptr;
+    const float *extra_ev = nullptr;       // second stream: the extra entries (none: extra_C = 0)
+    const uint16_t *extra_ec = nullptr;
+    const int *extra_chunk_row0 = nullptr, *extra_tile_chunk0 = nullptr;
+    int extra_C = 0;
+    int64_t extra_E = 0;
     const int32_t *perm = nullptr, *own_perm = nullptr, *own_pos = nullptr;
     float2 *Yp = nullptr, *Yown = nullptr, *Fp = nullptr;
     int ntiles = 0, T = 0, C = 0;
@@ -128,8 +148,11 @@ struct BlockedAttractive {
 };
 int order_points_by_cell(const float *X, int64_t N, int D, int32_t *perm, cudaStream_t st);
 int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const float *P_rows, const int32_t *ids_rows, int64_t N, int K,
-                             int64_t row_lo, int64_t row_hi, const int32_t *perm, cudaStream_t st);
-int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st);
+                             int64_t row_lo, int64_t row_hi, const int32_t *perm, const ExtraEntries *extra, cudaStream_t st);
+int launch_exclusive_scan_i32(int *data, int64_t n, cudaStream_t st);   // in place; small arrays (one block)
+// convert = false: the kernel(s) only; the caller keeps b.Yp current and reads and clears b.Fp itself (update kernel)
+int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st, bool convert = true);
+int blocked_refresh_embedding(const BlockedAttractive &b, const float2 *Y2, cudaStream_t st);   // Yp from Y2, Fp = 0
 
 // repulsive.cu
 struct FftWorkspace {
@@ -161,9 +184,12 @@ struct UpdateTargets {
     float2 *p[kMaxUpdateTargets];
     int n;
 };
+// cell_pos (null = off): single GPU with the blocked attractive kernel; the attractive force is read from (and cleared in)
+// Fattr_cell[cell_pos[r]] and the new coordinates also go to Y_cell[cell_pos[r]]
 int launch_update(const float2 *Y2, const UpdateTargets &dst, const float2 *Fattr2, const float2 *Frep2, float2 *gains2, float2 *u2,
                   int64_t N, int64_t row_lo, int64_t row_hi, IterState *state, int slot, float eta, float momentum,
-                  float exaggeration, int want_norm, cudaStream_t st);
+                  float exaggeration, int want_norm, cudaStream_t st, const int32_t *cell_pos = nullptr, float2 *Fattr_cell = nullptr,
+                  float2 *Y_cell = nullptr);
 int launch_apply_forces_soa(float *Y, float *attr, float *rep, float *gains, float *old_forces, float eta, float Z,
                             float momentum, float exaggeration, int64_t N, cudaStream_t st);
 int launch_soa_to_aos(const float *soa, float2 *aos, int64_t N, cudaStream_t st);

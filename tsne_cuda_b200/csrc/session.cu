@@ -187,6 +187,7 @@ int Session::set_embedding_soa(const float *Y_host, bool reset)
     B200_TRY(launch_state_reset(state, stream));
     B200_TRY(launch_minmax_init(Y2, N, state, step & 1, stream));
     B200_CUDA(cudaMemsetAsync(w, 0, sizeof(float4) * kG * kG, stream));
+    if (fused_order()) B200_TRY(blocked_refresh_embedding(blocked, Y2, stream));   // the loop keeps it current from here on
     B200_CUDA(cudaStreamSynchronize(stream));
     launches += 4;
     return 0;
@@ -288,7 +289,7 @@ int Session::one_iteration(bool want_norm)
         B200_CUDA(cudaStreamWaitEvent(stream2, ev_fork, 0));
         B200_TRY(attractive(sa));
         B200_CUDA(cudaEventRecord(ev_join, stream2));
-        launches += blocked.ready ? 3 : 1;
+        launches += attractive_launches();
     }
 
     // The embedding reshuffles quickly while it is being exaggerated and slowly afterwards: sort every
@@ -341,7 +342,7 @@ int Session::one_iteration(bool want_norm)
     if (stage_timers) {
         clk.begin(stream);
         B200_TRY(attractive(stream));
-        clk.end(stream, kStAttractive, blocked.ready ? 3 : 1);
+        clk.end(stream, kStAttractive, attractive_launches());
     } else {
         B200_CUDA(cudaStreamWaitEvent(stream, ev_join, 0));
     }
@@ -353,8 +354,10 @@ int Session::one_iteration(bool want_norm)
         dst.n = comm->world;
         for (int r = 0; r < comm->world; r++) dst.p[r] = px->tab.y[px->parity ^ 1][r];
     }
+    const bool fused = fused_order();
     B200_TRY(launch_update(Y2, dst, Fattr, Frep, gains, u, N, row_lo, row_hi, state, slot, eta, momentum, exag,
-                           want_norm ? 1 : 0, stream));
+                           want_norm ? 1 : 0, stream, fused ? blocked.own_pos : nullptr, fused ? blocked.Fp : nullptr,
+                           fused ? blocked.Yp : nullptr));
     clk.end(stream, kStUpdate, 1);
     if (p2p) {
         clk.begin(stream);
@@ -375,10 +378,18 @@ int Session::one_iteration(bool want_norm)
     return 0;
 }
 
+bool Session::fused_order() const
+{
+    static const bool allowed = !(getenv("B200TSNE_FUSE_ORDER") && atoi(getenv("B200TSNE_FUSE_ORDER")) == 0);
+    return allowed && blocked.ready && !(comm && comm->world > 1) && blocked.rows == N;
+}
+
 int Session::attractive(cudaStream_t st)
 {
-    if (blocked.ready) return launch_attractive_blocked(blocked, Y2, Fattr, st);
-    return launch_attractive(P, ids, Y2, N, K, row_lo, row_hi, Fattr, st);
+    if (blocked.ready) return launch_attractive_blocked(blocked, Y2, Fattr, st, !fused_order());
+    B200_TRY(launch_attractive(P, ids, Y2, N, K, row_lo, row_hi, Fattr, st));
+    if (extra.count > 0) B200_TRY(launch_attractive_extra(extra.ptr, extra.ids, extra.val, Y2, N, row_lo, row_hi, Fattr, st));
+    return 0;
 }
 
 int Session::build_blocked()
@@ -390,7 +401,13 @@ int Session::build_blocked()
     blocked_arena.release();
     blocked_arena.serve(stream);
     blocked_arena.serve(stream2);
-    return blocked_attractive_build(&blocked, blocked_arena, P, ids, N, K, row_lo, row_hi, cell_order, stream);
+    B200_TRY(blocked_attractive_build(&blocked, blocked_arena, P, ids, N, K, row_lo, row_hi, cell_order, extra.count > 0 ? &extra : nullptr,
+                                      stream));
+    if (fused_order()) {
+        B200_TRY(blocked_refresh_embedding(blocked, Y2, stream));
+        B200_CUDA(cudaStreamSynchronize(stream));
+    }
+    return 0;
 }
 
 void Session::drop_graphs()
@@ -624,6 +641,19 @@ int Session::affinities_from_points(const float *X_host, int D, float perplexity
         ids_for_sym = ids_all;
     }
     B200_TRY(launch_symmetrize(p_all, ids_for_sym, N, K, row_lo, row_hi, P, stream));
+    extra = ExtraEntries();
+    if (symmetric_p || (getenv("B200TSNE_SYMMETRIC_P") && atoi(getenv("B200TSNE_SYMMETRIC_P")) != 0)) {
+        // the mirror images of the one-directional edges whose target is an owned row (affinities.cu)
+        int64_t n_extra = 0;
+        int *cursor = nullptr;
+        if (!extra_ptr) B200_TRY(arena.alloc((void **)&extra_ptr, sizeof(int) * (r + 1)));
+        B200_TRY(launch_reverse_only_count(p_all, ids_for_sym, N, K, row_lo, row_hi, extra_ptr, &n_extra, stream));
+        B200_TRY(tmp.alloc((void **)&cursor, sizeof(int) * std::max<int64_t>(r, 1)));
+        B200_TRY(arena.alloc((void **)&extra_ids, sizeof(int32_t) * std::max<int64_t>(n_extra, 1)));   // (a second call leaves the first lists to the arena)
+        B200_TRY(arena.alloc((void **)&extra_val, sizeof(float) * std::max<int64_t>(n_extra, 1)));
+        B200_TRY(launch_reverse_only_fill(p_all, ids_for_sym, N, K, row_lo, row_hi, extra_ptr, cursor, extra_ids, extra_val, stream));
+        extra.ptr = extra_ptr; extra.ids = extra_ids; extra.val = extra_val; extra.count = n_extra;
+    }
     B200_TRY(build_blocked());
     clk.end(stream, kStAffinities, 3);
     B200_CUDA(cudaStreamSynchronize(stream));

@@ -42,6 +42,13 @@ struct Session {
     DeviceArena blocked_arena;
     int32_t *cell_order = nullptr;   // [N] point order by cell (from the points; null = natural order)
     int build_blocked();             // (re)builds `blocked` from P / ids; drops captured iterations
+    // Opt-in: P truly symmetric, (p + p^T) / 2N, instead of the reference's fixed-width form that drops the mirror
+    // image of one-directional edges.  The extra entries of the owned rows live beside P / ids.
+    bool symmetric_p = false;
+    ExtraEntries extra;
+    int *extra_ptr = nullptr;
+    int32_t *extra_ids = nullptr;
+    float *extra_val = nullptr;
     // embedding and optimiser state
     float2 *Y2 = nullptr;     // [N] AoS, replicated on every rank
     float2 *Fattr = nullptr;  // [N] (owned rows valid)
@@ -114,6 +121,13 @@ struct Session {
     int iterate(int n_iters, float min_gradient_norm, float *elapsed_ms, int *iters_done);
     int one_iteration(bool want_norm);
     int attractive(cudaStream_t st);   // Fattr of the owned rows from the current embedding
+    // Single GPU with the blocked kernel: the update kernel reads the force in cell order and keeps the cell-ordered
+    // embedding current, so an iteration launches the blocked kernel(s) only (B200TSNE_FUSE_ORDER=0 keeps the conversions)
+    bool fused_order() const;
+    int attractive_launches() const
+    {
+        return blocked.ready ? (fused_order() ? 1 : 3) + (blocked.extra_C > 0) : 1 + (extra.count > 0);
+    }
     int affinities_from_points(const float *X_host, int D, float perplexity, float eps);
 };
 
