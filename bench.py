@@ -145,8 +145,9 @@ def run_ours(args):
     stages = s.stage_times()
     s.enable_stage_timers(False)
     stage_us = {k: v[0] / n_prof * 1e3 for k, v in stages.items() if v[1] > 0}
-    # the attractive stage of one iteration: the row-major kernel alone, or the blocked kernel with its two small
-    # companions (gather of the embedding into the cell order, scatter of the forces back), timed together
+    # the attractive stage of one iteration: the row-major kernel alone, or the blocked kernel - alone on one GPU, where
+    # the update kernel converts between point order and cell order, else with its two small companions (gather of the
+    # embedding into the cell order, scatter of the forces back), timed together
     attr_s = stages["attractive"][0] / n_prof * 1e-3
     rows = hi - lo
     attr_bytes = 8.0 * rows * K + 16.0 * rows
@@ -160,7 +161,7 @@ def run_ours(args):
             "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
             "traffic": attr_bytes * traffic_ratio, "entries_per_row_and_tile": entries_per_group,
             "algorithmic_bytes_per_launch": attr_bytes, "avg_launch_us": attr_s * 1e6,
-            "launches_timed_together": 3 if attr_mode else 1}
+            "launches_timed_together": int(round(stages["attractive"][1] / n_prof))}
     roof["frac"] = roof["achieved"] / peak if roof["achieved"] else None
     it_bytes = iter_bytes(N, K) / world
     roof["iteration"] = {"achieved": it_bytes / (ms * 1e-3 / args.steps) / 1e9, "frac": it_bytes / (ms * 1e-3 / args.steps) / 1e9 / peak,

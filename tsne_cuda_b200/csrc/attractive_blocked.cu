@@ -1044,19 +1044,14 @@ int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const flo
 }
 
 // F2[row_lo + r] = attractive force of the owned rows on the embedding Y2 (three launches)
-int blocked_refresh_embedding(const BlockedAttractive &b, const float2 *Y2, cudaStream_t st)
-{
-    if (!b.ready) return 0;
-    const unsigned gN = (unsigned)((std::max(b.N, b.rows) + 255) / 256);
-    permute_kernel<<<gN, 256, 0, st>>>(Y2, b.perm, b.N, b.Yp, b.own_perm, b.rows, b.Yown, b.Fp);
-    B200_CUDA(cudaGetLastError());
-    return 0;
-}
-
-int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st, bool convert)
+// (Reading the force in cell order from the update kernel and letting it keep the cell-ordered embedding current
+// instead of these two conversion kernels was measured on one GPU: the update kernel's three scattered 8-byte
+// accesses per point cost it 148 us more - 169 instead of 21 - against the 17 us the conversions take.)
+int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st)
 {
     if (!b.ready) { set_error("attractive: the blocked copy of P was not built"); return -1; }
-    if (convert) B200_TRY(blocked_refresh_embedding(b, Y2, st));
+    const unsigned gN = (unsigned)((std::max(b.N, b.rows) + 255) / 256);
+    permute_kernel<<<gN, 256, 0, st>>>(Y2, b.perm, b.N, b.Yp, b.own_perm, b.rows, b.Yown, b.Fp);
     BlockedStream s;
     s.ev = b.ev; s.ec = b.ec; s.chunk_row0 = b.chunk_row0; s.tile_chunk0 = b.tile_chunk0;
     s.ntiles = b.ntiles; s.T = b.T; s.C = b.C;
@@ -1084,7 +1079,7 @@ int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, floa
         attractive_blocked_kernel<<<std::max(1, std::min(sms, b.extra_C)), kBlockedThreads, (size_t)b.T * sizeof(float2), st>>>(x, b.Yp, b.Yown, b.N,
                                                                                                                           b.Fp);
     }
-    if (convert) unpermute_kernel<<<(unsigned)((b.rows + 255) / 256), 256, 0, st>>>(b.Fp, b.own_pos, b.row_lo, b.rows, F2);
+    unpermute_kernel<<<(unsigned)((b.rows + 255) / 256), 256, 0, st>>>(b.Fp, b.own_pos, b.row_lo, b.rows, F2);
     B200_CUDA(cudaGetLastError());
     return 0;
 }

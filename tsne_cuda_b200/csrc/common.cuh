@@ -150,9 +150,7 @@ int order_points_by_cell(const float *X, int64_t N, int D, int32_t *perm, cudaSt
 int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const float *P_rows, const int32_t *ids_rows, int64_t N, int K,
                              int64_t row_lo, int64_t row_hi, const int32_t *perm, const ExtraEntries *extra, cudaStream_t st);
 int launch_exclusive_scan_i32(int *data, int64_t n, cudaStream_t st);   // in place; small arrays (one block)
-// convert = false: the kernel(s) only; the caller keeps b.Yp current and reads and clears b.Fp itself (update kernel)
-int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st, bool convert = true);
-int blocked_refresh_embedding(const BlockedAttractive &b, const float2 *Y2, cudaStream_t st);   // Yp from Y2, Fp = 0
+int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st);
 
 // repulsive.cu
 struct FftWorkspace {
@@ -184,12 +182,9 @@ struct UpdateTargets {
     float2 *p[kMaxUpdateTargets];
     int n;
 };
-// cell_pos (null = off): single GPU with the blocked attractive kernel; the attractive force is read from (and cleared in)
-// Fattr_cell[cell_pos[r]] and the new coordinates also go to Y_cell[cell_pos[r]]
 int launch_update(const float2 *Y2, const UpdateTargets &dst, const float2 *Fattr2, const float2 *Frep2, float2 *gains2, float2 *u2,
                   int64_t N, int64_t row_lo, int64_t row_hi, IterState *state, int slot, float eta, float momentum,
-                  float exaggeration, int want_norm, cudaStream_t st, const int32_t *cell_pos = nullptr, float2 *Fattr_cell = nullptr,
-                  float2 *Y_cell = nullptr);
+                  float exaggeration, int want_norm, cudaStream_t st);
 int launch_apply_forces_soa(float *Y, float *attr, float *rep, float *gains, float *old_forces, float eta, float Z,
                             float momentum, float exaggeration, int64_t N, cudaStream_t st);
 int launch_soa_to_aos(const float *soa, float2 *aos, int64_t N, cudaStream_t st);

@@ -187,7 +187,6 @@ int Session::set_embedding_soa(const float *Y_host, bool reset)
     B200_TRY(launch_state_reset(state, stream));
     B200_TRY(launch_minmax_init(Y2, N, state, step & 1, stream));
     B200_CUDA(cudaMemsetAsync(w, 0, sizeof(float4) * kG * kG, stream));
-    if (fused_order()) B200_TRY(blocked_refresh_embedding(blocked, Y2, stream));   // the loop keeps it current from here on
     B200_CUDA(cudaStreamSynchronize(stream));
     launches += 4;
     return 0;
@@ -354,10 +353,8 @@ int Session::one_iteration(bool want_norm)
         dst.n = comm->world;
         for (int r = 0; r < comm->world; r++) dst.p[r] = px->tab.y[px->parity ^ 1][r];
     }
-    const bool fused = fused_order();
     B200_TRY(launch_update(Y2, dst, Fattr, Frep, gains, u, N, row_lo, row_hi, state, slot, eta, momentum, exag,
-                           want_norm ? 1 : 0, stream, fused ? blocked.own_pos : nullptr, fused ? blocked.Fp : nullptr,
-                           fused ? blocked.Yp : nullptr));
+                           want_norm ? 1 : 0, stream));
     clk.end(stream, kStUpdate, 1);
     if (p2p) {
         clk.begin(stream);
@@ -378,15 +375,9 @@ int Session::one_iteration(bool want_norm)
     return 0;
 }
 
-bool Session::fused_order() const
-{
-    static const bool allowed = !(getenv("B200TSNE_FUSE_ORDER") && atoi(getenv("B200TSNE_FUSE_ORDER")) == 0);
-    return allowed && blocked.ready && !(comm && comm->world > 1) && blocked.rows == N;
-}
-
 int Session::attractive(cudaStream_t st)
 {
-    if (blocked.ready) return launch_attractive_blocked(blocked, Y2, Fattr, st, !fused_order());
+    if (blocked.ready) return launch_attractive_blocked(blocked, Y2, Fattr, st);
     B200_TRY(launch_attractive(P, ids, Y2, N, K, row_lo, row_hi, Fattr, st));
     if (extra.count > 0) B200_TRY(launch_attractive_extra(extra.ptr, extra.ids, extra.val, Y2, N, row_lo, row_hi, Fattr, st));
     return 0;
@@ -401,13 +392,8 @@ int Session::build_blocked()
     blocked_arena.release();
     blocked_arena.serve(stream);
     blocked_arena.serve(stream2);
-    B200_TRY(blocked_attractive_build(&blocked, blocked_arena, P, ids, N, K, row_lo, row_hi, cell_order, extra.count > 0 ? &extra : nullptr,
-                                      stream));
-    if (fused_order()) {
-        B200_TRY(blocked_refresh_embedding(blocked, Y2, stream));
-        B200_CUDA(cudaStreamSynchronize(stream));
-    }
-    return 0;
+    return blocked_attractive_build(&blocked, blocked_arena, P, ids, N, K, row_lo, row_hi, cell_order, extra.count > 0 ? &extra : nullptr,
+                                    stream);
 }
 
 void Session::drop_graphs()

@@ -121,13 +121,7 @@ struct Session {
     int iterate(int n_iters, float min_gradient_norm, float *elapsed_ms, int *iters_done);
     int one_iteration(bool want_norm);
     int attractive(cudaStream_t st);   // Fattr of the owned rows from the current embedding
-    // Single GPU with the blocked kernel: the update kernel reads the force in cell order and keeps the cell-ordered
-    // embedding current, so an iteration launches the blocked kernel(s) only (B200TSNE_FUSE_ORDER=0 keeps the conversions)
-    bool fused_order() const;
-    int attractive_launches() const
-    {
-        return blocked.ready ? (fused_order() ? 1 : 3) + (blocked.extra_C > 0) : 1 + (extra.count > 0);
-    }
+    int attractive_launches() const { return blocked.ready ? 3 + (blocked.extra_C > 0) : 1 + (extra.count > 0); }
     int affinities_from_points(const float *X_host, int D, float perplexity, float eps);
 };
 

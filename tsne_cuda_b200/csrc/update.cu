@@ -34,16 +34,11 @@ __device__ __forceinline__ void step_point(float2 &y, const float2 fa, const flo
 // from state->zsum[slot] (sum of Z_i; Z = sum - n_total as in src/kernels/rep_forces.cu:51-54),
 // accumulates min/max of the new coordinates into slot^1 and clears zsum[slot^1] for the next
 // iteration's gather.
-//
-// CELL_ORDER (single GPU with the blocked attractive kernel): the attractive force arrives in the cell order of
-// that kernel (Fa_cell[cell_pos[r]], cleared here for the next iteration's reductions) and the new coordinates also
-// go to the cell-ordered copy of the embedding that kernel reads, which saves the two conversion kernels.
-template <bool CELL_ORDER>
 __global__ void __launch_bounds__(256)
 update_kernel(const float2 *Y2, UpdateTargets dst, const float2 *__restrict__ Fa, const float2 *__restrict__ Fr,
               float2 *__restrict__ gains, float2 *__restrict__ u2, long long row_lo, long long n_rows,
               long long n_total, IterState *state, int slot, float eta, float momentum, float exaggeration,
-              int want_norm, const int32_t *__restrict__ cell_pos, float2 *__restrict__ Fa_cell, float2 *__restrict__ Y_cell)
+              int want_norm)
 {
     const float Z = (float)state->zsum[slot] - (float)n_total;
     const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -52,21 +47,11 @@ update_kernel(const float2 *Y2, UpdateTargets dst, const float2 *__restrict__ Fa
     if (r < n_rows) {
         const long long i = row_lo + r;
         float2 y = Y2[i], g = gains[r], u = u2[r];
-        float2 fa;
-        int q = 0;
-        if (CELL_ORDER) {
-            q = cell_pos[r];
-            fa = Fa_cell[q];
-            Fa_cell[q] = make_float2(0.0f, 0.0f);
-        } else {
-            fa = __ldcs(Fa + i);
-        }
-        const float2 fr = __ldcs(Fr + i);
+        const float2 fa = __ldcs(Fa + i), fr = __ldcs(Fr + i);
         step_point(y, fa, fr, g, u, eta, Z, momentum, exaggeration);
 #pragma unroll
         for (int t = 0; t < kMaxUpdateTargets; t++)
             if (t < dst.n) dst.p[t][i] = y;
-        if (CELL_ORDER) Y_cell[q] = y;
         gains[r] = g;
         u2[r] = u;
         mn = fminf(y.x, y.y);
@@ -138,17 +123,13 @@ inline unsigned nblk(long long n, int t) { return (unsigned)((n + t - 1) / t); }
 
 int launch_update(const float2 *Y2, const UpdateTargets &dst, const float2 *Fattr2, const float2 *Frep2, float2 *gains2, float2 *u2,
                   int64_t N, int64_t row_lo, int64_t row_hi, IterState *state, int slot, float eta, float momentum,
-                  float exaggeration, int want_norm, cudaStream_t st, const int32_t *cell_pos, float2 *Fattr_cell, float2 *Y_cell)
+                  float exaggeration, int want_norm, cudaStream_t st)
 {
     const long long n_rows = row_hi - row_lo;
     // even an empty shard must run one block so that the state slots are recycled
     const unsigned blocks = n_rows > 0 ? nblk(n_rows, 256) : 1;
-    if (cell_pos)
-        update_kernel<true><<<blocks, 256, 0, st>>>(Y2, dst, Fattr2, Frep2, gains2, u2, row_lo, n_rows, N, state, slot, eta, momentum,
-                                                    exaggeration, want_norm, cell_pos, Fattr_cell, Y_cell);
-    else
-        update_kernel<false><<<blocks, 256, 0, st>>>(Y2, dst, Fattr2, Frep2, gains2, u2, row_lo, n_rows, N, state, slot, eta, momentum,
-                                                     exaggeration, want_norm, nullptr, nullptr, nullptr);
+    update_kernel<<<blocks, 256, 0, st>>>(Y2, dst, Fattr2, Frep2, gains2, u2, row_lo, n_rows, N, state, slot, eta, momentum,
+                                          exaggeration, want_norm);
     B200_CUDA(cudaGetLastError());
     return 0;
 }
