@@ -24,11 +24,14 @@ def test_knn_bit_exact(engine, oracle_cpu, n, d, k):
     assert np.array_equal(d2, d2_o)
 
 
+@pytest.mark.parametrize("pairs", ["bf16", "tf32"])
 @pytest.mark.parametrize("n,d,k", [(3000, 50, 90), (70000, 30, 150), (420000, 50, 90)])
-def test_knn_tensor_core_paths(engine, oracle_cpu, n, d, k):
+def test_knn_tensor_core_paths(engine, oracle_cpu, monkeypatch, n, d, k, pairs):
     """Online threshold (small), sample -> full (medium) and sample -> strided -> full (large) variants of the
-    tensor-core search: exact on sampled queries, and the SIMT fallback is only needed for a few rows."""
+    tensor-core search, with both operand forms of the filter (bf16 pairs are the default): exact on sampled
+    queries, and the SIMT fallback is only needed for a few rows."""
     from tsne_cuda_b200 import datasets
+    monkeypatch.setenv("B200TSNE_KNN_FILTER", pairs)
     X = datasets.gaussian_mixture(n, d, seed=n)
     ids, d2 = engine.knn(X, k)
     st = engine.knn_last_stats()
@@ -65,11 +68,13 @@ def test_knn_tensor_core_windows_and_cells(engine, monkeypatch):
     assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
 
 
+@pytest.mark.parametrize("pairs", ["bf16", "tf32"])
 @pytest.mark.parametrize("n,d,k", [(20000, 100, 40), (30000, 784, 90), (17000, 65, 150)])
-def test_knn_tensor_core_wide_points(engine, monkeypatch, n, d, k):
+def test_knn_tensor_core_wide_points(engine, monkeypatch, n, d, k, pairs):
     """More inner dimensions than one shared-memory image holds: the chunked tensor-core kernel, same lists as the
-    SIMT search on every row."""
+    SIMT search on every row, with both operand forms of the filter."""
     from tsne_cuda_b200 import datasets
+    monkeypatch.setenv("B200TSNE_KNN_FILTER", pairs)
     X = datasets.mnist_shaped(n, d, seed=n) if d == 784 else datasets.gaussian_mixture(n, d, seed=n)
     a = engine.knn(X, k)
     st = engine.knn_last_stats()

@@ -6,10 +6,13 @@
 // (sequential, unfused) with ties broken by index.  It is obtained in three steps:
 //
 //  1. Filter.  Ranking keys  key_ij = |x_j|^2 - 2 x_i.x_j  come straight out of the tensor cores: the
-//     query operand is [x_i, 1], the database operand [-2 x_j, |x_j|^2] (one of the padding columns of
-//     the 8-aligned inner dimension carries the norm), multiplied as a 3xTF32 product (v = hi + lo with
-//     hi, lo representable in TF32;  hi.hi + lo.hi + hi.lo, accumulated in fp32 in TMEM), accurate to
-//     about 2^-20 of |x_i||x_j|.  A block owns 256 queries (one TMEM lane each per query tile) and
+//     query operand is [x_i, 1], the database operand [-2 x_j, |x_j|^2] (padding columns of the inner
+//     dimension carry the norm), each value split in a pair v = hi + lo and multiplied as three products
+//     hi.hi + lo.hi + hi.lo accumulated in fp32 in TMEM.  By default the pairs are bf16 (kind::f16, K steps
+//     of 16, keys accurate to 3 * 2^-16 of sum_k |x_ik||2 x_jk|; the norm travels in two column pairs);
+//     B200TSNE_KNN_FILTER=tf32 selects TF32 pairs (K steps of 8, about 2^-20 of |x_i||x_j|) at nearly twice
+//     the tensor-core time.  Either error is covered by the proof of step 3.  A block owns 256 queries (one
+//     TMEM lane each per query tile) and
 //     walks the database in tiles of 128 points; each epilogue thread compares its row of the
 //     accumulator tile with a per-query threshold and appends the rare survivors to the query's
 //     candidate buffer with plain stores; the L = K + slack best are kept.  No N x N matrix is written.
@@ -60,6 +63,8 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+
+#include <cuda_bf16.h>
 
 #include <algorithm>
 
@@ -151,6 +156,18 @@ __device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, ui
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
+// D[tmem] (+)= A[smem] * B[smem]^T, 128 x 128 x 16, bf16 operands, fp32 accumulation
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
 // 32 consecutive accumulator columns of this thread's TMEM lane: asynchronous issue ...
 __device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, uint32_t (&r)[32])
 {
@@ -199,6 +216,13 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr)
 // Instruction descriptor: fp32 accumulate (bits 4-5 = 1), TF32 A and B (bits 7-9, 10-12 = 2), both
 // K-major (bits 15, 16 = 0), N/8 in bits 17-22, M/16 in bits 24-28.
 constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+// the same with bf16 A and B (format 1 of kind::f16); one K step is 32 operand bytes per row in either kind
+constexpr uint32_t kInstrDescBf16 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+__device__ __forceinline__ void tc_mma_step(bool bf16, uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t accumulate)
+{
+    if (bf16) tc_mma_bf16(d_tmem, make_desc(a_addr), make_desc(b_addr), kInstrDescBf16, accumulate);
+    else tc_mma_tf32(d_tmem, make_desc(a_addr), make_desc(b_addr), kInstrDesc, accumulate);
+}
 
 // ------------------------------------------------------------------------------------------------
 // operand preparation
@@ -249,6 +273,82 @@ knn_tc_prepare_kernel(const float *__restrict__ X, const int *__restrict__ list,
         im[part + image_offset(r, k % KC)] = to_tf32(v - vh);
     }
     if (norms) norms[pos] = n2;
+}
+
+// The bf16 form of the images: v = hi + lo + r with hi, lo in bf16 (round to nearest) and |r| <= 2^-16 |v|; the
+// same byte geometry as the TF32 images (a K step is 16 values = 32 bytes per row, core matrices of 8 rows x 16
+// bytes), so the shared-memory descriptors are the same and an image has half the bytes per inner dimension.
+// [tiles][Dp/KC chunks][2 (hi, lo)][KC/16][2048 values].  Two columns carry the norm (its bf16 pair and the pair of
+// what that pair leaves over: 32 significant bits), against 1, 1 in the query form.
+__device__ __forceinline__ size_t image_offset_bf16(int r, int k)
+{
+    return (size_t)(k >> 4) * 2048 + (size_t)(r >> 3) * 128 + (size_t)((k >> 3) & 1) * 64 + (size_t)(r & 7) * 8 + (k & 7);
+}
+
+// What the three products drop is bounded per pair from the actual leftovers: with a, b the data columns of a
+// query and a database operand, a = a_hi + a_lo + a_r,  |dropped| <= |a_lo||b_lo| + |a - a_r||b_r| + |a_r||b - b_r|
+// + |a_r||b_r| (Cauchy-Schwarz on the leftover vectors).  Queries record |a_lo| and |a_r| (res), the database the
+// largest |b_lo|/|b| and |b_r|/|b| over its rows (rho_bits: float bits, raised with atomicMax).
+__global__ void __launch_bounds__(128)
+knn_tc_prepare_bf16_kernel(const float *__restrict__ X, const int *__restrict__ list, int D, int Dp, int KC, int db_form,
+                           __nv_bfloat16 *__restrict__ img, double *__restrict__ norms, float2 *__restrict__ res,
+                           int *__restrict__ rho_bits)
+{
+    const long long tile = blockIdx.x;
+    const int r = threadIdx.x;
+    const long long pos = tile * TM + r;
+    const int i = list[pos];
+    __nv_bfloat16 *im_tile = img + (size_t)tile * 2 * Dp * 128;
+    const size_t part = (size_t)KC * 128;
+    double n2 = 0.0;
+    for (int k = 0; k < D; k++) {
+        const float x = (i >= 0) ? X[(long long)i * D + k] : 0.0f;
+        n2 += (double)x * (double)x;
+    }
+    const float nf = (i >= 0) ? (float)n2 : 3.0e38f;
+    const float nf_hi = __bfloat162float(__float2bfloat16_rn(nf));
+    const float nf_rest = (nf - nf_hi) - __bfloat162float(__float2bfloat16_rn(nf - nf_hi));   // both differences are exact in fp32
+    double lo2 = 0.0, r2 = 0.0;   // squared norms of the lo parts and of the leftovers of the data columns
+    for (int k = 0; k < Dp; k++) {
+        float v = 0.0f;
+        if (k < D) {
+            const float x = (i >= 0) ? X[(long long)i * D + k] : 0.0f;
+            v = db_form ? -2.0f * x : x;
+        } else if (k == D) {
+            v = db_form ? nf : ((i >= 0) ? 1.0f : 0.0f);
+        } else if (k == D + 1) {
+            v = db_form ? nf_rest : ((i >= 0) ? 1.0f : 0.0f);
+        }
+        const __nv_bfloat16 vh = __float2bfloat16_rn(v);
+        const float rest = v - __bfloat162float(vh);
+        const __nv_bfloat16 vl = __float2bfloat16_rn(rest);
+        __nv_bfloat16 *im = im_tile + (size_t)(k / KC) * 2 * part;
+        im[image_offset_bf16(r, k % KC)] = vh;
+        im[part + image_offset_bf16(r, k % KC)] = vl;
+        if (k < D) {
+            const float left = rest - __bfloat162float(vl);
+            lo2 += (double)__bfloat162float(vl) * (double)__bfloat162float(vl);
+            r2 += (double)left * (double)left;
+        }
+    }
+    if (norms) norms[pos] = n2;
+    if (res) res[pos] = make_float2((float)(sqrt(lo2) * 1.000001), (float)(sqrt(r2) * 1.000001));   // rounded up
+    if (rho_bits) {
+        float rl = 0.0f, rr = 0.0f;
+        if (i >= 0 && n2 > 0.0) {
+            rl = (float)(sqrt(lo2 / (4.0 * n2)) * 1.000001);
+            rr = (float)(sqrt(r2 / (4.0 * n2)) * 1.000001);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            rl = fmaxf(rl, __shfl_xor_sync(0xffffffffu, rl, o));
+            rr = fmaxf(rr, __shfl_xor_sync(0xffffffffu, rr, o));
+        }
+        if ((threadIdx.x & 31) == 0) {   // non-negative floats: integer order == float order
+            atomicMax(rho_bits + 0, __float_as_int(rl));
+            atomicMax(rho_bits + 1, __float_as_int(rr));
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -562,7 +662,7 @@ __global__ void __launch_bounds__(tc_threads(QH), 1)
 knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int Dp, long long nq, long long nd_pos,
                      const int2 *__restrict__ segs, const int *__restrict__ nseg, int seg_stride, int tile_stride, int win_lo,
                      int win_hi, const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id, int *counts,
-                     int *error_flag)
+                     int *error_flag, int bf16)
 {
     constexpr int C = 32 * EPL;   // capacity handled by one compaction
     constexpr int L = 16 * EPL;
@@ -570,11 +670,11 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
     constexpr uint32_t kTmemCols = kAccBufs * QH * TN;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) TcShared sh;
-    const uint32_t image_bytes = (uint32_t)Dp * 1024u;        // hi + lo
+    const uint32_t image_bytes = (uint32_t)Dp * (bf16 ? 512u : 1024u);        // hi + lo
     float *sA = reinterpret_cast<float *>(smem);                          // [QH] images
     float *sB = reinterpret_cast<float *>(smem + QH * image_bytes);       // [kBStages] images
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nks = Dp >> 3;
+    const int nks = bf16 ? Dp >> 4 : Dp >> 3;   // K steps of 32 operand bytes per row
     const long long qt = (long long)blockIdx.x * QH;   // first query tile of the block
     const int2 *my_segs = segs + (size_t)blockIdx.x * seg_stride;
     const int my_nseg = nseg[seg_stride ? blockIdx.x : 0];
@@ -641,13 +741,13 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
                     const uint32_t d_tmem = tmem_base + (uint32_t)((b * QH + h) * TN);
                     uint32_t acc = 0;
                     for (int ks = 0; ks < nks; ks++) {      // hi . hi
-                        tc_mma_tf32(d_tmem, make_desc(a_hi + ks * 4096u), make_desc(b_hi + ks * 4096u), kInstrDesc, acc);
+                        tc_mma_step(bf16, d_tmem, a_hi + ks * 4096u, b_hi + ks * 4096u, acc);
                         acc = 1;
                     }
                     for (int ks = 0; ks < nks; ks++)        // lo . hi
-                        tc_mma_tf32(d_tmem, make_desc(a_lo + ks * 4096u), make_desc(b_hi + ks * 4096u), kInstrDesc, 1);
+                        tc_mma_step(bf16, d_tmem, a_lo + ks * 4096u, b_hi + ks * 4096u, 1);
                     for (int ks = 0; ks < nks; ks++)        // hi . lo
-                        tc_mma_tf32(d_tmem, make_desc(a_hi + ks * 4096u), make_desc(b_lo + ks * 4096u), kInstrDesc, 1);
+                        tc_mma_step(bf16, d_tmem, a_hi + ks * 4096u, b_lo + ks * 4096u, 1);
                 }
                 tc_commit(&sh.empty_b[s]);    // the stage may be refilled once these MMAs have read it
                 tc_commit(&sh.acc_full[b]);   // the accumulator tiles are complete
@@ -814,7 +914,7 @@ __global__ void __launch_bounds__(tc_threads(2), 1)
 knn_tc_wide_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int n_chunks, long long nq,
                    const int2 *__restrict__ segs, const int *__restrict__ nseg, int seg_stride, int unit_stride, int win_lo,
                    int win_hi, const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id, int *counts,
-                   int *error_flag)
+                   int *error_flag, int bf16)
 {
     constexpr int kProducerWarp = 16, kMmaWarp = 17;
     constexpr uint32_t kTmemCols = 512;
@@ -897,13 +997,13 @@ knn_tc_wide_kernel(const float *__restrict__ img_q, const float *__restrict__ im
                         const uint32_t d_tmem = tmem_base + (uint32_t)((h * 2 + g) * TN);
                         uint32_t acc = (c > 0) ? 1u : 0u;
                         for (int ks = 0; ks < kSteps; ks++) {      // hi . hi
-                            tc_mma_tf32(d_tmem, make_desc(a_hi + ks * 4096u), make_desc(b_hi + ks * 4096u), kInstrDesc, acc);
+                            tc_mma_step(bf16, d_tmem, a_hi + ks * 4096u, b_hi + ks * 4096u, acc);
                             acc = 1;
                         }
                         for (int ks = 0; ks < kSteps; ks++)        // lo . hi
-                            tc_mma_tf32(d_tmem, make_desc(a_lo + ks * 4096u), make_desc(b_hi + ks * 4096u), kInstrDesc, 1);
+                            tc_mma_step(bf16, d_tmem, a_lo + ks * 4096u, b_hi + ks * 4096u, 1);
                         for (int ks = 0; ks < kSteps; ks++)        // hi . lo
-                            tc_mma_tf32(d_tmem, make_desc(a_hi + ks * 4096u), make_desc(b_lo + ks * 4096u), kInstrDesc, 1);
+                            tc_mma_step(bf16, d_tmem, a_hi + ks * 4096u, b_lo + ks * 4096u, 1);
                     }
                     tc_commit(&sh.empty[s]);
                 }
@@ -1113,7 +1213,8 @@ __global__ void __launch_bounds__(kRerankWarps * 32)
 knn_tc_rerank_kernel(const float *__restrict__ X, int D, const int *__restrict__ qlist, const int *__restrict__ dblist,
                      long long out_base, long long nq, const float *__restrict__ cand_key,
                      const int32_t *__restrict__ cand_id, int L, int C, int K, const double *__restrict__ norms_exact,
-                     float err_scale, const int *__restrict__ row_flags, int32_t *__restrict__ ids, float *__restrict__ d2,
+                     float err_scale, const float2 *__restrict__ res_q, const float *__restrict__ rho, const int *__restrict__ row_flags,
+                     int32_t *__restrict__ ids, float *__restrict__ d2,
                      int *__restrict__ failed,
                      int *__restrict__ n_failed, float *__restrict__ max_err_ratio, const float *__restrict__ Xp)
 {
@@ -1176,14 +1277,25 @@ knn_tc_rerank_kernel(const float *__restrict__ X, int D, const int *__restrict__
         bool ok = true;
         // Error bound of the filter's key for this row: it scales with |x_i||x_j|, and a point whose key is
         // near T lies within sqrt(|x_i|^2 + T) of x_i, so |x_i||x_j| <= |x_i|^2 + (|x_i|^2 + T)+ up to a factor 2.
-        const double E = (double)err_scale * (ni + fmax(0.0, ni + (double)T) + 1.0);
+        double E = (double)err_scale * (ni + fmax(0.0, ni + (double)T) + 1.0);
+        double dropped = 0.0;
+        if (res_q) {
+            // bf16 pairs: what the three products drop, bounded from the leftovers of this query and the largest
+            // relative leftovers of the database, for every point with |x_j| <= |x_i| + sqrt(|x_i|^2 + T) (a point
+            // further out cannot come closer than the threshold whatever the error of its key); the last term is
+            // the fp32 rounding of the norm column.  err_scale then covers the accumulation only.
+            const double xi = sqrt(ni), xj = xi + sqrt(fmax(0.0, ni + (double)T));
+            const float2 rq = res_q[q];
+            dropped = 1.001 * 2.0 * xj * ((double)rq.x * (double)rho[0] + xi * (double)rho[1] + (double)rq.y) + 1.2e-7 * xj * xj;
+            E += dropped;
+        }
         if (n_valid == L) {
             // outsiders: key >= T  =>  canonical distance >= (ni + T - E) * (1 - theta)
             const double theta = (double)(D + 4) * 5.9604644775390625e-08;   // (D+4) * 2^-24
             const double bound = (ni + (double)T - E) * (1.0 - theta);
             ok = (double)dK < bound;
         }
-        const float ratio = (float)((double)worst / E);
+        const float ratio = (float)(fmax(0.0, (double)worst - dropped) / (E - dropped));
         if (ratio > 0.5f) ok = false;   // the filter was less accurate than the bound assumes
         if (row_flags && row_flags[q]) ok = false;   // the fixed threshold kept too few or too many candidates
         failed[q] = ok ? 0 : 1;
@@ -1356,6 +1468,13 @@ __global__ void mbar_wait_selftest_kernel(int *abort_flag, int *gave_up, unsigne
 
 // wide points: the inner dimension (D + 1) does not fit the narrow kernel's shared-memory images
 static bool tc_wide(int D) { return D + 1 > 64; }
+// Operand form of the filter: bf16 pairs (three bf16 products per key, half the tensor-core time of 3xTF32, error
+// 3 * 2^-16 of sum |x_ik||2 x_jk|) unless B200TSNE_KNN_FILTER=tf32 asks for the TF32 pairs (error ~2^-20).
+static bool tc_bf16()
+{
+    const char *e = getenv("B200TSNE_KNN_FILTER");
+    return !(e && strcmp(e, "tf32") == 0);
+}
 constexpr long long kWideMinRows = 16384;   // the wide kernel has fixed thresholds only: it needs a database to sample
 
 // nd: database rows the search will scan
@@ -1373,11 +1492,13 @@ constexpr long long kTwoPassMinTiles = 512;   // below this many database tiles 
 
 // Device workspace of launch_knn_tc, carved in this order.
 struct TcWorkspace {
-    bool wide;
+    bool wide, bf16;
+    size_t image_bytes;        // one tile's image (hi and lo)
     int Dp, cells;
     long long tq, td;          // tiles allocated for the query list / the database list
     float *img_q, *img_db;
     double *norms_q;
+    float2 *res_q;             // bf16 form: norms of the lo parts and of the leftovers of every query
     int *qlist, *dblist;
     float *xp;   // database rows in list order (cells only)
     unsigned char *cell_q, *cell_db;
@@ -1394,8 +1515,11 @@ static TcWorkspace tc_carve(void *base, int D, int K, long long nq, long long nd
 {
     TcWorkspace w;
     w.wide = tc_wide(D);
-    // one extra inner column carries the norm; wide points are chunked along the inner dimension
-    w.Dp = w.wide ? (D + 1 + kWideKC - 1) / kWideKC * kWideKC : (D + 1 + 7) / 8 * 8;
+    w.bf16 = tc_bf16();
+    // one extra inner column carries the norm (two in bf16); wide points are chunked along the inner dimension
+    if (w.bf16) w.Dp = w.wide ? (D + 2 + 2 * kWideKC - 1) / (2 * kWideKC) * (2 * kWideKC) : (D + 2 + 15) / 16 * 16;
+    else w.Dp = w.wide ? (D + 1 + kWideKC - 1) / kWideKC * kWideKC : (D + 1 + 7) / 8 * 8;
+    w.image_bytes = (size_t)w.Dp * (w.bf16 ? 512 : 1024);
     const bool two_pass = nd >= (w.wide ? kWideMinRows : kTwoPassMinTiles * TN);
     // cells of at least 16384 points: the padding between them stays below 1 % of the database
     // (wide points are not visited by cells: the cell kernels keep a point in registers)
@@ -1406,9 +1530,10 @@ static TcWorkspace tc_carve(void *base, int D, int K, long long nq, long long nd
     const int C = (K + 32 <= 128) ? 256 : 512;
     char *p = static_cast<char *>(base);
     auto take = [&](size_t bytes) { char *r = p; p += (bytes + 255) / 256 * 256; return r; };
-    w.img_q = reinterpret_cast<float *>(take((size_t)w.tq * w.Dp * 1024));
-    w.img_db = reinterpret_cast<float *>(take((size_t)w.td * w.Dp * 1024));
+    w.img_q = reinterpret_cast<float *>(take((size_t)w.tq * w.image_bytes));
+    w.img_db = reinterpret_cast<float *>(take((size_t)w.td * w.image_bytes));
     w.norms_q = reinterpret_cast<double *>(take(sizeof(double) * (size_t)w.tq * TM));
+    w.res_q = reinterpret_cast<float2 *>(take(sizeof(float2) * (size_t)w.tq * TM));
     w.qlist = reinterpret_cast<int *>(take(sizeof(int) * (size_t)w.tq * TM));
     w.dblist = reinterpret_cast<int *>(take(sizeof(int) * (size_t)w.td * TN));
     w.xp = (w.cells > 1) ? reinterpret_cast<float *>(take(sizeof(float) * (size_t)w.td * TN * D)) : nullptr;
@@ -1429,7 +1554,7 @@ static TcWorkspace tc_carve(void *base, int D, int K, long long nq, long long nd
     }
     w.failed = reinterpret_cast<int *>(take(sizeof(int) * (size_t)nq));
     w.flist = reinterpret_cast<int *>(take(sizeof(int) * (size_t)nq));
-    w.counters = reinterpret_cast<int *>(take(sizeof(int) * 16));   // [0] wait time-out flag, [1] failed rows, [2] listed rows, [3] max error ratio (float bits)
+    w.counters = reinterpret_cast<int *>(take(sizeof(int) * 16));   // [0] wait time-out flag, [1] failed rows, [2] listed rows, [3] max error ratio (float bits), [4], [5] largest relative lo part / leftover of a database row (float bits)
     w.bytes = (size_t)(p - static_cast<char *>(base));
     return w;
 }
@@ -1452,7 +1577,8 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     TcWorkspace w = tc_carve(workspace, D, K, nq, nd);
     const int Dp = w.Dp, cells = w.cells;
     const bool wide = w.wide;
-    const int KC = wide ? kWideKC : Dp;   // inner dimensions per image chunk
+    const int bf16 = w.bf16 ? 1 : 0;
+    const int KC = wide ? (bf16 ? 2 * kWideKC : kWideKC) : Dp;   // inner dimensions per image chunk
     const int EPL = (K + 32 <= 128) ? 8 : 16, C = 32 * EPL, L = 16 * EPL;
     const int kFixedCap = fixed_cap(K);
     const bool two_pass = w.fix_key != nullptr;
@@ -1480,12 +1606,19 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         knn_iota_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(w.qlist, q_lo, nq);
     }
     B200_CUDA(cudaGetLastError());
-    knn_tc_prepare_kernel<<<(unsigned)w.tq, 128, 0, st>>>(X, w.qlist, D, Dp, KC, 0, w.img_q, w.norms_q);
-    knn_tc_prepare_kernel<<<(unsigned)w.td, 128, 0, st>>>(X, w.dblist, D, Dp, KC, 1, w.img_db, nullptr);
+    if (bf16) {
+        knn_tc_prepare_bf16_kernel<<<(unsigned)w.tq, 128, 0, st>>>(X, w.qlist, D, Dp, KC, 0, reinterpret_cast<__nv_bfloat16 *>(w.img_q), w.norms_q,
+                                                                   w.res_q, nullptr);
+        knn_tc_prepare_bf16_kernel<<<(unsigned)w.td, 128, 0, st>>>(X, w.dblist, D, Dp, KC, 1, reinterpret_cast<__nv_bfloat16 *>(w.img_db), nullptr,
+                                                                   nullptr, counters + 4);
+    } else {
+        knn_tc_prepare_kernel<<<(unsigned)w.tq, 128, 0, st>>>(X, w.qlist, D, Dp, KC, 0, w.img_q, w.norms_q);
+        knn_tc_prepare_kernel<<<(unsigned)w.td, 128, 0, st>>>(X, w.dblist, D, Dp, KC, 1, w.img_db, nullptr);
+    }
     B200_CUDA(cudaGetLastError());
 
     // two query tiles per block when their images and the database stages fit in shared memory
-    const int QH = ((size_t)(2 + kBStages) * Dp * 1024 + 1024 <= 227 * 1024) ? 2 : 1;
+    const int QH = ((size_t)(2 + kBStages) * w.image_bytes + 1024 <= 227 * 1024) ? 2 : 1;
     const long long q_tiles = (nq + TM - 1) / TM;
     // Segments of the blocks: all database tiles (one shared list) unless the cells prune (per block).
     // The blocks of an online pass hold one query tile, those of a fixed-threshold pass QH.
@@ -1504,12 +1637,12 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     // that run at the same time then read the same ~60 MB, which stays in L2.  In one launch the blocks
     // drift apart until each streams its own copy from HBM with only one 56 KB stage in flight, and the
     // scan becomes latency-bound (measured at 10^7 rows: 3.85 s per 2^20 queries against 1.3 s of MMAs).
-    const long long db_image_bytes = (long long)w.td * Dp * 1024;
-    int window_tiles = db_image_bytes > (512ll << 20) ? (int)((60ll << 20) / ((long long)Dp * 1024)) : INT_MAX;
+    const long long db_image_bytes = (long long)w.td * (long long)w.image_bytes;
+    int window_tiles = db_image_bytes > (512ll << 20) ? (int)((60ll << 20) / (long long)w.image_bytes) : INT_MAX;
     if (const char *e = getenv("B200TSNE_KNN_WINDOW_TILES")) window_tiles = std::max(1, atoi(e));   // for tests
 #define B200_KNN_FILTER_V(EPL_, FIXED_, QH_, stride_, tau_, cap_, key_, id_, counts_)                                           \
     do {                                                                                                                        \
-        const size_t smem_ = (size_t)(QH_ + kBStages) * Dp * 1024;                                                              \
+        const size_t smem_ = (size_t)(QH_ + kBStages) * w.image_bytes;                                                          \
         B200_CUDA(cudaFuncSetAttribute(knn_tc_filter_kernel<EPL_, FIXED_, QH_>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
                                        (int)smem_));                                                                            \
         if (FIXED_) B200_CUDA(cudaMemsetAsync(counts_, 0, sizeof(int) * (size_t)nq * kAccBufs, st));                            \
@@ -1518,7 +1651,7 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
             const int hi_ = (int)std::min<long long>(w.td, lo_ + win_);                                                         \
             knn_tc_filter_kernel<EPL_, FIXED_, QH_><<<(unsigned)((q_tiles + QH_ - 1) / QH_), tc_threads(QH_), smem_, st>>>(      \
                 w.img_q, w.img_db, Dp, nq, nd_pos, w.segs, w.nseg, seg_stride, stride_, (int)lo_, hi_, tau_, cap_, key_, id_,   \
-                counts_, counters + 0);                                                                                         \
+                counts_, counters + 0, bf16);                                                                                   \
             B200_CUDA(cudaGetLastError());                                                                                      \
         }                                                                                                                       \
     } while (0)
@@ -1533,8 +1666,8 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         for (long long lo_ = 0; lo_ < units_; lo_ += win_) {                                                                    \
             const int hi_ = (int)std::min<long long>(units_, lo_ + win_);                                                       \
             knn_tc_wide_kernel<EPL_><<<(unsigned)((q_tiles + 1) / 2), tc_threads(2), smem_, st>>>(                               \
-                w.img_q, w.img_db, Dp / kWideKC, nq, w.segs, w.nseg, seg_stride, stride_, (int)lo_, hi_, tau_, cap_, key_, id_,  \
-                counts_, counters + 0);                                                                                         \
+                w.img_q, w.img_db, Dp / KC, nq, w.segs, w.nseg, seg_stride, stride_, (int)lo_, hi_, tau_, cap_, key_, id_,       \
+                counts_, counters + 0, bf16);                                                                                   \
             B200_CUDA(cudaGetLastError());                                                                                      \
         }                                                                                                                       \
     } while (0)
@@ -1617,9 +1750,13 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     // per addition) adds up to 2 D 2^-24 |x_i||x_j| in the worst case.  2^-14 covers both with a wide margin
     // up to D = 256; beyond, the bound grows with D.  The re-rank checks the observed error of every
     // candidate against half of it.
-    const float err_scale = std::max(6.103515625e-05f, (float)(D + 8) * 2.384185791015625e-07f);   // max(2^-14, (D + 8) 2^-22)
+    // bf16 pairs: what the products drop is bounded row by row in the re-rank (see knn_tc_prepare_bf16_kernel), so
+    // the scale covers the accumulation only.
+    const float err_scale = bf16 ? std::max(1.52587890625e-05f, (float)(D + 8) * 2.384185791015625e-07f)      // max(2^-16, (D + 8) 2^-22)
+                                 : std::max(6.103515625e-05f, (float)(D + 8) * 2.384185791015625e-07f);   // max(2^-14, (D + 8) 2^-22)
     knn_tc_rerank_kernel<<<(unsigned)((nq + kRerankWarps - 1) / kRerankWarps), kRerankWarps * 32, 0, st>>>(
-        X, D, w.qlist, w.dblist, q_lo, nq, final_key, final_id, L, final_stride, K, w.norms_q, err_scale, two_pass ? row_flags : nullptr, ids, d2,
+        X, D, w.qlist, w.dblist, q_lo, nq, final_key, final_id, L, final_stride, K, w.norms_q, err_scale, bf16 ? w.res_q : nullptr,
+        reinterpret_cast<const float *>(counters + 4), two_pass ? row_flags : nullptr, ids, d2,
         failed, counters + 1, reinterpret_cast<float *>(counters + 3), w.xp);
     B200_CUDA(cudaGetLastError());
     knn_tc_collect_failed_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(failed, nq, w.qlist, flist, counters + 2);
