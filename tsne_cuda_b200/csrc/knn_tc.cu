@@ -59,6 +59,7 @@
 // time, i.e. it is bound by the tensor pipe (42 MMAs 128x128x8 per tile pair at ~105 cycles each).
 // Every wait has a time limit; on expiry the kernel sets an error flag, drains and frees its TMEM.
 #include <limits.h>
+#include <stdio.h>
 #include <string.h>
 #include <stdlib.h>
 
@@ -213,6 +214,19 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr)
     d |= (uint64_t)1 << 46;
     return d;
 }
+// The same for a swizzled K-major image: rows of sw = 32, 64 or 128 bytes, 8-row groups 8 * sw bytes apart, the
+// 16-byte pieces of a row exchanged by the XOR pattern of that width (layout type 6, 4 or 2 in bits 61-63; the
+// leading offset is not used).  A K step inside a row is reached by adding its byte offset to the start address.
+__device__ __forceinline__ uint64_t make_desc_swizzled(uint32_t saddr, uint32_t sw)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)((8u * sw) >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)(sw == 128u ? 2u : (sw == 64u ? 4u : 6u)) << 61;
+    return d;
+}
 // Instruction descriptor: fp32 accumulate (bits 4-5 = 1), TF32 A and B (bits 7-9, 10-12 = 2), both
 // K-major (bits 15, 16 = 0), N/8 in bits 17-22, M/16 in bits 24-28.
 constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
@@ -223,6 +237,7 @@ __device__ __forceinline__ void tc_mma_step(bool bf16, uint32_t d_tmem, uint32_t
     if (bf16) tc_mma_bf16(d_tmem, make_desc(a_addr), make_desc(b_addr), kInstrDescBf16, accumulate);
     else tc_mma_tf32(d_tmem, make_desc(a_addr), make_desc(b_addr), kInstrDesc, accumulate);
 }
+
 
 // ------------------------------------------------------------------------------------------------
 // operand preparation
@@ -284,13 +299,25 @@ __device__ __forceinline__ size_t image_offset_bf16(int r, int k)
 {
     return (size_t)(k >> 4) * 2048 + (size_t)(r >> 3) * 128 + (size_t)((k >> 3) & 1) * 64 + (size_t)(r & 7) * 8 + (k & 7);
 }
+// The swizzled form (narrow kernel): rows of sw bytes (sw / 2 values), blocks of 128 rows one after the other along
+// the inner dimension; inside a block the 16-byte piece p of row r sits where piece p ^ ((r * sw / 128) mod (sw / 16))
+// would (the shared-memory swizzle of that width, which the tensor core undoes when it reads: operands in this
+// form are fetched about twice as fast as core matrices without swizzle, measured).  Offset in values.
+__device__ __forceinline__ size_t image_offset_bf16_swizzled(int r, int k, int sw)
+{
+    const int per_row = sw >> 1;
+    const int block = k / per_row;
+    unsigned off = (unsigned)r * (unsigned)sw + (unsigned)(k % per_row) * 2u;   // bytes inside the block
+    off ^= ((off >> 7) & ((unsigned)(sw >> 4) - 1u)) << 4;
+    return (size_t)block * 64 * sw + (off >> 1);
+}
 
 // What the three products drop is bounded per pair from the actual leftovers: with a, b the data columns of a
 // query and a database operand, a = a_hi + a_lo + a_r,  |dropped| <= |a_lo||b_lo| + |a - a_r||b_r| + |a_r||b - b_r|
 // + |a_r||b_r| (Cauchy-Schwarz on the leftover vectors).  Queries record |a_lo| and |a_r| (res), the database the
 // largest |b_lo|/|b| and |b_r|/|b| over its rows (rho_bits: float bits, raised with atomicMax).
 __global__ void __launch_bounds__(128)
-knn_tc_prepare_bf16_kernel(const float *__restrict__ X, const int *__restrict__ list, int D, int Dp, int KC, int db_form,
+knn_tc_prepare_bf16_kernel(const float *__restrict__ X, const int *__restrict__ list, int D, int Dp, int KC, int sw, int db_form,
                            __nv_bfloat16 *__restrict__ img, double *__restrict__ norms, float2 *__restrict__ res,
                            int *__restrict__ rho_bits)
 {
@@ -323,8 +350,9 @@ knn_tc_prepare_bf16_kernel(const float *__restrict__ X, const int *__restrict__ 
         const float rest = v - __bfloat162float(vh);
         const __nv_bfloat16 vl = __float2bfloat16_rn(rest);
         __nv_bfloat16 *im = im_tile + (size_t)(k / KC) * 2 * part;
-        im[image_offset_bf16(r, k % KC)] = vh;
-        im[part + image_offset_bf16(r, k % KC)] = vl;
+        const size_t at = sw ? image_offset_bf16_swizzled(r, k % KC, sw) : image_offset_bf16(r, k % KC);
+        im[at] = vh;
+        im[part + at] = vl;
         if (k < D) {
             const float left = rest - __bfloat162float(vl);
             lo2 += (double)__bfloat162float(vl) * (double)__bfloat162float(vl);
@@ -662,19 +690,20 @@ __global__ void __launch_bounds__(tc_threads(QH), 1)
 knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int Dp, long long nq, long long nd_pos,
                      const int2 *__restrict__ segs, const int *__restrict__ nseg, int seg_stride, int tile_stride, int win_lo,
                      int win_hi, const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id, int *counts,
-                     int *error_flag, int bf16)
+                     int *error_flag, int bf16, int sw, int nks)
 {
+    // bf16: the images hold bf16 pairs; sw != 0: in swizzled rows of sw bytes (else core matrices without swizzle);
+    // nks: K steps of 32 operand bytes per row to multiply
     constexpr int C = 32 * EPL;   // capacity handled by one compaction
     constexpr int L = 16 * EPL;
     constexpr int kProducerWarp = 8 * QH, kMmaWarp = 8 * QH + 1;
     constexpr uint32_t kTmemCols = kAccBufs * QH * TN;
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];   // swizzled images want their 8-row groups on 8 * sw bytes
     __shared__ __align__(8) TcShared sh;
     const uint32_t image_bytes = (uint32_t)Dp * (bf16 ? 512u : 1024u);        // hi + lo
     float *sA = reinterpret_cast<float *>(smem);                          // [QH] images
     float *sB = reinterpret_cast<float *>(smem + QH * image_bytes);       // [kBStages] images
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nks = bf16 ? Dp >> 4 : Dp >> 3;   // K steps of 32 operand bytes per row
     const long long qt = (long long)blockIdx.x * QH;   // first query tile of the block
     const int2 *my_segs = segs + (size_t)blockIdx.x * seg_stride;
     const int my_nseg = nseg[seg_stride ? blockIdx.x : 0];
@@ -724,8 +753,31 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
         }
     } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
+        // One thread issues every MMA, and a thread runs its dependent instructions several cycles apart: what it
+        // computes per MMA shows in the kernel's time.  So the descriptors of the query images and of both database
+        // stages are built once; a K step only adds its offset to the address field (the low 14 bits, in 16-byte
+        // units: shared-memory addresses stay far below the carry).
         if (lane == 0) {
             bool ok = mbar_wait(&sh.full_a, 0, abort_flag);
+            const uint32_t part16 = image_bytes >> 5;   // hi -> lo, in 16-byte units
+            // offset of K step ks inside a part: 4 KB blocks without swizzle; with it, sw / 32 steps side by side in a
+            // row (2 units apart) and blocks of 128 rows
+            const uint32_t spr_log = sw == 128 ? 2u : (sw == 64 ? 1u : 0u), spr_mask = (1u << spr_log) - 1u;
+            const uint32_t block16 = sw ? (128u * (uint32_t)sw) >> 4 : 256u, in_row16 = sw ? 2u : 0u;
+            const uint64_t no_addr = sw ? make_desc_swizzled(0u, (uint32_t)sw) : make_desc(0u);
+            const uint32_t a16 = smem_u32(sA) >> 4, b16 = smem_u32(sB) >> 4, image16 = image_bytes >> 4;
+            // every operand address must stay inside the block's images: checked once, here, instead of trusting
+            // the arguments (an MMA that reads outside the block's shared memory is a fault)
+            {
+                const uint32_t last_step = (uint32_t)(nks - 1);
+                const uint32_t last16 = (last_step >> spr_log) * block16 + (last_step & spr_mask) * in_row16;
+                const uint32_t step_span16 = sw ? (127u * (uint32_t)sw + 32u) >> 4 : 256u;   // what one K step reads
+                if (nks < 1 || part16 * 2u != image16 || last16 + step_span16 > part16 ||
+                    b16 + kBStages * image16 > ((smem_u32(smem) + (uint32_t)(QH + kBStages) * image_bytes) >> 4)) {
+                    sh.abort_flag = 1;
+                    ok = false;
+                }
+            }
             TileWalk walk(my_segs, my_nseg, tile_stride, win_lo, win_hi);
             int tile;
             for (long long t = 0; ok && walk.next(tile); t++) {
@@ -734,20 +786,32 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
                 if (!mbar_wait(&sh.acc_empty[b], ph_b ^ 1u, abort_flag)) break;
                 if (!mbar_wait(&sh.full_b[s], ph_s, abort_flag)) break;
                 tc_fence_after();
-                const uint32_t b_hi = smem_u32(sB + (size_t)s * (image_bytes / 4)), b_lo = b_hi + (uint32_t)nks * 4096u;
+                const uint64_t b_hi = no_addr + (uint64_t)(b16 + (uint32_t)s * image16), b_lo = b_hi + part16;
 #pragma unroll 1
                 for (int h = 0; h < QH; h++) {
-                    const uint32_t a_hi = smem_u32(sA) + (uint32_t)h * image_bytes, a_lo = a_hi + (uint32_t)nks * 4096u;
+                    const uint64_t a_hi = no_addr + (uint64_t)(a16 + (uint32_t)h * image16), a_lo = a_hi + part16;
                     const uint32_t d_tmem = tmem_base + (uint32_t)((b * QH + h) * TN);
-                    uint32_t acc = 0;
-                    for (int ks = 0; ks < nks; ks++) {      // hi . hi
-                        tc_mma_step(bf16, d_tmem, a_hi + ks * 4096u, b_hi + ks * 4096u, acc);
-                        acc = 1;
+                    if (bf16) {
+                        for (uint32_t ks = 0; ks < (uint32_t)nks; ks++) {      // hi . hi
+                            const uint32_t o = (ks >> spr_log) * block16 + (ks & spr_mask) * in_row16;
+                            tc_mma_bf16(d_tmem, a_hi + o, b_hi + o, kInstrDescBf16, ks ? 1u : 0u);
+                        }
+                        for (uint32_t ks = 0; ks < (uint32_t)nks; ks++) {      // lo . hi
+                            const uint32_t o = (ks >> spr_log) * block16 + (ks & spr_mask) * in_row16;
+                            tc_mma_bf16(d_tmem, a_lo + o, b_hi + o, kInstrDescBf16, 1u);
+                        }
+                        for (uint32_t ks = 0; ks < (uint32_t)nks; ks++) {      // hi . lo
+                            const uint32_t o = (ks >> spr_log) * block16 + (ks & spr_mask) * in_row16;
+                            tc_mma_bf16(d_tmem, a_hi + o, b_lo + o, kInstrDescBf16, 1u);
+                        }
+                    } else {
+                        for (uint32_t ks = 0; ks < (uint32_t)nks; ks++)        // hi . hi
+                            tc_mma_tf32(d_tmem, a_hi + ks * 256u, b_hi + ks * 256u, kInstrDesc, ks ? 1u : 0u);
+                        for (uint32_t ks = 0; ks < (uint32_t)nks; ks++)        // lo . hi
+                            tc_mma_tf32(d_tmem, a_lo + ks * 256u, b_hi + ks * 256u, kInstrDesc, 1u);
+                        for (uint32_t ks = 0; ks < (uint32_t)nks; ks++)        // hi . lo
+                            tc_mma_tf32(d_tmem, a_hi + ks * 256u, b_lo + ks * 256u, kInstrDesc, 1u);
                     }
-                    for (int ks = 0; ks < nks; ks++)        // lo . hi
-                        tc_mma_step(bf16, d_tmem, a_lo + ks * 4096u, b_hi + ks * 4096u, 1);
-                    for (int ks = 0; ks < nks; ks++)        // hi . lo
-                        tc_mma_step(bf16, d_tmem, a_hi + ks * 4096u, b_lo + ks * 4096u, 1);
                 }
                 tc_commit(&sh.empty_b[s]);    // the stage may be refilled once these MMAs have read it
                 tc_commit(&sh.acc_full[b]);   // the accumulator tiles are complete
@@ -919,7 +983,7 @@ knn_tc_wide_kernel(const float *__restrict__ img_q, const float *__restrict__ im
     constexpr int kProducerWarp = 16, kMmaWarp = 17;
     constexpr uint32_t kTmemCols = 512;
     constexpr int kSteps = kWideKC / 8;
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ __align__(8) WideShared sh;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long qt = (long long)blockIdx.x * 2;   // first query tile of the block
@@ -1495,6 +1559,7 @@ struct TcWorkspace {
     bool wide, bf16;
     size_t image_bytes;        // one tile's image (hi and lo)
     int Dp, cells;
+    int sw, nks;               // narrow kernel: bytes of a swizzled image row (0: core matrices without swizzle), K steps
     long long tq, td;          // tiles allocated for the query list / the database list
     float *img_q, *img_db;
     double *norms_q;
@@ -1517,8 +1582,20 @@ static TcWorkspace tc_carve(void *base, int D, int K, long long nq, long long nd
     w.wide = tc_wide(D);
     w.bf16 = tc_bf16();
     // one extra inner column carries the norm (two in bf16); wide points are chunked along the inner dimension
-    if (w.bf16) w.Dp = w.wide ? (D + 2 + 2 * kWideKC - 1) / (2 * kWideKC) * (2 * kWideKC) : (D + 2 + 15) / 16 * 16;
-    else w.Dp = w.wide ? (D + 1 + kWideKC - 1) / kWideKC * kWideKC : (D + 1 + 7) / 8 * 8;
+    w.sw = 0;
+    if (w.bf16 && !w.wide) {
+        // swizzled rows of 32, 64 or 128 bytes (16, 32 or 64 values); more inner dimensions: blocks of 128-byte rows
+        const int need = D + 2;
+        w.sw = need <= 16 ? 32 : (need <= 32 ? 64 : 128);
+        w.Dp = (need + w.sw / 2 - 1) / (w.sw / 2) * (w.sw / 2);
+        w.nks = (need + 15) / 16;
+    } else if (w.bf16) {
+        w.Dp = (D + 2 + 2 * kWideKC - 1) / (2 * kWideKC) * (2 * kWideKC);
+        w.nks = w.Dp / 16;
+    } else {
+        w.Dp = w.wide ? (D + 1 + kWideKC - 1) / kWideKC * kWideKC : (D + 1 + 7) / 8 * 8;
+        w.nks = w.Dp / 8;
+    }
     w.image_bytes = (size_t)w.Dp * (w.bf16 ? 512 : 1024);
     const bool two_pass = nd >= (w.wide ? kWideMinRows : kTwoPassMinTiles * TN);
     // cells of at least 16384 points: the padding between them stays below 1 % of the database
@@ -1559,6 +1636,42 @@ static TcWorkspace tc_carve(void *base, int D, int K, long long nq, long long nd
     return w;
 }
 
+// B200TSNE_KNN_TIMERS=1: device time of the phases of one search (CUDA events on the launching stream, printed to
+// stderr when the search ends; the marks synchronise nothing, the print waits for the stream).
+struct PhaseTimer {
+    static constexpr int kMax = 12;
+    bool on = false;
+    cudaStream_t st = nullptr;
+    cudaEvent_t ev[kMax] = {};
+    const char *name[kMax] = {};
+    int n = 0;
+    explicit PhaseTimer(cudaStream_t s) : st(s)
+    {
+        const char *e = getenv("B200TSNE_KNN_TIMERS");
+        on = e && atoi(e) != 0;
+    }
+    void mark(const char *what)
+    {
+        if (!on || n >= kMax) return;
+        if (cudaEventCreate(&ev[n]) != cudaSuccess) { on = false; return; }
+        cudaEventRecord(ev[n], st);
+        name[n++] = what;
+    }
+    ~PhaseTimer()
+    {
+        if (n > 1 && cudaEventSynchronize(ev[n - 1]) == cudaSuccess) {
+            fprintf(stderr, "knn phases (ms):");
+            for (int i = 1; i < n; i++) {
+                float ms = 0.0f;
+                cudaEventElapsedTime(&ms, ev[i - 1], ev[i]);
+                fprintf(stderr, " %s %.2f", name[i], ms);
+            }
+            fprintf(stderr, "\n");
+        }
+        for (int i = 0; i < n; i++) cudaEventDestroy(ev[i]);
+    }
+};
+
 // Workspace (device, 256-byte aligned) needed by launch_knn_tc for nq queries against nd database rows.
 size_t knn_tc_workspace_bytes(int D, int K, int64_t nq, int64_t nd) { return tc_carve(nullptr, D, K, nq, nd).bytes; }
 
@@ -1586,6 +1699,8 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     int32_t *cand_id = w.cand_id, *fix_id = w.fix_id;
     int *row_flags = w.row_flags, *counts = w.counts, *failed = w.failed, *flist = w.flist, *counters = w.counters;
     B200_CUDA(cudaMemsetAsync(counters, 0, sizeof(int) * 16, st));
+    PhaseTimer phases(st);
+    phases.mark("start");
 
     // ---- visiting order of the queries and of the database, operand images ----
     B200_CUDA(cudaMemsetAsync(w.qlist, 0xff, sizeof(int) * (size_t)w.tq * TM, st));    // -1 = padding
@@ -1607,16 +1722,17 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     }
     B200_CUDA(cudaGetLastError());
     if (bf16) {
-        knn_tc_prepare_bf16_kernel<<<(unsigned)w.tq, 128, 0, st>>>(X, w.qlist, D, Dp, KC, 0, reinterpret_cast<__nv_bfloat16 *>(w.img_q), w.norms_q,
-                                                                   w.res_q, nullptr);
-        knn_tc_prepare_bf16_kernel<<<(unsigned)w.td, 128, 0, st>>>(X, w.dblist, D, Dp, KC, 1, reinterpret_cast<__nv_bfloat16 *>(w.img_db), nullptr,
-                                                                   nullptr, counters + 4);
+        knn_tc_prepare_bf16_kernel<<<(unsigned)w.tq, 128, 0, st>>>(X, w.qlist, D, Dp, KC, w.sw, 0, reinterpret_cast<__nv_bfloat16 *>(w.img_q),
+                                                                   w.norms_q, w.res_q, nullptr);
+        knn_tc_prepare_bf16_kernel<<<(unsigned)w.td, 128, 0, st>>>(X, w.dblist, D, Dp, KC, w.sw, 1, reinterpret_cast<__nv_bfloat16 *>(w.img_db),
+                                                                   nullptr, nullptr, counters + 4);
     } else {
         knn_tc_prepare_kernel<<<(unsigned)w.tq, 128, 0, st>>>(X, w.qlist, D, Dp, KC, 0, w.img_q, w.norms_q);
         knn_tc_prepare_kernel<<<(unsigned)w.td, 128, 0, st>>>(X, w.dblist, D, Dp, KC, 1, w.img_db, nullptr);
     }
     B200_CUDA(cudaGetLastError());
 
+    phases.mark("cells+images");
     // two query tiles per block when their images and the database stages fit in shared memory
     const int QH = ((size_t)(2 + kBStages) * w.image_bytes + 1024 <= 227 * 1024) ? 2 : 1;
     const long long q_tiles = (nq + TM - 1) / TM;
@@ -1651,7 +1767,7 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
             const int hi_ = (int)std::min<long long>(w.td, lo_ + win_);                                                         \
             knn_tc_filter_kernel<EPL_, FIXED_, QH_><<<(unsigned)((q_tiles + QH_ - 1) / QH_), tc_threads(QH_), smem_, st>>>(      \
                 w.img_q, w.img_db, Dp, nq, nd_pos, w.segs, w.nseg, seg_stride, stride_, (int)lo_, hi_, tau_, cap_, key_, id_,   \
-                counts_, counters + 0, bf16);                                                                                   \
+                counts_, counters + 0, bf16, w.sw, w.nks);                                                                      \
             B200_CUDA(cudaGetLastError());                                                                                      \
         }                                                                                                                       \
     } while (0)
@@ -1713,6 +1829,7 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
             knn_sample_tau_kernel<<<(unsigned)((nq + kTauThreads - 1) / kTauThreads), kTauThreads, 0, st>>>(X, D, w.qlist, nq, db_lo, a_stride,
                                                                                                     m_a, rank_a, tau);
         B200_CUDA(cudaGetLastError());
+        phases.mark("level_A");
         B200_TRY(prune());
         const unsigned sel_grid = (unsigned)((nq + 3) / 4);
         if (!direct) {
@@ -1727,16 +1844,20 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
                                                                  row_flags);
             }
             B200_CUDA(cudaGetLastError());
+            phases.mark("level_B+pick");
             B200_TRY(prune());
         }
         // level C: the L best go to the (otherwise unused) online buffers, in no particular order
         if (EPL == 8) {
             B200_KNN_FILTER(8, true, 1, tau, kFixedCap, fix_key, fix_id, counts);
+            phases.mark("level_C");
             knn_tc_pick_kernel<32><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, L, cand_key, cand_id, C, nullptr, row_flags);
         } else {
             B200_KNN_FILTER(16, true, 1, tau, kFixedCap, fix_key, fix_id, counts);
+            phases.mark("level_C");
             knn_tc_pick_kernel<64><<<sel_grid, 128, 0, st>>>(fix_key, fix_id, kFixedCap, counts, nq, L, cand_key, cand_id, C, nullptr, row_flags);
         }
+        phases.mark("pick");
         B200_CUDA(cudaGetLastError());
         final_key = cand_key;
         final_id = cand_id;
@@ -1761,6 +1882,7 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
     B200_CUDA(cudaGetLastError());
     knn_tc_collect_failed_kernel<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(failed, nq, w.qlist, flist, counters + 2);
     B200_CUDA(cudaGetLastError());
+    phases.mark("rerank");
     int h[4] = {0, 0, 0, 0};
     B200_CUDA(cudaMemcpyAsync(h, counters, sizeof(h), cudaMemcpyDeviceToHost, st));
     B200_CUDA(cudaStreamSynchronize(st));
