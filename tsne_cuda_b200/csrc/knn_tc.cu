@@ -675,6 +675,64 @@ struct TcShared {
     int abort_flag;
 };
 
+// The MMAs of one accumulator tile: three products over NKS K steps, every descriptor a register plus a register.
+// NKS is a template argument so that the loops unroll into independent instruction sequences: one thread issues
+// every MMA of the block, and whatever it computes per MMA shows in the kernel's time.
+template <bool BF16, int NKS>
+__device__ __forceinline__ void tc_issue_products(uint32_t d_tmem, uint64_t a_hi, uint64_t a_lo, uint64_t b_hi, uint64_t b_lo,
+                                                  const uint32_t (&off16)[NKS])
+{
+#pragma unroll
+    for (int ks = 0; ks < NKS; ks++) {      // hi . hi
+        if (BF16) tc_mma_bf16(d_tmem, a_hi + off16[ks], b_hi + off16[ks], kInstrDescBf16, ks ? 1u : 0u);
+        else tc_mma_tf32(d_tmem, a_hi + off16[ks], b_hi + off16[ks], kInstrDesc, ks ? 1u : 0u);
+    }
+#pragma unroll
+    for (int ks = 0; ks < NKS; ks++) {      // lo . hi
+        if (BF16) tc_mma_bf16(d_tmem, a_lo + off16[ks], b_hi + off16[ks], kInstrDescBf16, 1u);
+        else tc_mma_tf32(d_tmem, a_lo + off16[ks], b_hi + off16[ks], kInstrDesc, 1u);
+    }
+#pragma unroll
+    for (int ks = 0; ks < NKS; ks++) {      // hi . lo
+        if (BF16) tc_mma_bf16(d_tmem, a_hi + off16[ks], b_lo + off16[ks], kInstrDescBf16, 1u);
+        else tc_mma_tf32(d_tmem, a_hi + off16[ks], b_lo + off16[ks], kInstrDesc, 1u);
+    }
+}
+
+// The MMA issuer's walk over the block's database tiles (one thread).  a16 / b16 / end16: the block's images in
+// 16-byte units of shared memory; span16: what one K step reads beyond its start.  Every tile's descriptors are
+// checked against that range before they are used (an MMA that reads outside the block's shared memory is a fault).
+template <int QH, bool BF16, int NKS>
+__device__ __noinline__ void tc_issue_walk(TcShared *shp, volatile int *abort_flag, TileWalk walk, uint32_t tmem_base, uint64_t no_addr,
+                                           uint32_t a16, uint32_t b16, uint32_t image16, uint32_t spr_log, uint32_t block16,
+                                           uint32_t in_row16, uint32_t span16, uint32_t end16)
+{
+    TcShared &sh = *shp;
+    const uint32_t part16 = image16 >> 1, spr_mask = (1u << spr_log) - 1u;
+    uint32_t off16[NKS];
+#pragma unroll
+    for (int ks = 0; ks < NKS; ks++) off16[ks] = ((uint32_t)ks >> spr_log) * block16 + ((uint32_t)ks & spr_mask) * in_row16;
+    const uint32_t reach16 = off16[NKS - 1] + span16;   // the furthest a part's K steps read
+    int tile;
+    for (long long t = 0; walk.next(tile); t++) {
+        const int s = (int)(t % kBStages), b = (int)(t % kAccBufs);
+        const uint32_t ph_s = (uint32_t)((t / kBStages) & 1), ph_b = (uint32_t)((t / kAccBufs) & 1);
+        if (!mbar_wait(&sh.acc_empty[b], ph_b ^ 1u, abort_flag)) break;
+        if (!mbar_wait(&sh.full_b[s], ph_s, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t bs16 = b16 + (uint32_t)s * image16;
+        if (reach16 > part16 || a16 + QH * image16 > b16 || bs16 + image16 > end16) { *abort_flag = 1; break; }
+        const uint64_t b_hi = no_addr + (uint64_t)bs16, b_lo = b_hi + part16;
+#pragma unroll
+        for (int h = 0; h < QH; h++) {
+            const uint64_t a_hi = no_addr + (uint64_t)(a16 + (uint32_t)h * image16), a_lo = a_hi + part16;
+            tc_issue_products<BF16, NKS>(tmem_base + (uint32_t)((b * QH + h) * TN), a_hi, a_lo, b_hi, b_lo, off16);
+        }
+        tc_commit(&sh.empty_b[s]);    // the stage may be refilled once these MMAs have read it
+        tc_commit(&sh.acc_full[b]);   // the accumulator tiles are complete
+    }
+}
+
 // img_q / img_db: tile images of the query list and of the database list.  A block serves the queries
 // [blockIdx.x * QH * 128, ...) of the list (nq in all) against the database tiles of its segments
 // (segs + blockIdx.x * seg_stride, nseg[blockIdx.x * (seg_stride != 0)] of them; seg_stride = 0: one list shared by
@@ -717,7 +775,7 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
     if (threadIdx.x == 0) {
         mbar_init(&sh.full_a, 1);
         for (int s = 0; s < kBStages; s++) { mbar_init(&sh.full_b[s], 1); mbar_init(&sh.empty_b[s], 1); }
-        for (int b = 0; b < kAccBufs; b++) { mbar_init(&sh.acc_full[b], 1); mbar_init(&sh.acc_empty[b], 4 * QH); }
+        for (int b = 0; b < kAccBufs; b++) { mbar_init(&sh.acc_full[b], 1); mbar_init(&sh.acc_empty[b], (FIXED ? 8 : 4) * QH); }
         sh.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -754,76 +812,42 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
     } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
         // One thread issues every MMA, and a thread runs its dependent instructions several cycles apart: what it
-        // computes per MMA shows in the kernel's time.  So the descriptors of the query images and of both database
-        // stages are built once; a K step only adds its offset to the address field (the low 14 bits, in 16-byte
-        // units: shared-memory addresses stay far below the carry).
-        if (lane == 0) {
-            bool ok = mbar_wait(&sh.full_a, 0, abort_flag);
-            const uint32_t part16 = image_bytes >> 5;   // hi -> lo, in 16-byte units
-            // offset of K step ks inside a part: 4 KB blocks without swizzle; with it, sw / 32 steps side by side in a
-            // row (2 units apart) and blocks of 128 rows
-            const uint32_t spr_log = sw == 128 ? 2u : (sw == 64 ? 1u : 0u), spr_mask = (1u << spr_log) - 1u;
+        // computes per MMA shows in the kernel's time (descriptors built inside the K loop: 170 cycles per MMA
+        // measured, with additions only 125).  tc_issue_walk is instantiated per number of K steps, so that the
+        // MMAs of a tile are unrolled, independent instruction sequences.
+        if (lane == 0 && mbar_wait(&sh.full_a, 0, abort_flag)) {
+            // offset of K step ks inside a part, in 16-byte units: 4 KB blocks without swizzle; with it, sw / 32
+            // steps side by side in a row (2 units apart) and blocks of 128 rows
+            const uint32_t spr_log = sw == 128 ? 2u : (sw == 64 ? 1u : 0u);
             const uint32_t block16 = sw ? (128u * (uint32_t)sw) >> 4 : 256u, in_row16 = sw ? 2u : 0u;
+            const uint32_t span16 = sw ? (127u * (uint32_t)sw + 32u) >> 4 : 256u;
             const uint64_t no_addr = sw ? make_desc_swizzled(0u, (uint32_t)sw) : make_desc(0u);
             const uint32_t a16 = smem_u32(sA) >> 4, b16 = smem_u32(sB) >> 4, image16 = image_bytes >> 4;
-            // every operand address must stay inside the block's images: checked once, here, instead of trusting
-            // the arguments (an MMA that reads outside the block's shared memory is a fault)
-            {
-                const uint32_t last_step = (uint32_t)(nks - 1);
-                const uint32_t last16 = (last_step >> spr_log) * block16 + (last_step & spr_mask) * in_row16;
-                const uint32_t step_span16 = sw ? (127u * (uint32_t)sw + 32u) >> 4 : 256u;   // what one K step reads
-                if (nks < 1 || part16 * 2u != image16 || last16 + step_span16 > part16 ||
-                    b16 + kBStages * image16 > ((smem_u32(smem) + (uint32_t)(QH + kBStages) * image_bytes) >> 4)) {
-                    sh.abort_flag = 1;
-                    ok = false;
-                }
+            const uint32_t end16 = (smem_u32(smem) + (uint32_t)(QH + kBStages) * image_bytes) >> 4;
+            const TileWalk walk(my_segs, my_nseg, tile_stride, win_lo, win_hi);
+#define B200_ISSUE(NKS_)                                                                                                        \
+    case NKS_:                                                                                                                  \
+        if (bf16) tc_issue_walk<QH, true, NKS_>(&sh, abort_flag, walk, tmem_base, no_addr, a16, b16, image16, spr_log, block16,  \
+                                                in_row16, span16, end16);                                                       \
+        else tc_issue_walk<QH, false, NKS_>(&sh, abort_flag, walk, tmem_base, no_addr, a16, b16, image16, spr_log, block16,      \
+                                            in_row16, span16, end16);                                                           \
+        break;
+            switch (nks) {
+                B200_ISSUE(1) B200_ISSUE(2) B200_ISSUE(3) B200_ISSUE(4) B200_ISSUE(5) B200_ISSUE(6) B200_ISSUE(7) B200_ISSUE(8)
+                default: sh.abort_flag = 1; break;   // more K steps than a narrow image holds
             }
-            TileWalk walk(my_segs, my_nseg, tile_stride, win_lo, win_hi);
-            int tile;
-            for (long long t = 0; ok && walk.next(tile); t++) {
-                const int s = (int)(t % kBStages), b = (int)(t % kAccBufs);
-                const uint32_t ph_s = (uint32_t)((t / kBStages) & 1), ph_b = (uint32_t)((t / kAccBufs) & 1);
-                if (!mbar_wait(&sh.acc_empty[b], ph_b ^ 1u, abort_flag)) break;
-                if (!mbar_wait(&sh.full_b[s], ph_s, abort_flag)) break;
-                tc_fence_after();
-                const uint64_t b_hi = no_addr + (uint64_t)(b16 + (uint32_t)s * image16), b_lo = b_hi + part16;
-#pragma unroll 1
-                for (int h = 0; h < QH; h++) {
-                    const uint64_t a_hi = no_addr + (uint64_t)(a16 + (uint32_t)h * image16), a_lo = a_hi + part16;
-                    const uint32_t d_tmem = tmem_base + (uint32_t)((b * QH + h) * TN);
-                    if (bf16) {
-                        for (uint32_t ks = 0; ks < (uint32_t)nks; ks++) {      // hi . hi
-                            const uint32_t o = (ks >> spr_log) * block16 + (ks & spr_mask) * in_row16;
-                            tc_mma_bf16(d_tmem, a_hi + o, b_hi + o, kInstrDescBf16, ks ? 1u : 0u);
-                        }
-                        for (uint32_t ks = 0; ks < (uint32_t)nks; ks++) {      // lo . hi
-                            const uint32_t o = (ks >> spr_log) * block16 + (ks & spr_mask) * in_row16;
-                            tc_mma_bf16(d_tmem, a_lo + o, b_hi + o, kInstrDescBf16, 1u);
-                        }
-                        for (uint32_t ks = 0; ks < (uint32_t)nks; ks++) {      // hi . lo
-                            const uint32_t o = (ks >> spr_log) * block16 + (ks & spr_mask) * in_row16;
-                            tc_mma_bf16(d_tmem, a_hi + o, b_lo + o, kInstrDescBf16, 1u);
-                        }
-                    } else {
-                        for (uint32_t ks = 0; ks < (uint32_t)nks; ks++)        // hi . hi
-                            tc_mma_tf32(d_tmem, a_hi + ks * 256u, b_hi + ks * 256u, kInstrDesc, ks ? 1u : 0u);
-                        for (uint32_t ks = 0; ks < (uint32_t)nks; ks++)        // lo . hi
-                            tc_mma_tf32(d_tmem, a_lo + ks * 256u, b_hi + ks * 256u, kInstrDesc, 1u);
-                        for (uint32_t ks = 0; ks < (uint32_t)nks; ks++)        // hi . lo
-                            tc_mma_tf32(d_tmem, a_hi + ks * 256u, b_lo + ks * 256u, kInstrDesc, 1u);
-                    }
-                }
-                tc_commit(&sh.empty_b[s]);    // the stage may be refilled once these MMAs have read it
-                tc_commit(&sh.acc_full[b]);   // the accumulator tiles are complete
-            }
+#undef B200_ISSUE
         }
     } else {
         // ---------------- epilogue: one query per thread ----------------
         // 2 * QH groups of four warps; a warp reaches the TMEM lane quarter (warp % 4).  Group g belongs to
-        // query tile g % QH of the block.  With a fixed threshold it takes the database tiles
-        // t = buf, buf + 2, ... (buf = g / QH, always accumulator buffer buf) and appends to segment buf of
-        // the query's candidate buffer, so the groups share nothing; with the online threshold (per-query
-        // state that cannot be shared) only the groups with buf = 0 work, on every tile.
+        // query tile g % QH of the block.  With a fixed threshold every group works on every database tile: it
+        // takes the 64 accumulator columns buf * 64 ... (buf = g / QH) and appends to segment buf of the query's
+        // candidate buffer, so the groups share nothing.  (A warp walks its keys as one dependent chain, about
+        // 800 cycles per 32 keys: with all sixteen warps on a tile its epilogue takes half as long as with the
+        // groups taking whole tiles in turn, and the accumulator goes back to the MMAs that much earlier.)  With
+        // the online threshold (per-query state that cannot be shared) only the groups with buf = 0 work, on
+        // all columns of every tile.
         const int group = warp >> 2, quarter = warp & 3;
         const int buf = group / QH, half = group % QH;
         const bool active = FIXED || buf == 0;
@@ -900,21 +924,21 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
         int tile;
         for (long long t = 0; walk.next(tile); t++) {
             const int b = (int)(t % kAccBufs);
-            if (FIXED && b != buf) continue;
             const uint32_t ph_b = (uint32_t)((t / kAccBufs) & 1);
             if (!mbar_wait(&sh.acc_full[b], ph_b, abort_flag, 32)) break;
             tc_fence_after();
             const long long p0 = (long long)tile * TN;
             const bool inside = p0 + TN <= nd_pos;
             const uint32_t tcol = lane_base + (uint32_t)(b * QH * TN);
-            // one copy of the chunk code, executed four times: the epilogue is issue- and
-            // instruction-fetch-bound, so small code beats overlapping the (fast) TMEM reads
+            // one copy of the chunk code, executed once per 32 columns: small code beats overlapping the TMEM reads
+            // (16 keys per read with the next read in flight while these are compared was 4 % slower)
+            const int c_lo = FIXED ? buf * (TN / 2) : 0, c_hi = FIXED ? c_lo + TN / 2 : TN;   // this group's columns
 #pragma unroll 1
-            for (int c0 = 0; c0 < TN; c0 += 32) {
+            for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
                 uint32_t r[32];
                 tc_ld32_issue(tcol + (uint32_t)c0, r);
                 tc_ld32_wait(r);
-                if (c0 == TN - 32) {   // the last read has landed: hand the accumulator buffer back
+                if (c0 == c_hi - 32) {   // the last read has landed: hand the accumulator buffer back
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sh.acc_empty[b]);
@@ -1734,6 +1758,7 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
 
     phases.mark("cells+images");
     // two query tiles per block when their images and the database stages fit in shared memory
+    // (one query tile per block, two blocks per SM: 3 % faster at N = 10^6, D = 50, for twice the L2 traffic; not used)
     const int QH = ((size_t)(2 + kBStages) * w.image_bytes + 1024 <= 227 * 1024) ? 2 : 1;
     const long long q_tiles = (nq + TM - 1) / TM;
     // Segments of the blocks: all database tiles (one shared list) unless the cells prune (per block).
