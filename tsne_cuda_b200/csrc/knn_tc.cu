@@ -232,11 +232,6 @@ __device__ __forceinline__ uint64_t make_desc_swizzled(uint32_t saddr, uint32_t 
 constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
 // the same with bf16 A and B (format 1 of kind::f16); one K step is 32 operand bytes per row in either kind
 constexpr uint32_t kInstrDescBf16 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
-__device__ __forceinline__ void tc_mma_step(bool bf16, uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t accumulate)
-{
-    if (bf16) tc_mma_bf16(d_tmem, make_desc(a_addr), make_desc(b_addr), kInstrDescBf16, accumulate);
-    else tc_mma_tf32(d_tmem, make_desc(a_addr), make_desc(b_addr), kInstrDesc, accumulate);
-}
 
 
 // ------------------------------------------------------------------------------------------------
@@ -1069,6 +1064,8 @@ knn_tc_wide_kernel(const float *__restrict__ img_q, const float *__restrict__ im
             int unit;
             long long it = 0, n_unit = 0;
             bool ok = true;
+            const uint64_t no_addr = make_desc(0u);
+            const uint32_t stage16 = smem_u32(smem) >> 4, chunk16 = kWideChunkBytes >> 4;
             while (ok && walk.next(unit)) {
                 // the accumulators of the previous unit must have been read
                 if (!mbar_wait(&sh.acc_empty, (uint32_t)((n_unit & 1) ^ 1), abort_flag)) break;
@@ -1077,21 +1074,37 @@ knn_tc_wide_kernel(const float *__restrict__ img_q, const float *__restrict__ im
                     const uint32_t ph = (uint32_t)((it / kWideStages) & 1);
                     if (!mbar_wait(&sh.full[s], ph, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-#pragma unroll 1
+                    // descriptors by addition only (see the narrow kernel's issuer); a stage's four chunk images
+                    // are kWideChunkBytes apart, lo follows hi after kSteps blocks of 4 KB
+                    const uint64_t st0 = no_addr + (uint64_t)(stage16 + (uint32_t)s * 4u * chunk16);
+#pragma unroll
                     for (int pair = 0; pair < 4; pair++) {
                         const int h = pair >> 1, g = pair & 1;
-                        const uint32_t a_hi = smem_u32(stage_ptr(s, h)), a_lo = a_hi + kSteps * 4096u;
-                        const uint32_t b_hi = smem_u32(stage_ptr(s, 2 + g)), b_lo = b_hi + kSteps * 4096u;
+                        const uint64_t a_hi = st0 + (uint64_t)((uint32_t)h * chunk16), a_lo = a_hi + kSteps * 256u;
+                        const uint64_t b_hi = st0 + (uint64_t)((uint32_t)(2 + g) * chunk16), b_lo = b_hi + kSteps * 256u;
                         const uint32_t d_tmem = tmem_base + (uint32_t)((h * 2 + g) * TN);
-                        uint32_t acc = (c > 0) ? 1u : 0u;
-                        for (int ks = 0; ks < kSteps; ks++) {      // hi . hi
-                            tc_mma_step(bf16, d_tmem, a_hi + ks * 4096u, b_hi + ks * 4096u, acc);
-                            acc = 1;
+                        const uint32_t acc0 = (c > 0) ? 1u : 0u;
+                        if (bf16) {
+#pragma unroll
+                            for (int ks = 0; ks < kSteps; ks++)        // hi . hi
+                                tc_mma_bf16(d_tmem, a_hi + ks * 256u, b_hi + ks * 256u, kInstrDescBf16, ks ? 1u : acc0);
+#pragma unroll
+                            for (int ks = 0; ks < kSteps; ks++)        // lo . hi
+                                tc_mma_bf16(d_tmem, a_lo + ks * 256u, b_hi + ks * 256u, kInstrDescBf16, 1u);
+#pragma unroll
+                            for (int ks = 0; ks < kSteps; ks++)        // hi . lo
+                                tc_mma_bf16(d_tmem, a_hi + ks * 256u, b_lo + ks * 256u, kInstrDescBf16, 1u);
+                        } else {
+#pragma unroll
+                            for (int ks = 0; ks < kSteps; ks++)        // hi . hi
+                                tc_mma_tf32(d_tmem, a_hi + ks * 256u, b_hi + ks * 256u, kInstrDesc, ks ? 1u : acc0);
+#pragma unroll
+                            for (int ks = 0; ks < kSteps; ks++)        // lo . hi
+                                tc_mma_tf32(d_tmem, a_lo + ks * 256u, b_hi + ks * 256u, kInstrDesc, 1u);
+#pragma unroll
+                            for (int ks = 0; ks < kSteps; ks++)        // hi . lo
+                                tc_mma_tf32(d_tmem, a_hi + ks * 256u, b_lo + ks * 256u, kInstrDesc, 1u);
                         }
-                        for (int ks = 0; ks < kSteps; ks++)        // lo . hi
-                            tc_mma_step(bf16, d_tmem, a_lo + ks * 4096u, b_hi + ks * 4096u, 1);
-                        for (int ks = 0; ks < kSteps; ks++)        // hi . lo
-                            tc_mma_step(bf16, d_tmem, a_hi + ks * 4096u, b_lo + ks * 4096u, 1);
                     }
                     tc_commit(&sh.empty[s]);
                 }
@@ -1281,12 +1294,36 @@ __global__ void knn_gather_rows_kernel(const float *__restrict__ X, const int *_
 // ------------------------------------------------------------------------------------------------
 // exact re-rank + proof
 // ------------------------------------------------------------------------------------------------
+// The canonical distance: differences, squares and the running sum rounded one by one, in the order of the
+// dimensions.  Rows are read 16 or 8 bytes at a time where D keeps them aligned (a lane reads a row of its own,
+// so wide loads mean fewer sectors touched per instruction); the arithmetic and its order do not change.
+__device__ __forceinline__ float canon_step(float acc, float x, float y)
+{
+    const float t = __fsub_rn(x, y);
+    return __fadd_rn(acc, __fmul_rn(t, t));
+}
 __device__ __forceinline__ float canon_dist(const float *__restrict__ a, const float *__restrict__ b, int D)
 {
     float acc = 0.0f;
-    for (int d = 0; d < D; d++) {
-        const float t = __fsub_rn(a[d], b[d]);
-        acc = __fadd_rn(acc, __fmul_rn(t, t));
+    const unsigned long long both = (unsigned long long)(size_t)a | (unsigned long long)(size_t)b;
+    if ((D & 3) == 0 && (both & 15) == 0) {
+        const float4 *a4 = reinterpret_cast<const float4 *>(a), *b4 = reinterpret_cast<const float4 *>(b);
+        for (int d = 0; d < (D >> 2); d++) {
+            const float4 u = a4[d], v = b4[d];
+            acc = canon_step(acc, u.x, v.x);
+            acc = canon_step(acc, u.y, v.y);
+            acc = canon_step(acc, u.z, v.z);
+            acc = canon_step(acc, u.w, v.w);
+        }
+    } else if ((D & 1) == 0 && (both & 7) == 0) {
+        const float2 *a2 = reinterpret_cast<const float2 *>(a), *b2 = reinterpret_cast<const float2 *>(b);
+        for (int d = 0; d < (D >> 1); d++) {
+            const float2 u = a2[d], v = b2[d];
+            acc = canon_step(acc, u.x, v.x);
+            acc = canon_step(acc, u.y, v.y);
+        }
+    } else {
+        for (int d = 0; d < D; d++) acc = canon_step(acc, a[d], b[d]);
     }
     return acc;
 }
