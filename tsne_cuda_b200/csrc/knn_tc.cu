@@ -738,13 +738,17 @@ __device__ __noinline__ void tc_issue_walk(TcShared *shp, volatile int *abort_fl
 // where the database had fewer points).  FIXED = true: threshold tau[query] fixed, two segments of cap/2
 // entries per query; counts[2*query + buffer] receives the number of entries appended to each (bit 30 set
 // if it overflowed); knn_tc_pick_kernel finishes.
-template <int EPL, bool FIXED, int QH>
+// RANKED (with FIXED = false): no candidate buffers at all; every query thread keeps its 16 smallest keys in
+// registers and rank_out[query] receives the one of rank `rank` (0-based, < 16) when the scan ends: the first
+// threshold level, a scan of a few thousand sample points.
+template <int EPL, bool FIXED, int QH, bool RANKED = false>
 __global__ void __launch_bounds__(tc_threads(QH), 1)
 knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int Dp, long long nq, long long nd_pos,
                      const int2 *__restrict__ segs, const int *__restrict__ nseg, int seg_stride, int tile_stride, int win_lo,
                      int win_hi, const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id, int *counts,
-                     int *error_flag, int bf16, int sw, int nks)
+                     int *error_flag, int bf16, int sw, int nks, int rank = 0, float *__restrict__ rank_out = nullptr)
 {
+    static_assert(!(RANKED && FIXED), "the ranked scan keeps its own threshold");
     // bf16: the images hold bf16 pairs; sw != 0: in swizzled rows of sw bytes (else core matrices without swizzle);
     // nks: K steps of 32 operand bytes per row to multiply
     constexpr int C = 32 * EPL;   // capacity handled by one compaction
@@ -869,6 +873,9 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
         // independent three-input min operations and one comparison.  Only if the minimum beats the
         // threshold (rare once the scan is under way) are the quarters whose minimum does so compared
         // element by element; everything is indexed statically, so the keys never leave the registers.
+        float top[RANKED ? 16 : 1];
+#pragma unroll
+        for (int i = 0; i < (RANKED ? 16 : 1); i++) top[i] = INFINITY;
         auto process_chunk = [&](const uint32_t (&r)[32], long long col0, bool tile_inside) {
             float m4[4];
 #pragma unroll
@@ -889,7 +896,18 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
                             const float key = __uint_as_float(r[c]);
                             const long long cid = col0 + c;
                             const bool pass = key < thr && (tile_inside || cid < nd_pos);
-                            if (pass) {
+                            if constexpr (RANKED) {
+                                if (pass) {   // replaces the largest of the 16 and sinks to its place
+                                    top[15] = key;
+#pragma unroll
+                                    for (int i = 15; i > 0; i--) {
+                                        const float lo = fminf(top[i - 1], top[i]), hi = fmaxf(top[i - 1], top[i]);
+                                        top[i - 1] = lo;
+                                        top[i] = hi;
+                                    }
+                                    thr = top[15];
+                                }
+                            } else if (pass) {
                                 __stcg(bk + cnt, key);
                                 __stcg(bi + cnt, (int32_t)cid);
                                 cnt++;
@@ -898,7 +916,9 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
                     }
                 }
             }
-            if (FIXED) {
+            if constexpr (RANKED) {
+                // nothing is buffered
+            } else if (FIXED) {
                 // a chunk appends at most 32 entries: stop a buffer that could overflow in the next one
                 if (cnt > seg_cap - 32) { overflow = true; thr = -INFINITY; }
             } else {
@@ -945,6 +965,13 @@ knn_tc_filter_kernel(const float *__restrict__ img_q, const float *__restrict__ 
             // The final selection is a separate kernel (one warp per query, thousands in flight): it is a chain of
             // dependent global round trips, which the warps of this block would walk through one query at a time.
             if (serve) counts[gq * kAccBufs + buf] = cnt | (overflow ? 0x40000000 : 0);
+        } else if (RANKED) {
+            if (serve) {
+                float t = top[0];
+#pragma unroll
+                for (int i = 1; i < (RANKED ? 16 : 1); i++) t = (i == rank) ? top[i] : t;
+                rank_out[gq] = t;
+            }
         } else if (active) {
             // online threshold (small databases): one last compaction leaves the L best, sorted, in front
             unsigned m = __ballot_sync(0xffffffffu, serve);
@@ -992,12 +1019,14 @@ struct WideShared {
     int abort_flag;
 };
 
-template <int EPL>
+// RANKED: the first threshold level (see the narrow kernel): no buffers, the warps of the unit's first database tile
+// read both tiles and keep the 16 smallest keys of their queries in registers; positions from n_pos on are padding.
+template <int EPL, bool RANKED = false>
 __global__ void __launch_bounds__(tc_threads(2), 1)
 knn_tc_wide_kernel(const float *__restrict__ img_q, const float *__restrict__ img_db, int n_chunks, long long nq,
                    const int2 *__restrict__ segs, const int *__restrict__ nseg, int seg_stride, int unit_stride, int win_lo,
                    int win_hi, const float *__restrict__ tau, int cap, float *cand_key, int32_t *cand_id, int *counts,
-                   int *error_flag, int bf16)
+                   int *error_flag, int bf16, int rank = 0, float *__restrict__ rank_out = nullptr, long long n_pos = 0)
 {
     constexpr int kProducerWarp = 16, kMmaWarp = 17;
     constexpr uint32_t kTmemCols = 512;
@@ -1021,7 +1050,7 @@ knn_tc_wide_kernel(const float *__restrict__ img_q, const float *__restrict__ im
     if (threadIdx.x == 0) {
         for (int s = 0; s < kWideStages; s++) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 1); }
         mbar_init(&sh.acc_full, 1);
-        mbar_init(&sh.acc_empty, 16);
+        mbar_init(&sh.acc_empty, RANKED ? 8 : 16);
         sh.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1118,65 +1147,98 @@ knn_tc_wide_kernel(const float *__restrict__ img_q, const float *__restrict__ im
         const int seg_cap = cap / 2;
         const int row = quarter * 32 + lane;
         const long long gq = (qt + half) * TM + row;
-        const bool serve = gq < nq;
+        const bool active = !RANKED || g == 0;
+        const bool serve = gq < nq && active;
         float *bk = cand_key + (serve ? gq : 0) * cap + g * seg_cap;
         int32_t *bi = cand_id + (serve ? gq : 0) * cap + g * seg_cap;
-        float thr = serve ? tau[gq] : -INFINITY;
+        float thr = serve ? (RANKED ? INFINITY : tau[gq]) : -INFINITY;
         int cnt = 0;
         bool overflow = false;
-        if (serve) {
+        if (!RANKED && serve) {
             const int c0 = counts[gq * 2 + g];
             cnt = c0 & 0x3fffffff;
             overflow = (c0 & 0x40000000) != 0;
             if (overflow) thr = -INFINITY;
         }
-        const uint32_t tcol = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((half * 2 + g) * TN);
-        TileWalk walk(my_segs, my_nseg, unit_stride, win_lo, win_hi);
-        int unit;
-        for (long long n_unit = 0; walk.next(unit); n_unit++) {
-            if (!mbar_wait(&sh.acc_full, (uint32_t)(n_unit & 1), abort_flag, 32)) break;
-            tc_fence_after();
-            const long long p0 = (long long)unit * kWideUnit + (long long)g * TN;
-#pragma unroll 1
-            for (int c0 = 0; c0 < TN; c0 += 32) {
-                uint32_t r[32];
-                tc_ld32_issue(tcol + (uint32_t)c0, r);
-                tc_ld32_wait(r);
-                if (c0 == TN - 32) {   // the last read has landed: hand the accumulators back
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&sh.acc_empty);
-                }
-                float m4[4];
+        float top[RANKED ? 16 : 1];
+#pragma unroll
+        for (int i = 0; i < (RANKED ? 16 : 1); i++) top[i] = INFINITY;
+        // 32 keys of this thread's query: positions pos0 ...
+        auto process_chunk = [&](const uint32_t (&r)[32], long long pos0) {
+            float m4[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float a = min3(__uint_as_float(r[8 * q]), __uint_as_float(r[8 * q + 1]), __uint_as_float(r[8 * q + 2]));
+                const float b = min3(__uint_as_float(r[8 * q + 3]), __uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
+                const float c = fminf(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+                m4[q] = min3(a, b, c);
+            }
+            const float mn = fminf(min3(m4[0], m4[1], m4[2]), m4[3]);
+            if (mn < thr) {
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    const float a = min3(__uint_as_float(r[8 * q]), __uint_as_float(r[8 * q + 1]), __uint_as_float(r[8 * q + 2]));
-                    const float b = min3(__uint_as_float(r[8 * q + 3]), __uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
-                    const float c = fminf(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
-                    m4[q] = min3(a, b, c);
-                }
-                const float mn = fminf(min3(m4[0], m4[1], m4[2]), m4[3]);
-                if (mn < thr) {
+                    if (m4[q] < thr) {
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        if (m4[q] < thr) {
+                        for (int e = 0; e < 8; e++) {
+                            const int c = q * 8 + e;
+                            const float key = __uint_as_float(r[c]);
+                            if constexpr (RANKED) {
+                                if (key < thr && pos0 + c < n_pos) {   // replaces the largest of the 16 and sinks to its place
+                                    top[15] = key;
 #pragma unroll
-                            for (int e = 0; e < 8; e++) {
-                                const int c = q * 8 + e;
-                                const float key = __uint_as_float(r[c]);
-                                if (key < thr) {   // padding rows carry a huge norm and never pass a finite threshold
-                                    __stcg(bk + cnt, key);
-                                    __stcg(bi + cnt, (int32_t)(p0 + c0 + c));
-                                    cnt++;
+                                    for (int i = 15; i > 0; i--) {
+                                        const float lo = fminf(top[i - 1], top[i]), hi = fmaxf(top[i - 1], top[i]);
+                                        top[i - 1] = lo;
+                                        top[i] = hi;
+                                    }
+                                    thr = top[15];
                                 }
+                            } else if (key < thr) {   // padding rows carry a huge norm and never pass a finite threshold
+                                __stcg(bk + cnt, key);
+                                __stcg(bi + cnt, (int32_t)(pos0 + c));
+                                cnt++;
                             }
                         }
                     }
                 }
-                if (cnt > seg_cap - 32) { overflow = true; thr = -INFINITY; }
+            }
+            if (!RANKED && cnt > seg_cap - 32) { overflow = true; thr = -INFINITY; }
+        };
+        const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        TileWalk walk(my_segs, active ? my_nseg : 0, unit_stride, win_lo, win_hi);
+        int unit;
+        for (long long n_unit = 0; walk.next(unit); n_unit++) {
+            if (!mbar_wait(&sh.acc_full, (uint32_t)(n_unit & 1), abort_flag, 32)) break;
+            tc_fence_after();
+            // this warp's database tiles of the unit: its own, or both when ranked
+#pragma unroll 1
+            for (int gg = RANKED ? 0 : g; gg <= (RANKED ? 1 : g); gg++) {
+                const uint32_t tcol = tlane + (uint32_t)((half * 2 + gg) * TN);
+                const long long p0 = (long long)unit * kWideUnit + (long long)gg * TN;
+#pragma unroll 1
+                for (int c0 = 0; c0 < TN; c0 += 32) {
+                    uint32_t r[32];
+                    tc_ld32_issue(tcol + (uint32_t)c0, r);
+                    tc_ld32_wait(r);
+                    if (c0 == TN - 32 && gg == (RANKED ? 1 : g)) {   // the last read has landed: hand the accumulators back
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sh.acc_empty);
+                    }
+                    process_chunk(r, p0 + c0);
+                }
             }
         }
-        if (serve) counts[gq * 2 + g] = cnt | (overflow ? 0x40000000 : 0);
+        if constexpr (RANKED) {
+            if (serve) {
+                float t = top[0];
+#pragma unroll
+                for (int i = 1; i < 16; i++) t = (i == rank) ? top[i] : t;
+                rank_out[gq] = t;
+            }
+        } else {
+            if (serve) counts[gq * 2 + g] = cnt | (overflow ? 0x40000000 : 0);
+        }
     }
     // ---------------- teardown ----------------
     tc_fence_before();
@@ -1434,6 +1496,16 @@ knn_tc_rerank_kernel(const float *__restrict__ X, int D, const int *__restrict__
 // plain fp32 FMA sums: this threshold only has to be roughly right (it sizes the candidate set of the
 // next level).  One query per thread, held in registers; sample points staged 32 at a time in shared
 // memory and read as broadcast float4.
+// The sample of the first threshold level as a list of rows: position k < m holds the jittered systematic sample
+// point s_lo + k * s_stride + jitter_k (a plain stride would alias with any periodic ordering of the data), the
+// positions from m on are padding.
+__global__ void knn_sample_list_kernel(int *__restrict__ list, long long n_pos, int m, long long s_lo, long long s_stride)
+{
+    const long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= n_pos) return;
+    list[k] = (k < m) ? (int)(s_lo + k * s_stride + (long long)(((unsigned long long)k * 2654435761ull) % (unsigned long long)s_stride)) : -1;
+}
+
 constexpr int kTauThreads = 128;
 __global__ void __launch_bounds__(kTauThreads)
 knn_sample_tau_kernel(const float *__restrict__ X, int D, const int *__restrict__ qlist, long long nq, long long s_lo, long long s_stride,
@@ -1613,6 +1685,7 @@ bool knn_tc_supported(int64_t nd, int D, int K)
 // candidate buffer entries per query in a fixed-threshold pass: 8 L (two halves of 4 L for ~1.5 L expected each)
 static int fixed_cap(int K) { return (K + 32 <= 128) ? 1024 : 2048; }
 constexpr int kSampleStride = 16;    // the sample pass looks at every 16th database tile
+constexpr int kMaxSampleTiles = 128; // first threshold level: at most 16 384 sample points
 constexpr long long kTwoPassMinTiles = 512;   // below this many database tiles the online pass alone is used
 
 // Device workspace of launch_knn_tc, carved in this order.
@@ -1625,6 +1698,8 @@ struct TcWorkspace {
     float *img_q, *img_db;
     double *norms_q;
     float2 *res_q;             // bf16 form: norms of the lo parts and of the leftovers of every query
+    float *img_s;              // images of the sample of the first threshold level (two-pass searches)
+    int *slist;
     int *qlist, *dblist;
     float *xp;   // database rows in list order (cells only)
     unsigned char *cell_q, *cell_db;
@@ -1675,6 +1750,11 @@ static TcWorkspace tc_carve(void *base, int D, int K, long long nq, long long nd
     w.qlist = reinterpret_cast<int *>(take(sizeof(int) * (size_t)w.tq * TM));
     w.dblist = reinterpret_cast<int *>(take(sizeof(int) * (size_t)w.td * TN));
     w.xp = (w.cells > 1) ? reinterpret_cast<float *>(take(sizeof(float) * (size_t)w.td * TN * D)) : nullptr;
+    w.img_s = nullptr; w.slist = nullptr;
+    if (two_pass) {
+        w.img_s = reinterpret_cast<float *>(take((size_t)kMaxSampleTiles * w.image_bytes));
+        w.slist = reinterpret_cast<int *>(take(sizeof(int) * (size_t)kMaxSampleTiles * TN));
+    }
     w.cell_q = reinterpret_cast<unsigned char *>(take((size_t)nq));
     w.cell_db = reinterpret_cast<unsigned char *>(take((size_t)nd));
     w.tab = reinterpret_cast<CellTable *>(take(sizeof(CellTable)));
@@ -1884,12 +1964,43 @@ int launch_knn_tc(const float *X, int64_t N, int D, int K, int64_t q_lo, int64_t
         const double a_target = direct ? 3.0 * L * m_a / (double)db_n : 300.0 * m_a / b_points;
         const int rank_a = std::min(16, std::max(4, (int)(a_target + 0.5))) - 1;
         const int rank_b = std::max(4, (3 * L + kSampleStride - 1) / kSampleStride) - 1;
-        if (wide)
-            knn_sample_tau_wide_kernel<<<(unsigned)((nq + kTauThreads - 1) / kTauThreads), kTauThreads, 0, st>>>(X, D, w.qlist, nq, db_lo,
-                                                                                                         a_stride, m_a, rank_a, tau);
-        else
-            knn_sample_tau_kernel<<<(unsigned)((nq + kTauThreads - 1) / kTauThreads), kTauThreads, 0, st>>>(X, D, w.qlist, nq, db_lo, a_stride,
-                                                                                                    m_a, rank_a, tau);
+        if (getenv("B200TSNE_KNN_LEVEL_A") && strcmp(getenv("B200TSNE_KNN_LEVEL_A"), "simt") == 0) {
+            if (wide)
+                knn_sample_tau_wide_kernel<<<(unsigned)((nq + kTauThreads - 1) / kTauThreads), kTauThreads, 0, st>>>(X, D, w.qlist, nq, db_lo,
+                                                                                                             a_stride, m_a, rank_a, tau);
+            else
+                knn_sample_tau_kernel<<<(unsigned)((nq + kTauThreads - 1) / kTauThreads), kTauThreads, 0, st>>>(X, D, w.qlist, nq, db_lo,
+                                                                                                        a_stride, m_a, rank_a, tau);
+        } else {
+            // the same sample on the tensor cores: its points as a few tile images, every query thread keeping its
+            // 16 smallest keys in registers (the keys differ from the fp32 sums of the CUDA-core kernels by the
+            // filter's error only, and this threshold has to be roughly right, no more)
+            const int ts = wide ? (m_a + kWideUnit - 1) / kWideUnit * 2 : (m_a + TN - 1) / TN;
+            knn_sample_list_kernel<<<(unsigned)((ts * TN + 255) / 256), 256, 0, st>>>(w.slist, (long long)ts * TN, m_a, db_lo, a_stride);
+            if (bf16)
+                knn_tc_prepare_bf16_kernel<<<(unsigned)ts, 128, 0, st>>>(X, w.slist, D, Dp, KC, w.sw, 1, reinterpret_cast<__nv_bfloat16 *>(w.img_s),
+                                                                         nullptr, nullptr, nullptr);
+            else
+                knn_tc_prepare_kernel<<<(unsigned)ts, 128, 0, st>>>(X, w.slist, D, Dp, KC, 1, w.img_s, nullptr);
+            knn_single_segment_kernel<<<1, 1, 0, st>>>(w.segs, w.nseg, wide ? ts / 2 : ts);
+            B200_CUDA(cudaGetLastError());
+            if (wide) {
+                const size_t smem_a = (size_t)kWideStages * 4 * kWideChunkBytes;
+                B200_CUDA(cudaFuncSetAttribute(knn_tc_wide_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a));
+                knn_tc_wide_kernel<8, true><<<(unsigned)((q_tiles + 1) / 2), tc_threads(2), smem_a, st>>>(
+                    w.img_q, w.img_s, Dp / KC, nq, w.segs, w.nseg, 0, 1, 0, ts / 2, nullptr, 0, nullptr, nullptr, nullptr, counters + 0, bf16,
+                    rank_a, tau, (long long)m_a);
+            } else {
+                const size_t smem_a = (size_t)(1 + kBStages) * w.image_bytes;
+                B200_CUDA(cudaFuncSetAttribute(knn_tc_filter_kernel<8, false, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a));
+                knn_tc_filter_kernel<8, false, 1, true><<<(unsigned)q_tiles, tc_threads(1), smem_a, st>>>(
+                    w.img_q, w.img_s, Dp, nq, (long long)m_a, w.segs, w.nseg, 0, 1, 0, ts, nullptr, 0, nullptr, nullptr, nullptr, counters + 0,
+                    bf16, w.sw, w.nks, rank_a, tau);
+            }
+            B200_CUDA(cudaGetLastError());
+            // back to all database tiles
+            knn_single_segment_kernel<<<1, 1, 0, st>>>(w.segs, w.nseg, wide ? (int)(w.td / 2) : (int)((nd + TN - 1) / TN));
+        }
         B200_CUDA(cudaGetLastError());
         phases.mark("level_A");
         B200_TRY(prune());
