@@ -85,15 +85,20 @@ perplexity_kernel(const float *__restrict__ d2, long long n_rows, int K, float p
 
 // One warp per row i.  For each slot s: j = ids[i][s]; scan the K ids of row j for i and add the
 // matching p[j][.]; divide by 2N in double like the reference.
+// visit (optional, n_rows entries, all inside [row_lo, row_lo + n_rows)): the order in which the warps take the rows.
+// The kernel is bound by the K random row reads per row (32 GB at N = 10^6, K = 90); rows visited cluster by cluster
+// find the rows of their neighbours, which lie in the same cluster, in L2.
 constexpr int kSymWarps = 8;
 __global__ void __launch_bounds__(kSymWarps * 32)
 symmetrize_kernel(const float *__restrict__ p, const int32_t *__restrict__ ids, long long N, int K, long long row_lo,
-                  long long n_rows, float *__restrict__ P_rows)
+                  long long n_rows, const int32_t *__restrict__ visit, float *__restrict__ P_rows)
 {
     const int lane = threadIdx.x & 31;
-    const long long r = (long long)blockIdx.x * kSymWarps + (threadIdx.x >> 5);
-    if (r >= n_rows) return;
-    const long long i = row_lo + r;
+    const long long w = (long long)blockIdx.x * kSymWarps + (threadIdx.x >> 5);
+    if (w >= n_rows) return;
+    const long long i = visit ? (long long)visit[w] : row_lo + w;
+    const long long r = i - row_lo;
+    if (r < 0 || r >= n_rows) return;
     const double inv = 2.0 * (double)N;
     for (int s0 = 0; s0 < K; s0 += 32) {
         const int s_mine = s0 + lane;
@@ -231,11 +236,11 @@ int launch_perplexity(const float *d2, int64_t n_rows, int K, float perplexity, 
 }
 
 int launch_symmetrize(const float *p_all, const int32_t *ids_all, int64_t N, int K, int64_t row_lo, int64_t row_hi,
-                      float *P_rows, cudaStream_t st)
+                      float *P_rows, cudaStream_t st, const int32_t *visit)
 {
     const long long n_rows = row_hi - row_lo;
     if (n_rows <= 0) return 0;
-    symmetrize_kernel<<<nblk(n_rows, kSymWarps), kSymWarps * 32, 0, st>>>(p_all, ids_all, N, K, row_lo, n_rows, P_rows);
+    symmetrize_kernel<<<nblk(n_rows, kSymWarps), kSymWarps * 32, 0, st>>>(p_all, ids_all, N, K, row_lo, n_rows, visit, P_rows);
     B200_CUDA(cudaGetLastError());
     return 0;
 }

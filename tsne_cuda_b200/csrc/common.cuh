@@ -109,8 +109,9 @@ int launch_reverse_only_count(const float *p_all, const int32_t *ids_all, int64_
                               int64_t *count_host, cudaStream_t st);
 int launch_reverse_only_fill(const float *p_all, const int32_t *ids_all, int64_t N, int K, int64_t row_lo, int64_t row_hi, const int *ptr,
                              int *cursor, int32_t *ext_ids, float *ext_val, cudaStream_t st);
+// visit (optional): row_hi - row_lo row numbers inside [row_lo, row_hi), the order in which the rows are taken
 int launch_symmetrize(const float *p_all, const int32_t *ids_all, int64_t N, int K, int64_t row_lo, int64_t row_hi,
-                      float *P_rows, cudaStream_t st);
+                      float *P_rows, cudaStream_t st, const int32_t *visit = nullptr);
 
 // attractive.cu   (Y2: AoS float2 [N]; F2: AoS float2, rows [row_lo,row_hi) written at their global index)
 int launch_attractive(const float *P_rows, const int32_t *ids_rows, const float2 *Y2, int64_t N, int K, int64_t row_lo,

@@ -626,7 +626,8 @@ int Session::affinities_from_points(const float *X_host, int D, float perplexity
         B200_TRY(comm->all_gather_inplace(p_all, sizeof(float) * (size_t)chunk * K, stream));
         ids_for_sym = ids_all;
     }
-    B200_TRY(launch_symmetrize(p_all, ids_for_sym, N, K, row_lo, row_hi, P, stream));
+    // one GPU: the rows are taken in the cell order, cluster by cluster (the rows a row looks up are then in L2)
+    B200_TRY(launch_symmetrize(p_all, ids_for_sym, N, K, row_lo, row_hi, P, stream, (!multi && cell_order && row_lo == 0 && row_hi == N) ? cell_order : nullptr));
     extra = ExtraEntries();
     if (symmetric_p || (getenv("B200TSNE_SYMMETRIC_P") && atoi(getenv("B200TSNE_SYMMETRIC_P")) != 0)) {
         // the mirror images of the one-directional edges whose target is an owned row (affinities.cu)
