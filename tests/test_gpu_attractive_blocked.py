@@ -116,3 +116,42 @@ def test_session_uses_the_blocked_copy_and_matches_the_row_kernel(engine, oracle
     assert np.array_equal(out["blocked"][0], out["rows"][0]) and np.array_equal(out["blocked"][1], out["rows"][1])
     assert rel_l2(out["blocked"][2], out["rows"][2]) < 1e-5
     assert abs(out["blocked"][3] - out["rows"][3]) / out["rows"][3] < 0.01
+
+
+def test_state_in_cell_order_and_in_natural_order_agree(engine, oracle_cpu, monkeypatch):
+    """On one GPU the session keeps embedding, momentum and gains in the blocked copy's point order and converts at
+    its entry points (B200TSNE_ATTRACTIVE_RESIDENT=0 keeps the natural order and converts around the kernel instead).
+    Both must show the caller the same values: after one iteration to rounding (the kernel's atomics add in any
+    order), the optimizer state row by row, an embedding set after the affinities or before them, and a state
+    saved in one form must resume in the other."""
+    n, k = 30000, 40
+    X = mixture(n, 16, 5)
+    Y0 = (1e-4 * np.random.default_rng(2).standard_normal((2, n))).astype(np.float32)
+    got = {}
+    for mode in ("resident", "natural"):
+        if mode == "natural":
+            monkeypatch.setenv("B200TSNE_ATTRACTIVE_RESIDENT", "0")
+        else:
+            monkeypatch.delenv("B200TSNE_ATTRACTIVE_RESIDENT", raising=False)
+        with engine.Session(n, k) as s:
+            s.set_schedule(200.0, 12.0, 250, 0.5, 0.8)
+            s.set_embedding(Y0)                      # before the affinities: converted when the copy is built
+            s.affinities_from_points(X, 15.0, 1e-3)
+            assert s.attractive_mode()[0] == 1
+            assert np.array_equal(s.get_embedding(), Y0)
+            s.run(1)
+            Y1 = s.get_embedding()
+            s.run(9)
+            got[mode] = (Y1,) + tuple(s.get_state())
+    assert rel_l2(got["resident"][0], got["natural"][0]) < 1e-5
+    Ya, ma, ga, step_a = got["resident"][1:]
+    Yb, mb, gb, step_b = got["natural"][1:]
+    assert step_a == step_b == 10
+    assert rel_l2(Ya, Yb) < 1e-4 and rel_l2(ma, mb) < 1e-3 and np.mean(ga != gb) < 1e-3
+    # a state saved from the cell-ordered session resumes in a natural-order one (env still "0") and continues alike
+    with engine.Session(n, k) as s:
+        s.set_schedule(200.0, 12.0, 250, 0.5, 0.8)
+        s.affinities_from_points(X, 15.0, 1e-3)
+        s.set_state(Ya, ma, ga, step_a)
+        Y2, m2, g2, st2 = s.get_state()
+        assert np.array_equal(Y2, Ya) and np.array_equal(m2, ma) and np.array_equal(g2, ga) and st2 == step_a

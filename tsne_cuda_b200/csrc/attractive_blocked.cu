@@ -1047,11 +1047,18 @@ int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const flo
 // (Reading the force in cell order from the update kernel and letting it keep the cell-ordered embedding current
 // instead of these two conversion kernels was measured on one GPU: the update kernel's three scattered 8-byte
 // accesses per point cost it 148 us more - 169 instead of 21 - against the 17 us the conversions take.)
-int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st)
+int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st, bool in_cell_order)
 {
     if (!b.ready) { set_error("attractive: the blocked copy of P was not built"); return -1; }
+    if (in_cell_order && b.rows != b.N) { set_error("attractive: the cell order as the caller's order needs all rows"); return -1; }
+    // in_cell_order: the caller keeps its points in this copy's order (a session on one GPU does: it converts where
+    // embeddings enter and leave), so the kernel reads the embedding and adds to the forces where they are: the two
+    // conversions are 18 of the stage's 209 us at N = 10^6
+    const float2 *Yp = in_cell_order ? Y2 : b.Yp, *Yown = in_cell_order ? Y2 : b.Yown;
+    float2 *Fp = in_cell_order ? F2 : b.Fp;
     const unsigned gN = (unsigned)((std::max(b.N, b.rows) + 255) / 256);
-    permute_kernel<<<gN, 256, 0, st>>>(Y2, b.perm, b.N, b.Yp, b.own_perm, b.rows, b.Yown, b.Fp);
+    if (in_cell_order) B200_CUDA(cudaMemsetAsync(F2, 0, sizeof(float2) * (size_t)b.rows, st));
+    else permute_kernel<<<gN, 256, 0, st>>>(Y2, b.perm, b.N, b.Yp, b.own_perm, b.rows, b.Yown, b.Fp);
     BlockedStream s;
     s.ev = b.ev; s.ec = b.ec; s.chunk_row0 = b.chunk_row0; s.tile_chunk0 = b.tile_chunk0;
     s.ntiles = b.ntiles; s.T = b.T; s.C = b.C;
@@ -1072,14 +1079,14 @@ int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, floa
     static const int want_blocks = getenv("B200TSNE_ATTRACTIVE_BLOCKS") ? atoi(getenv("B200TSNE_ATTRACTIVE_BLOCKS")) : 0;
     sms = want_blocks > 0 ? std::min(sms, want_blocks) : sms - sms / 9;
     const int grid = std::max(1, std::min(sms, b.C));
-    attractive_blocked_kernel<<<grid, kBlockedThreads, (size_t)b.T * sizeof(float2), st>>>(s, b.Yp, b.Yown, b.N, b.Fp);
+    attractive_blocked_kernel<<<grid, kBlockedThreads, (size_t)b.T * sizeof(float2), st>>>(s, Yp, Yown, b.N, Fp);
     if (b.extra_C > 0) {   // the reverse-only entries of a truly symmetric P add to the same forces
         BlockedStream x = s;
         x.ev = b.extra_ev; x.ec = b.extra_ec; x.chunk_row0 = b.extra_chunk_row0; x.tile_chunk0 = b.extra_tile_chunk0; x.C = b.extra_C;
-        attractive_blocked_kernel<<<std::max(1, std::min(sms, b.extra_C)), kBlockedThreads, (size_t)b.T * sizeof(float2), st>>>(x, b.Yp, b.Yown, b.N,
-                                                                                                                          b.Fp);
+        attractive_blocked_kernel<<<std::max(1, std::min(sms, b.extra_C)), kBlockedThreads, (size_t)b.T * sizeof(float2), st>>>(x, Yp, Yown, b.N,
+                                                                                                                          Fp);
     }
-    unpermute_kernel<<<(unsigned)((b.rows + 255) / 256), 256, 0, st>>>(b.Fp, b.own_pos, b.row_lo, b.rows, F2);
+    if (!in_cell_order) unpermute_kernel<<<(unsigned)((b.rows + 255) / 256), 256, 0, st>>>(b.Fp, b.own_pos, b.row_lo, b.rows, F2);
     B200_CUDA(cudaGetLastError());
     return 0;
 }

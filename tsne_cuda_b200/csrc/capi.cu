@@ -532,6 +532,7 @@ int b200tsne_session_attach_comm(b200tsne_session *h, const void *id128, int ran
         return B200TSNE_ERR_INVALID;
     }
     B200_CUDA(cudaSetDevice(s.device));
+    B200_TRY(s.set_resident(false));   // a sharded session keeps its state in the natural order
     B200_TRY(comm_acquire(&s.comm, id128, rank, world_size));
     return s.attach_peer_exchange();
 }

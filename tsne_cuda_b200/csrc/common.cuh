@@ -151,7 +151,8 @@ int order_points_by_cell(const float *X, int64_t N, int D, int32_t *perm, cudaSt
 int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const float *P_rows, const int32_t *ids_rows, int64_t N, int K,
                              int64_t row_lo, int64_t row_hi, const int32_t *perm, const ExtraEntries *extra, cudaStream_t st);
 int launch_exclusive_scan_i32(int *data, int64_t n, cudaStream_t st);   // in place; small arrays (one block)
-int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st);
+// in_cell_order: Y2 and F2 are in the copy's own point order (one GPU): no conversion before or after the kernel
+int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, float2 *F2, cudaStream_t st, bool in_cell_order = false);
 
 // repulsive.cu
 struct FftWorkspace {
@@ -188,8 +189,11 @@ int launch_update(const float2 *Y2, const UpdateTargets &dst, const float2 *Fatt
                   float exaggeration, int want_norm, cudaStream_t st);
 int launch_apply_forces_soa(float *Y, float *attr, float *rep, float *gains, float *old_forces, float eta, float Z,
                             float momentum, float exaggeration, int64_t N, cudaStream_t st);
-int launch_soa_to_aos(const float *soa, float2 *aos, int64_t N, cudaStream_t st);
-int launch_aos_to_soa(const float2 *aos, float *soa, int64_t N, cudaStream_t st);
+// perm (optional): position q of the pair array holds point perm[q] of the block-wise (x block, y block) array
+int launch_soa_to_aos(const float *soa, float2 *aos, int64_t N, cudaStream_t st, const int32_t *perm = nullptr);
+int launch_aos_to_soa(const float2 *aos, float *soa, int64_t N, cudaStream_t st, const int32_t *perm = nullptr);
+// dst[q] = src[perm[q]], or with scatter dst[perm[q]] = src[q]
+int launch_reorder_pairs(const float2 *src, float2 *dst, int64_t N, const int32_t *perm, bool scatter, cudaStream_t st);
 int launch_fill(float *p, float v, int64_t n, cudaStream_t st);
 
 }  // namespace b200

@@ -177,7 +177,7 @@ int Session::set_embedding_soa(const float *Y_host, bool reset)
 {
     B200_CUDA(cudaSetDevice(device));
     B200_CUDA(cudaMemcpyAsync(soa_tmp, Y_host, sizeof(float) * 2 * N, cudaMemcpyHostToDevice, stream));
-    B200_TRY(launch_soa_to_aos(soa_tmp, Y2, N, stream));
+    B200_TRY(launch_soa_to_aos(soa_tmp, Y2, N, stream, state_order()));
     if (reset) {
         const int64_t r = std::max<int64_t>(rows(), 1);
         B200_TRY(launch_fill(reinterpret_cast<float *>(gains), 1.0f, 2 * r, stream));
@@ -195,7 +195,7 @@ int Session::set_embedding_soa(const float *Y_host, bool reset)
 int Session::get_embedding_soa(float *Y_host)
 {
     B200_CUDA(cudaSetDevice(device));
-    B200_TRY(launch_aos_to_soa(Y2, soa_tmp, N, stream));
+    B200_TRY(launch_aos_to_soa(Y2, soa_tmp, N, stream, state_order()));
     B200_CUDA(cudaMemcpyAsync(Y_host, soa_tmp, sizeof(float) * 2 * N, cudaMemcpyDeviceToHost, stream));
     B200_CUDA(cudaStreamSynchronize(stream));
     launches += 1;
@@ -208,12 +208,12 @@ int Session::get_optimizer_soa(float *momentum_host, float *gains_host)
     const int64_t r = rows();
     if (r == 0) return 0;
     if (momentum_host) {
-        B200_TRY(launch_aos_to_soa(u, soa_tmp, r, stream));
+        B200_TRY(launch_aos_to_soa(u, soa_tmp, r, stream, state_order()));
         B200_CUDA(cudaMemcpyAsync(momentum_host, soa_tmp, sizeof(float) * 2 * r, cudaMemcpyDeviceToHost, stream));
         B200_CUDA(cudaStreamSynchronize(stream));
     }
     if (gains_host) {
-        B200_TRY(launch_aos_to_soa(gains, soa_tmp, r, stream));
+        B200_TRY(launch_aos_to_soa(gains, soa_tmp, r, stream, state_order()));
         B200_CUDA(cudaMemcpyAsync(gains_host, soa_tmp, sizeof(float) * 2 * r, cudaMemcpyDeviceToHost, stream));
         B200_CUDA(cudaStreamSynchronize(stream));
     }
@@ -227,12 +227,12 @@ int Session::set_optimizer_soa(const float *momentum_host, const float *gains_ho
     if (r == 0) return 0;
     if (momentum_host) {
         B200_CUDA(cudaMemcpyAsync(soa_tmp, momentum_host, sizeof(float) * 2 * r, cudaMemcpyHostToDevice, stream));
-        B200_TRY(launch_soa_to_aos(soa_tmp, u, r, stream));
+        B200_TRY(launch_soa_to_aos(soa_tmp, u, r, stream, state_order()));
         B200_CUDA(cudaStreamSynchronize(stream));
     }
     if (gains_host) {
         B200_CUDA(cudaMemcpyAsync(soa_tmp, gains_host, sizeof(float) * 2 * r, cudaMemcpyHostToDevice, stream));
-        B200_TRY(launch_soa_to_aos(soa_tmp, gains, r, stream));
+        B200_TRY(launch_soa_to_aos(soa_tmp, gains, r, stream, state_order()));
         B200_CUDA(cudaStreamSynchronize(stream));
     }
     return 0;
@@ -377,9 +377,24 @@ int Session::one_iteration(bool want_norm)
 
 int Session::attractive(cudaStream_t st)
 {
-    if (blocked.ready) return launch_attractive_blocked(blocked, Y2, Fattr, st);
+    if (blocked.ready) return launch_attractive_blocked(blocked, Y2, Fattr, st, resident);
     B200_TRY(launch_attractive(P, ids, Y2, N, K, row_lo, row_hi, Fattr, st));
     if (extra.count > 0) B200_TRY(launch_attractive_extra(extra.ptr, extra.ids, extra.val, Y2, N, row_lo, row_hi, Fattr, st));
+    return 0;
+}
+
+int Session::set_resident(bool on)
+{
+    if (on == resident) return 0;
+    if (!blocked.ready || rows() != N) { set_error("session: no point order to keep the state in"); return -1; }
+    // Frep is scratch between iterations
+    float2 *arrays[3] = {Y2, u, gains};
+    for (float2 *a : arrays) {
+        B200_TRY(launch_reorder_pairs(a, Frep, N, blocked.perm, /*scatter=*/!on, stream));
+        B200_CUDA(cudaMemcpyAsync(a, Frep, sizeof(float2) * (size_t)N, cudaMemcpyDeviceToDevice, stream));
+    }
+    B200_CUDA(cudaStreamSynchronize(stream));
+    resident = on;
     return 0;
 }
 
@@ -388,12 +403,17 @@ int Session::build_blocked()
     B200_CUDA(cudaStreamSynchronize(stream));
     B200_CUDA(cudaStreamSynchronize(stream2));
     drop_graphs();   // captured iterations hold the pointers of the previous copy
+    B200_TRY(set_resident(false));   // back to the natural order while the old copy's order still exists
     blocked.clear();
     blocked_arena.release();
     blocked_arena.serve(stream);
     blocked_arena.serve(stream2);
-    return blocked_attractive_build(&blocked, blocked_arena, P, ids, N, K, row_lo, row_hi, cell_order, extra.count > 0 ? &extra : nullptr,
-                                    stream);
+    B200_TRY(blocked_attractive_build(&blocked, blocked_arena, P, ids, N, K, row_lo, row_hi, cell_order, extra.count > 0 ? &extra : nullptr,
+                                      stream));
+    const char *e = getenv("B200TSNE_ATTRACTIVE_RESIDENT");
+    const bool multi = comm && comm->world > 1;
+    if (blocked.ready && !multi && rows() == N && !(e && atoi(e) == 0)) B200_TRY(set_resident(true));
+    return 0;
 }
 
 void Session::drop_graphs()
@@ -535,11 +555,12 @@ int Session::attach_peer_exchange()
     B200_TRY(peer_exchange_acquire(&px, comm, N + 16, stream));
     if (!px) return 0;
     // The grid sum: every rank reads all partial grids ((W - 1) x 2.4 MB over NVLink per rank), or the slice owners
-    // form (2 x 2.4 MB x (W - 1) / W and one more flag round trip).  B200TSNE_GRID_SUM = "all" / "slices"; default:
-    // slices from four ranks on.
+    // form (2 x 2.4 MB x (W - 1) / W and one more flag round trip).  B200TSNE_GRID_SUM = "all" (default) / "slices":
+    // at four ranks the slice owners were measured 3 % slower (6 078 against 6 290 iterations/s at N = 10^6), the extra
+    // round trip costing more than the 3.6 MB less traffic saves; at eight the two should about break even.
     {
         const char *g = getenv("B200TSNE_GRID_SUM");
-        grid_two_shot = g ? strcmp(g, "slices") == 0 : comm->world >= 4;
+        grid_two_shot = g && strcmp(g, "slices") == 0;
     }
     if (grid_two_shot) w_sum = px->ws_local();
     else B200_TRY(arena.alloc((void **)&w_sum, sizeof(float4) * kG * kG));

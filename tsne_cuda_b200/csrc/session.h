@@ -42,6 +42,11 @@ struct Session {
     DeviceArena blocked_arena;
     int32_t *cell_order = nullptr;   // [N] point order by cell (from the points; null = natural order)
     int build_blocked();             // (re)builds `blocked` from P / ids; drops captured iterations
+    // One GPU with the blocked copy: the embedding, momentum and gains live in the copy's point order (`resident`),
+    // so the attractive stage needs no conversion; the accessors convert where values enter and leave.
+    bool resident = false;
+    int set_resident(bool on);       // converts the three arrays when the state changes
+    const int32_t *state_order() const { return resident ? blocked.perm : nullptr; }
     // Opt-in: P truly symmetric, (p + p^T) / 2N, instead of the reference's fixed-width form that drops the mirror
     // image of one-directional edges.  The extra entries of the owned rows live beside P / ids.
     bool symmetric_p = false;
@@ -121,7 +126,7 @@ struct Session {
     int iterate(int n_iters, float min_gradient_norm, float *elapsed_ms, int *iters_done);
     int one_iteration(bool want_norm);
     int attractive(cudaStream_t st);   // Fattr of the owned rows from the current embedding
-    int attractive_launches() const { return blocked.ready ? 3 + (blocked.extra_C > 0) : 1 + (extra.count > 0); }
+    int attractive_launches() const { return blocked.ready ? (resident ? 1 : 3) + (blocked.extra_C > 0) : 1 + (extra.count > 0); }
     int affinities_from_points(const float *X_host, int D, float perplexity, float eps);
 };
 

@@ -102,15 +102,24 @@ __global__ void apply_forces_soa_kernel(float *Y, float *attr, float *rep, float
     attr[i] = 0.0f; attr[N + i] = 0.0f; rep[i] = 0.0f; rep[N + i] = 0.0f;
 }
 
-__global__ void soa_to_aos_kernel(const float *soa, float2 *aos, long long N)
+// perm (optional): position q of the pair array holds point perm[q] of the block-wise array
+__global__ void soa_to_aos_kernel(const float *soa, float2 *aos, long long N, const int32_t *perm)
 {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < N) aos[i] = make_float2(soa[i], soa[N + i]);
+    if (i < N) { const long long j = perm ? perm[i] : i; aos[i] = make_float2(soa[j], soa[N + j]); }
 }
-__global__ void aos_to_soa_kernel(const float2 *aos, float *soa, long long N)
+__global__ void aos_to_soa_kernel(const float2 *aos, float *soa, long long N, const int32_t *perm)
 {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < N) { const float2 v = aos[i]; soa[i] = v.x; soa[N + i] = v.y; }
+    if (i < N) { const long long j = perm ? perm[i] : i; const float2 v = aos[i]; soa[j] = v.x; soa[N + j] = v.y; }
+}
+// dst[q] = src[perm[q]] (gather) or dst[perm[q]] = src[q] (scatter)
+__global__ void reorder_pairs_kernel(const float2 *src, float2 *dst, long long N, const int32_t *perm, int scatter)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    if (scatter) dst[perm[i]] = src[i];
+    else dst[i] = src[perm[i]];
 }
 __global__ void fill_kernel(float *p, float v, long long n)
 {
@@ -144,17 +153,25 @@ int launch_apply_forces_soa(float *Y, float *attr, float *rep, float *gains, flo
     return 0;
 }
 
-int launch_soa_to_aos(const float *soa, float2 *aos, int64_t N, cudaStream_t st)
+int launch_soa_to_aos(const float *soa, float2 *aos, int64_t N, cudaStream_t st, const int32_t *perm)
 {
     if (N <= 0) return 0;
-    soa_to_aos_kernel<<<nblk(N, 256), 256, 0, st>>>(soa, aos, N);
+    soa_to_aos_kernel<<<nblk(N, 256), 256, 0, st>>>(soa, aos, N, perm);
     B200_CUDA(cudaGetLastError());
     return 0;
 }
-int launch_aos_to_soa(const float2 *aos, float *soa, int64_t N, cudaStream_t st)
+int launch_aos_to_soa(const float2 *aos, float *soa, int64_t N, cudaStream_t st, const int32_t *perm)
 {
     if (N <= 0) return 0;
-    aos_to_soa_kernel<<<nblk(N, 256), 256, 0, st>>>(aos, soa, N);
+    aos_to_soa_kernel<<<nblk(N, 256), 256, 0, st>>>(aos, soa, N, perm);
+    B200_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_reorder_pairs(const float2 *src, float2 *dst, int64_t N, const int32_t *perm, bool scatter, cudaStream_t st)
+{
+    if (N <= 0) return 0;
+    reorder_pairs_kernel<<<nblk(N, 256), 256, 0, st>>>(src, dst, N, perm, scatter ? 1 : 0);
     B200_CUDA(cudaGetLastError());
     return 0;
 }
