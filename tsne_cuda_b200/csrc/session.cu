@@ -283,6 +283,13 @@ int Session::one_iteration(bool want_norm)
         B200_CUDA(cudaMemsetAsync(px->w_local(px->parity ^ 1), 0, sizeof(float4) * kG * kG, stream));
     }
 
+    // The attractive kernel (one block per SM on 8/9 of the SMs) and the grid pipeline run side by side.  Timestamps
+    // taken inside the kernels at N = 10^6 (one GPU): the attractive kernel runs 190 us and ends 37 us before the
+    // update can start; the pipeline, 90 us when it has the GPU to itself, takes 229 us on the SMs that are left and
+    // is what the update waits for.  More SMs for the pipeline slow the attractive kernel by as much as they speed
+    // the pipeline up (124, 132 and 140 attractive blocks: 3 940, 3 955, 3 905 iterations/s): the iteration is bound
+    // by the SM time of its kernels, not by their overlap.  Neither a higher stream priority for the attractive
+    // kernel nor holding the pipeline back until its blocks are resident (they are within 8 us anyway) changed it.
     if (!stage_timers) {
         B200_CUDA(cudaEventRecord(ev_fork, stream));
         B200_CUDA(cudaStreamWaitEvent(stream2, ev_fork, 0));
