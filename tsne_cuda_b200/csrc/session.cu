@@ -290,6 +290,9 @@ int Session::one_iteration(bool want_norm)
     // the pipeline up (124, 132 and 140 attractive blocks: 3 940, 3 955, 3 905 iterations/s): the iteration is bound
     // by the SM time of its kernels, not by their overlap.  Neither a higher stream priority for the attractive
     // kernel nor holding the pipeline back until its blocks are resident (they are within 8 us anyway) changed it.
+    // Inside the pipeline it is the spread that suffers: 118 us on the 16 spare SMs against 28 alone (scatter 37
+    // against 26; FFT and gather as when alone), 60 us when 32 SMs are spared, which costs the attractive kernel more.
+    // An L2 evict-first policy on the attractive kernel's stream loads: +0.8 %, not kept.
     if (!stage_timers) {
         B200_CUDA(cudaEventRecord(ev_fork, stream));
         B200_CUDA(cudaStreamWaitEvent(stream2, ev_fork, 0));
