@@ -598,9 +598,9 @@ int Session::affinities_from_points(const float *X_host, int D, float perplexity
     const int64_t npad = multi ? chunk * comm->world : N;
 
     StageClock clk(this);
-    clk.begin(stream);
     B200_TRY(tmp.alloc((void **)&X, sizeof(float) * N * D));
     B200_CUDA(cudaMemcpyAsync(X, X_host, sizeof(float) * N * D, cudaMemcpyHostToDevice, stream));
+    clk.begin(stream);   // the search itself: the points are on their way
     B200_TRY(tmp.alloc((void **)&d2, sizeof(float) * std::max<int64_t>(chunk, 1) * K));
     B200_TRY(tmp.alloc((void **)&max_enc, sizeof(unsigned int)));
     // Every rank holds all the points.  By default the QUERIES are sharded: a rank searches its own
@@ -610,7 +610,16 @@ int Session::affinities_from_points(const float *X_host, int D, float perplexity
     // searches all queries against its own rows, and the owners of the query rows receive the
     // partial lists (all-to-all) and merge them.  Both give the same lists bit for bit.
     const char *shard_env = getenv("B200TSNE_KNN_SHARD");
-    const bool db_sharded = multi && shard_env && strcmp(shard_env, "database") == 0;
+    bool db_sharded = multi && shard_env && strcmp(shard_env, "database") == 0;
+    if (multi && !shard_env && knn_tc_supported(N, D, K)) {
+        // no wish stated: shard the database when the operand images of ALL points and the buffers of this rank's
+        // queries would not fit in half of what is free (every rank decides alike: same sizes, and the ranks of a
+        // node have the same memory)
+        size_t free_b = 0, total_b = 0;
+        B200_CUDA(cudaMemGetInfo(&free_b, &total_b));
+        const int64_t batch = std::min<int64_t>(std::max<int64_t>(r, 1), 1 << 20);
+        if (knn_tc_workspace_bytes(D, K, batch, N) > total_b / 2) db_sharded = true;
+    }
     if (!db_sharded) {
         B200_TRY(knn_search(X, N, D, K, row_lo, row_hi, 0, N, ids, d2, &knn_stats, stream));
     } else {
