@@ -1286,9 +1286,18 @@ knn_tc_pick_kernel(const float *__restrict__ cand_key, const int32_t *__restrict
     }
     unsigned int v = 0xffffffffu;   // with fewer than k keys everything is kept
     if (n > k) {
-        unsigned int lo = 0u, hi = 0xfffffffeu;
+        // bisection between the smallest and the largest key of the buffer: they share their leading bits, so about
+        // half of the 32 steps of a search over all encodings are enough
+        unsigned int lo = 0xffffffffu, hi = 0u;
+#pragma unroll
+        for (int j = 0; j < SLOTS; j++) {
+            if (j >= jmax) break;
+            if (lane + 32 * j < n) { lo = min(lo, enc[j]); hi = max(hi, enc[j]); }
+        }
+        lo = __reduce_min_sync(0xffffffffu, lo);
+        hi = __reduce_max_sync(0xffffffffu, hi);
 #pragma unroll 1
-        for (int it = 0; it < 32; it++) {
+        for (int it = 0; it < 32 && lo < hi; it++) {
             const unsigned int mid = lo + ((hi - lo) >> 1);
             int cnt = 0;
 #pragma unroll
