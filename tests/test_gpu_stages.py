@@ -253,3 +253,18 @@ def test_stages_vs_live_reference_kernels(engine, oracle_cpu):
         F_o, _ = oracle_cpu.repulsive(Y)
         assert rel_l2(F, F_r) < max(1e-4, 2 * rel_l2(F_r, F_o))
         assert abs(Z - Z_r) / abs(Z_r) < 1e-4
+
+
+@pytest.mark.parametrize("shift,scale", [(0.0, 1.0), (300.0, 1.0), (0.0, 1e-18), (0.0, 1e12)])
+def test_knn_tensor_core_exact_whatever_the_norms(engine, monkeypatch, shift, scale):
+    """The filter's keys lose accuracy with |x_i||x_j|: far from the origin the proof closes for fewer rows (they go to
+    the SIMT search), at tiny or huge scales the bf16 pairs lose their low parts or their range.  Whatever happens to
+    the filter, the lists must equal the SIMT search's on every row."""
+    rng = np.random.default_rng(5)
+    X = ((rng.standard_normal((70000, 8)) + shift) * scale).astype(np.float32)
+    a = engine.knn(X, 30)
+    assert engine.knn_last_stats()["tensor_core"] == 1
+    monkeypatch.setenv("B200TSNE_KNN", "simt")
+    b = engine.knn(X, 30)
+    assert engine.knn_last_stats()["tensor_core"] == 0
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
