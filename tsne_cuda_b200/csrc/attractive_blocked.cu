@@ -338,17 +338,23 @@ own_scatter_kernel(const int32_t *__restrict__ perm, long long N, long long row_
 // ---- walking the rows of a range: per-warp scratch ----
 constexpr int kWalkWarps = 1;
 constexpr int kMaxK = 1024;
-struct WalkScratch {
-    long long run[kMaxTiles];      // count pass: entries this range adds to the tile; fill pass: next free entry of the tile
-    int rowcnt[kMaxTiles];         // entries of the current row per tile
-    unsigned slot[kMaxK];          // per slot of the current row, see kSlot*; 0xffffffff = unused slot
-    unsigned short col[kMaxK];     // per slot: column inside the tile
+// MAXT tiles and MAXS slots per segment: the common case (up to 64 tiles, rows of up to 128 slots) has a scratch of
+// 3 KB, so that a block's one warp shares its SM with 31 others; the general one (1,024 of each) takes 38 KB and
+// five warps fill an SM (the walk is a chain of dependent round trips: 14 ms against 5 at N = 10^6, K = 90).
+template <int MAXT, int MAXS>
+struct WalkScratchT {
+    long long run[MAXT];           // count pass: entries this range adds to the tile; fill pass: next free entry of the tile
+    int rowcnt[MAXT];              // entries of the current row per tile
+    unsigned slot[MAXS];           // per slot of the current row, see kSlot*; 0xffffffff = unused slot
+    unsigned short col[MAXS];      // per slot: column inside the tile
     unsigned bitmap[2][32];        // tiles touched by the previous / the current row
     // fill pass, per tile: bank pairs already taken in the half-warp window (16 lanes) that holds the tile's cursor
     // and in the window after it: bit 16 k + b = "the k-th gather of that window reads bank pair b"
-    unsigned long long win[kMaxTiles][2];
-    int win_id[kMaxTiles];         // absolute lane / 16 of win[.][0]
+    unsigned long long win[MAXT][2];
+    int win_id[MAXT];              // absolute lane / 16 of win[.][0]
 };
+using WalkScratchSmall = WalkScratchT<64, 128>;
+using WalkScratch = WalkScratchT<kMaxTiles, kMaxK>;
 // slot word: bits 16..25 tile, bit 30 first slot of its (row, tile) group; low 16 bits: rank inside the group in
 // slot order, later the cell (4 x lane of the group + entry) the slot's entry is written to
 constexpr unsigned kSlotUnused = 0xffffffffu, kSlotLeader = 1u << 30;
@@ -370,6 +376,7 @@ struct WalkArgs {
     int K, T, ntiles, range_rows;  // range_rows: segments per range
     long long n_ranges;
     int greedy;                    // place a group's entries by bank pair (place_group) instead of in slot order
+    int max_len;                   // the longest segment (K when the width is fixed)
 };
 struct Segment {
     long long lr, base;
@@ -394,7 +401,8 @@ __device__ __forceinline__ Segment get_segment(const WalkArgs &a, long long g)
 }
 
 // slot table, per-tile counts and the tile bitmap of one row
-__device__ __forceinline__ void analyse_row(const WalkArgs &a, const Segment &sg, WalkScratch &s, unsigned *bitmap, int lane)
+template <class S>
+__device__ __forceinline__ void analyse_row(const WalkArgs &a, const Segment &sg, S &s, unsigned *bitmap, int lane)
 {
     for (int k0 = 0; k0 < sg.len; k0 += 32) {
         const int sl = k0 + lane;
@@ -444,7 +452,8 @@ struct GroupGeom {
 // per tile, the bank pairs already taken in each of the four passes of the current half-warp window, and gives
 // every entry the first free cell of its group whose pass does not have the entry's bank pair yet (else the
 // first free cell).  Groups of more than 32 entries keep the slot order.  Returns the cells taken (bit per cell).
-__device__ __forceinline__ unsigned place_group(WalkScratch &s, int K, int t, int cnt, long long first_lane)
+template <class S>
+__device__ __forceinline__ unsigned place_group(S &s, int K, int t, int cnt, long long first_lane)
 {
     const int n_lanes = (cnt + 3) >> 2;
     const int w0 = (int)(first_lane >> 4);
@@ -479,8 +488,8 @@ __device__ __forceinline__ unsigned place_group(WalkScratch &s, int K, int t, in
 }
 
 // FILL = false: add the row's groups to run[] (sizes) and count them.  FILL = true: write the row's entries.
-template <bool FILL>
-__device__ __forceinline__ void emit_row(const WalkArgs &a, const Segment &sg, WalkScratch &s, const unsigned *prev, int lane,
+template <bool FILL, class S>
+__device__ __forceinline__ void emit_row(const WalkArgs &a, const Segment &sg, S &s, const unsigned *prev, int lane,
                                          float *__restrict__ ev, uint16_t *__restrict__ ec, int *__restrict__ chunk_row0,
                                          unsigned long long &n_groups)
 {
@@ -554,14 +563,14 @@ __device__ __forceinline__ void emit_row(const WalkArgs &a, const Segment &sg, W
 
 // A warp walks the rows of one range in order.  Count pass: range_size[t][range] = entries (padding and
 // markers included) the range puts into tile t.  Fill pass: starts from tile_start[t] + range_off[t][range].
-template <bool FILL>
+template <bool FILL, class S>
 __global__ void __launch_bounds__(kWalkWarps * 32)
 walk_kernel(WalkArgs a, unsigned *__restrict__ range_size, const unsigned *__restrict__ range_off, const long long *__restrict__ tile_start,
             float *__restrict__ ev, uint16_t *__restrict__ ec, int *__restrict__ chunk_row0, unsigned long long *__restrict__ totals)
 {
-    __shared__ WalkScratch scratch[kWalkWarps];
+    __shared__ S scratch[kWalkWarps];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    WalkScratch &s = scratch[w];
+    S &s = scratch[w];
     const long long range = (long long)blockIdx.x * kWalkWarps + w;
     if (range >= a.n_ranges) return;
     for (int t = lane; t < a.ntiles; t += 32) {
@@ -592,7 +601,7 @@ walk_kernel(WalkArgs a, unsigned *__restrict__ range_size, const unsigned *__res
         s.bitmap[cur][lane] = 0u;
         __syncwarp();
         analyse_row(a, sg, s, s.bitmap[cur], lane);
-        emit_row<FILL>(a, sg, s, s.bitmap[cur ^ 1], lane, ev, ec, chunk_row0, n_groups);
+        emit_row<FILL, S>(a, sg, s, s.bitmap[cur ^ 1], lane, ev, ec, chunk_row0, n_groups);
         cur ^= 1;
     }
     if (!FILL) {
@@ -603,12 +612,13 @@ walk_kernel(WalkArgs a, unsigned *__restrict__ range_size, const unsigned *__res
 }
 
 // distinct tiles and valid entries of a sample of rows: totals[1] += groups, totals[2] += entries
+template <class S>
 __global__ void __launch_bounds__(kWalkWarps * 32)
 sample_kernel(WalkArgs a, long long n_samples, unsigned long long *__restrict__ totals)
 {
-    __shared__ WalkScratch scratch[kWalkWarps];
+    __shared__ S scratch[kWalkWarps];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    WalkScratch &s = scratch[w];
+    S &s = scratch[w];
     const long long k = (long long)blockIdx.x * kWalkWarps + w;
     if (k >= n_samples) return;
     for (int t = lane; t < a.ntiles; t += 32) s.rowcnt[t] = 0;
@@ -898,7 +908,10 @@ int build_stream(StreamOut *out, DeviceArena &arena, DeviceArena &tmp, WalkArgs 
     B200_TRY(tmp.alloc((void **)&totals, sizeof(h_tot)));
     B200_CUDA(cudaMemsetAsync(totals, 0, sizeof(h_tot), st));
     const long long n_samples = std::min<long long>(a.n_seg, 4096);
-    sample_kernel<<<(unsigned)((n_samples + kWalkWarps - 1) / kWalkWarps), kWalkWarps * 32, 0, st>>>(a, n_samples, totals);
+    // the small scratch when the tiles and the longest segment fit it
+    const bool small = ntiles <= 64 && a.max_len <= 128;
+    if (small) sample_kernel<WalkScratchSmall><<<(unsigned)((n_samples + kWalkWarps - 1) / kWalkWarps), kWalkWarps * 32, 0, st>>>(a, n_samples, totals);
+    else sample_kernel<WalkScratch><<<(unsigned)((n_samples + kWalkWarps - 1) / kWalkWarps), kWalkWarps * 32, 0, st>>>(a, n_samples, totals);
     B200_CUDA(cudaGetLastError());
     B200_CUDA(cudaMemcpyAsync(h_tot, totals, sizeof(h_tot), cudaMemcpyDeviceToHost, st));
     B200_CUDA(cudaStreamSynchronize(st));
@@ -913,7 +926,8 @@ int build_stream(StreamOut *out, DeviceArena &arena, DeviceArena &tmp, WalkArgs 
     B200_TRY(tmp.alloc((void **)&tile_start, sizeof(long long) * (ntiles + 1)));
     B200_TRY(arena.alloc((void **)&out->tile_chunk0, sizeof(int) * (ntiles + 1)));
     const unsigned walk_blocks = (unsigned)((a.n_ranges + kWalkWarps - 1) / kWalkWarps);
-    walk_kernel<false><<<walk_blocks, kWalkWarps * 32, 0, st>>>(a, range_size, nullptr, nullptr, nullptr, nullptr, nullptr, totals);
+    if (small) walk_kernel<false, WalkScratchSmall><<<walk_blocks, kWalkWarps * 32, 0, st>>>(a, range_size, nullptr, nullptr, nullptr, nullptr, nullptr, totals);
+    else walk_kernel<false, WalkScratch><<<walk_blocks, kWalkWarps * 32, 0, st>>>(a, range_size, nullptr, nullptr, nullptr, nullptr, nullptr, totals);
     tile_scan_kernel<<<ntiles, 1024, 0, st>>>(range_size, a.n_ranges, tile_total);
     tile_layout_kernel<<<1, 1, 0, st>>>(tile_total, ntiles, tile_start, out->tile_chunk0, totals);
     B200_CUDA(cudaGetLastError());
@@ -927,7 +941,8 @@ int build_stream(StreamOut *out, DeviceArena &arena, DeviceArena &tmp, WalkArgs 
     B200_CUDA(cudaMemsetAsync(out->ev, 0, sizeof(float) * E, st));
     B200_CUDA(cudaMemsetAsync(out->ec, 0, sizeof(uint16_t) * E, st));
     B200_CUDA(cudaMemsetAsync(out->chunk_row0, 0, sizeof(int) * (E / kChunk), st));
-    walk_kernel<true><<<walk_blocks, kWalkWarps * 32, 0, st>>>(a, nullptr, range_size, tile_start, out->ev, out->ec, out->chunk_row0, totals);
+    if (small) walk_kernel<true, WalkScratchSmall><<<walk_blocks, kWalkWarps * 32, 0, st>>>(a, nullptr, range_size, tile_start, out->ev, out->ec, out->chunk_row0, totals);
+    else walk_kernel<true, WalkScratch><<<walk_blocks, kWalkWarps * 32, 0, st>>>(a, nullptr, range_size, tile_start, out->ev, out->ec, out->chunk_row0, totals);
     B200_CUDA(cudaGetLastError());
     B200_CUDA(cudaStreamSynchronize(st));   // the temporaries of the caller may go away
     out->C = (int)(E / kChunk);
@@ -985,7 +1000,7 @@ int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const flo
     WalkArgs a;
     memset(&a, 0, sizeof(a));
     a.val = P_rows; a.ids = ids_rows; a.pos = pos; a.own_perm = own_perm;
-    a.N = N; a.row_lo = row_lo; a.n_seg = rows; a.K = K; a.T = T; a.ntiles = ntiles;
+    a.N = N; a.row_lo = row_lo; a.n_seg = rows; a.K = K; a.T = T; a.ntiles = ntiles; a.max_len = K;
     StreamOut main_stream, extra_stream;
     B200_TRY(build_stream(&main_stream, arena, tmp, a, forced ? 0.0f : kMinEntriesPerGroup, st));
     b->entries_per_group = main_stream.entries_per_group;
@@ -1011,7 +1026,7 @@ int blocked_attractive_build(BlockedAttractive *b, DeviceArena &arena, const flo
         B200_CUDA(cudaGetLastError());
         WalkArgs e = a;
         e.val = extra->val; e.ids = extra->ids;
-        e.seg_row = seg_row; e.seg_base = seg_base; e.seg_len = seg_len; e.n_seg = n_seg;
+        e.seg_row = seg_row; e.seg_base = seg_base; e.seg_len = seg_len; e.n_seg = n_seg; e.max_len = kMaxK;
         B200_TRY(build_stream(&extra_stream, arena, tmp, e, 0.0f, st));
         if (!extra_stream.built) { set_error("attractive: the stream of the reverse-only entries could not be built"); return -4; }
     }
