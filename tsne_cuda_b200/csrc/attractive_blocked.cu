@@ -896,9 +896,9 @@ int build_stream(StreamOut *out, DeviceArena &arena, DeviceArena &tmp, WalkArgs 
     *out = StreamOut();
     if (a.n_seg <= 0) return 0;
     const int ntiles = a.ntiles;
-    // Measured at N = 10^6, K = 90: placing by bank pair takes the kernel from 190 to 185 us per iteration and the
-    // set-up from 15 to 74 ms (one lane per group walks the group's entries): it pays from 12,000 iterations on, so
-    // it is off unless B200TSNE_ATTRACTIVE_PLACE=1 asks for it.
+    // Measured at N = 10^6, K = 90: placing by bank pair takes the attractive stage from 197 to 191 us per iteration
+    // and the set-up from 0.190 to 0.217 s (one lane per group walks the group's entries): it pays from 4,500
+    // iterations on, so it is off unless B200TSNE_ATTRACTIVE_PLACE=1 asks for it.
     a.greedy = getenv("B200TSNE_ATTRACTIVE_PLACE") ? atoi(getenv("B200TSNE_ATTRACTIVE_PLACE")) : 0;
     a.range_rows = 64;
     while ((a.n_seg + a.range_rows - 1) / a.range_rows * ntiles > (1ll << 24)) a.range_rows *= 2;
