@@ -1089,10 +1089,13 @@ int launch_attractive_blocked(const BlockedAttractive &b, const float2 *Y2, floa
     }
     // A block fills its SM (1,024 threads, all registers, 224 KB of shared memory), so the grid pipeline that runs
     // beside this kernel on the other stream only gets the SMs this kernel leaves alone.  Measured at N = 10^6,
-    // K = 90 on 148 SMs: 148 blocks 3,680 iterations/s (attractive stage 196 us), 140: 3,854, 132: 3,896 (214 us),
-    // 116: 3,821.  Default: one SM in nine stays free; B200TSNE_ATTRACTIVE_BLOCKS overrides.
+    // K = 90 on 148 SMs, one GPU: 148 blocks 3,645 iterations/s (attractive stage 175 us), 140: 3,906, 132: 3,962
+    // (196 us), 124: 3,936.  A rank of a sharded run has fewer rows for this kernel and the same grid pipeline
+    // plus the meetings beside it: two GPUs 132 blocks 5,092 iterations/s, 116: 5,498, 100: 5,413, 92: 5,508, 74:
+    // 4,991; four GPUs 132: 6,302, 100: 7,159, 80: 6,935, 64: 6,579, 48: 5,926.  Default: one SM in nine stays free
+    // when the copy holds all rows, one in three when it holds a rank's share; B200TSNE_ATTRACTIVE_BLOCKS overrides.
     static const int want_blocks = getenv("B200TSNE_ATTRACTIVE_BLOCKS") ? atoi(getenv("B200TSNE_ATTRACTIVE_BLOCKS")) : 0;
-    sms = want_blocks > 0 ? std::min(sms, want_blocks) : sms - sms / 9;
+    sms = want_blocks > 0 ? std::min(sms, want_blocks) : (b.rows == b.N ? sms - sms / 9 : sms - sms / 3);
     const int grid = std::max(1, std::min(sms, b.C));
     attractive_blocked_kernel<<<grid, kBlockedThreads, (size_t)b.T * sizeof(float2), st>>>(s, Yp, Yown, b.N, Fp);
     if (b.extra_C > 0) {   // the reverse-only entries of a truly symmetric P add to the same forces
