@@ -565,12 +565,13 @@ int Session::attach_peer_exchange()
     B200_TRY(peer_exchange_acquire(&px, comm, N + 16, stream));
     if (!px) return 0;
     // The grid sum: every rank reads all partial grids ((W - 1) x 2.4 MB over NVLink per rank), or the slice owners
-    // form (2 x 2.4 MB x (W - 1) / W and one more flag round trip).  B200TSNE_GRID_SUM = "all" (default) / "slices":
-    // at four ranks the slice owners were measured 3 % slower (6 078 against 6 290 iterations/s at N = 10^6), the extra
-    // round trip costing more than the 3.6 MB less traffic saves; at eight the two should about break even.
+    // form (2 x 2.4 MB x (W - 1) / W and one more flag round trip).  B200TSNE_GRID_SUM = "all" / "slices"; default:
+    // slices from eight ranks on.  Measured at N = 10^6: four ranks, slices 3 % slower (6 078 against 6 290
+    // iterations/s: the extra round trip costs more than 3.6 MB less traffic saves); eight ranks, slices 12 % faster
+    // (7 807 against 6 939: 4.2 MB instead of 16.8 MB per rank and iteration).
     {
         const char *g = getenv("B200TSNE_GRID_SUM");
-        grid_two_shot = g && strcmp(g, "slices") == 0;
+        grid_two_shot = g ? strcmp(g, "slices") == 0 : comm->world >= 8;
     }
     if (grid_two_shot) w_sum = px->ws_local();
     else B200_TRY(arena.alloc((void **)&w_sum, sizeof(float4) * kG * kG));
